@@ -1,0 +1,111 @@
+/*
+ * ternix_b200 -- C ABI of the B200 (sm_100a) ternary matrix product
+ *
+ *      C[M,N] int32  =  A[M,K] int8  x  W[K,N] ternary
+ *
+ * W stays in TernixEngine's packed format: row-major K x (N/4) bytes, four weights per byte,
+ * weight j of a group in bits 2j..2j+1, code 00 -> 0, 01 -> +1, 11 -> -1 (code 10 is never produced by
+ * the packer and is undefined input).  All arithmetic is exact integer arithmetic.
+ *
+ * This header is what a foreign-function binding (ctypes, cgo, JNI, ...) binds.  Plain pointers and
+ * sizes only; every function returns a status code; nothing throws.  The C++ `ternix::` functions of
+ * include/ternix/ and the `ternix_engine` Python module are thin callers of these entry points.
+ * There is no CPU fallback: a device entry point on a machine without a usable GPU fails with
+ * TERNIX_B200_ERR_CUDA.
+ *
+ * Each entry point names the reference interface it replaces (path inside the reference project).
+ */
+#ifndef TERNIX_B200_H
+#define TERNIX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes --------------------------------------------------------------------------- */
+#define TERNIX_B200_OK                 0
+#define TERNIX_B200_ERR_INVALID_SHAPE  1  /* M,K,N out of domain (N % 4 != 0, negative, too large)  */
+#define TERNIX_B200_ERR_INVALID_ARG    2  /* null pointer, bad enum, bad pitch                       */
+#define TERNIX_B200_ERR_CUDA           3  /* a CUDA call failed; see ternix_b200_last_cuda_error()   */
+#define TERNIX_B200_ERR_TIMEOUT        4  /* a bounded device-side wait ran out (kernel returned)    */
+#define TERNIX_B200_ERR_UNSUPPORTED    5  /* the kernel that was asked for cannot take this problem  */
+
+/* ---- kernel selectors ------------------------------------------------------------------------ */
+#define TERNIX_B200_KERNEL_AUTO     0  /* pick by shape and alignment                                 */
+#define TERNIX_B200_KERNEL_GENERIC  1  /* any M, K; N % 4 == 0; any pitch or alignment                */
+#define TERNIX_B200_KERNEL_GEMV     2  /* decode regime, M <= 16: TMA-streamed packed W, dp4a         */
+#define TERNIX_B200_KERNEL_GEMM_TC  3  /* prefill regime: TMA + tcgen05 kind::i8, int32 in TMEM       */
+
+const char *ternix_b200_status_string(int status);
+/* cudaError_t (as int) of the last failing CUDA call made by the calling thread, 0 if none. */
+int ternix_b200_last_cuda_error(void);
+/* Text of a cudaError_t value (cudaGetErrorString), so that bindings need not link the CUDA runtime. */
+const char *ternix_b200_cuda_error_string(int cuda_error);
+/* Library version, major*10000 + minor*100 + patch. */
+int ternix_b200_version(void);
+
+/* ---- host side: the packed weight format -------------------------------------------------------
+ * replaces: ternix::pack_ternary_weights / unpack_ternary_weights / interleave_weights_offline,
+ *           include/ternix/bitpack.hpp:6-8, src/bitpack.cpp:5-33.  Byte-for-byte the same output;
+ *           `size` counts weights, size/4 bytes are produced (a tail of size%4 weights is dropped). */
+void ternix_b200_pack_ternary(uint8_t *packed, const int8_t *unpacked, size_t size);
+void ternix_b200_unpack_ternary(int8_t *unpacked, const uint8_t *packed, size_t size);
+void ternix_b200_interleave_offline(uint8_t *interleaved, const uint8_t *packed, size_t size);
+/* Index of the first value outside {-1,0,+1}, or -1 if all are in the domain
+ * (the check bindings/python/pybind11_wrapper.cpp:26-27 makes before packing). */
+long long ternix_b200_find_non_ternary(const int8_t *unpacked, size_t size);
+/* Copy the column shard [n0, n0+n_cols) of a packed K x (N/4) matrix into a packed K x (n_cols/4)
+ * matrix (n0, n_cols multiples of 4).  Host memory.  Used for N-column sharding across GPUs. */
+int ternix_b200_slice_columns(uint8_t *dst, const uint8_t *packed, size_t K, size_t N, size_t n0, size_t n_cols);
+
+/* ---- device side -----------------------------------------------------------------------------
+ * replaces: ternix::mul_mat_ternary_cuda_naive / _tiled, include/ternix/cuda_kernels.cuh:11-17,
+ *           src/cuda_kernels.cu:126-140.
+ * dA [M,K] int8 row-major, dW packed K x (N/4), dC [M,N] int32 row-major: device pointers.
+ * Asynchronous on `stream` (a cudaStream_t passed as void*; NULL = default stream).  C is fully
+ * overwritten.  Shape errors are reported before any pointer is touched.  Launch errors are returned;
+ * errors that occur while the kernel runs surface at the next synchronisation on the stream. */
+int ternix_b200_matmul(const int8_t *dA, const uint8_t *dW, int32_t *dC, int M, int K, int N, void *stream);
+
+/* Same, with control: `kernel` is one of TERNIX_B200_KERNEL_*; `ldc` is the row pitch of C in int32
+ * elements (>= N), so a column shard can be written straight into its place in a wider matrix;
+ * `d_status`, if not NULL, is a device int32 that a kernel sets to TERNIX_B200_ERR_TIMEOUT when one of
+ * its bounded waits runs out (the caller zeroes it and reads it after synchronising). */
+int ternix_b200_matmul_ex(const int8_t *dA, const uint8_t *dW, int32_t *dC, int M, int K, int N, long long ldc,
+                          int kernel, int32_t *d_status, void *stream);
+
+/* The kernel TERNIX_B200_KERNEL_AUTO would choose for this problem (no GPU needed). */
+int ternix_b200_select_kernel(const void *dA, const void *dW, const void *dC, int M, int K, int N, long long ldc);
+
+/* replaces: ternix::mul_mat_ternary_cuda_host, include/ternix/cuda_kernels.cuh:20-21,
+ *           src/cuda_kernels.cu:142-156.  HOST pointers: allocates, copies in, runs, copies back,
+ *           frees, synchronises.  Also the target of the CPU-named ternix::mul_mat_ternary_* shims. */
+int ternix_b200_matmul_host(const int8_t *A, const uint8_t *W_packed, int32_t *C, int M, int K, int N, int kernel);
+
+/* ---- N-column sharding plan (host arithmetic only) ---------------------------------------------
+ * Splits N columns over `world` ranks in granules of `granule` columns (a multiple of 4; 64 keeps each
+ * shard's packed rows 16-byte aligned).  Writes the first column and the column count of `rank`.
+ * Shards differ by at most one granule; trailing ranks may get zero columns when N is small. */
+int ternix_b200_shard_columns(int N, int world, int rank, int granule, int *n0, int *n_cols);
+
+/* Scatter a rank-major gather buffer [world][M][n_pad] (what an all-gather of equal-sized blocks
+ * delivers) into row-major dC[M, ldc] using the plan above.  Device pointers, asynchronous. */
+int ternix_b200_unpack_gathered(const int32_t *d_gathered, int32_t *dC, int M, int N, long long ldc, int world,
+                                int granule, int n_pad, void *stream);
+
+/* ---- seeded synthetic inputs (host) ----------------------------------------------------------
+ * Counter-based generator (splitmix64 of seed and index), so any slice can be regenerated anywhere.
+ * mode 0: int8 uniform on [-128,127]; mode 1: uniform on [-127,127]. */
+void ternix_b200_synth_activations(int8_t *A, size_t count, uint64_t seed, int mode);
+/* iid ternary with P(-1) = P(+1) = 0.3, P(0) = 0.4, already packed: K x (N/4) bytes. */
+void ternix_b200_synth_packed_weights(uint8_t *W_packed, size_t K, size_t N, uint64_t seed);
+/* The same weights, unpacked, for checking: K x N int8. */
+void ternix_b200_synth_weights(int8_t *W, size_t K, size_t N, uint64_t seed);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TERNIX_B200_H */

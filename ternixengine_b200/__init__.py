@@ -1,0 +1,306 @@
+"""B200-native ternary matrix product behind TernixEngine's API.
+
+    C[M,N] int32 = A[M,K] int8 x W[K,N] ternary, W packed K x (N/4) bytes (00 -> 0, 01 -> +1, 11 -> -1)
+
+This package is the Python host side: a ctypes binding of the C ABI (``include/ternix_b200.h``,
+built in-tree as ``libternix_b200.so``) plus the N-column sharding layer that runs one process
+per GPU over ``torch.distributed``.  PyTorch is used for device memory, streams and the process
+group only; all arithmetic happens in the library's own sm_100a kernels.  There is no CPU
+implementation here and no fallback: if the library is missing, importing fails.
+
+The reference's Python surface (``bindings/python/pybind11_wrapper.cpp:75-98``: ``pack_ternary``,
+``unpack_ternary``, ``ternary_matmul``, ``has_cuda``) is re-exported from the compiled module
+``ternix_engine`` that is built next to this file.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libternix_b200.so")
+
+OK = 0
+ERR_INVALID_SHAPE = 1
+ERR_INVALID_ARG = 2
+ERR_CUDA = 3
+ERR_TIMEOUT = 4
+ERR_UNSUPPORTED = 5
+
+KERNEL_AUTO = 0
+KERNEL_GENERIC = 1
+KERNEL_GEMV = 2
+KERNEL_GEMM_TC = 3
+KERNELS = {"auto": KERNEL_AUTO, "generic": KERNEL_GENERIC, "gemv": KERNEL_GEMV, "gemm_tc": KERNEL_GEMM_TC}
+
+# every symbol include/ternix_b200.h declares
+EXPORTS = (
+    "ternix_b200_status_string", "ternix_b200_last_cuda_error", "ternix_b200_cuda_error_string",
+    "ternix_b200_version",
+    "ternix_b200_pack_ternary", "ternix_b200_unpack_ternary", "ternix_b200_interleave_offline",
+    "ternix_b200_find_non_ternary", "ternix_b200_slice_columns",
+    "ternix_b200_matmul", "ternix_b200_matmul_ex", "ternix_b200_select_kernel", "ternix_b200_matmul_host",
+    "ternix_b200_shard_columns", "ternix_b200_unpack_gathered",
+    "ternix_b200_synth_activations", "ternix_b200_synth_packed_weights", "ternix_b200_synth_weights",
+)
+
+
+class TernixError(RuntimeError):
+    def __init__(self, status: int, what: str):
+        super().__init__(what)
+        self.status = status
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(_LIB_PATH):
+        raise ImportError(
+            f"{_LIB_PATH} is missing: build it with `make -C ternixengine_b200/csrc` "
+            "(or __graft_entry__.build()).  There is no fallback implementation.")
+    lib = ctypes.CDLL(_LIB_PATH)
+    c = ctypes
+    vp, i32, i64, sz, u64 = c.c_void_p, c.c_int, c.c_longlong, c.c_size_t, c.c_uint64
+    sig = {
+        "ternix_b200_status_string": (c.c_char_p, [i32]),
+        "ternix_b200_last_cuda_error": (i32, []),
+        "ternix_b200_cuda_error_string": (c.c_char_p, [i32]),
+        "ternix_b200_version": (i32, []),
+        "ternix_b200_pack_ternary": (None, [vp, vp, sz]),
+        "ternix_b200_unpack_ternary": (None, [vp, vp, sz]),
+        "ternix_b200_interleave_offline": (None, [vp, vp, sz]),
+        "ternix_b200_find_non_ternary": (i64, [vp, sz]),
+        "ternix_b200_slice_columns": (i32, [vp, vp, sz, sz, sz, sz]),
+        "ternix_b200_matmul": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+        "ternix_b200_matmul_ex": (i32, [vp, vp, vp, i32, i32, i32, i64, i32, vp, vp]),
+        "ternix_b200_select_kernel": (i32, [vp, vp, vp, i32, i32, i32, i64]),
+        "ternix_b200_matmul_host": (i32, [vp, vp, vp, i32, i32, i32, i32]),
+        "ternix_b200_shard_columns": (i32, [i32, i32, i32, i32, c.POINTER(i32), c.POINTER(i32)]),
+        "ternix_b200_unpack_gathered": (i32, [vp, vp, i32, i32, i64, i32, i32, i32, vp]),
+        "ternix_b200_synth_activations": (None, [vp, sz, u64, i32]),
+        "ternix_b200_synth_packed_weights": (None, [vp, sz, sz, u64]),
+        "ternix_b200_synth_weights": (None, [vp, sz, sz, u64]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+
+def status_string(status: int) -> str:
+    return lib.ternix_b200_status_string(status).decode()
+
+
+def _check(status: int, where: str) -> None:
+    if status == OK:
+        return
+    msg = f"{where}: {status_string(status)}"
+    if status == ERR_CUDA:
+        e = lib.ternix_b200_last_cuda_error()
+        msg += f" [cudaError {e}: {lib.ternix_b200_cuda_error_string(e).decode()}]"
+    if status in (ERR_INVALID_SHAPE, ERR_INVALID_ARG, ERR_UNSUPPORTED):
+        raise ValueError(msg)
+    raise TernixError(status, msg)
+
+
+def _np_ptr(a: np.ndarray) -> ctypes.c_void_p:
+    return ctypes.c_void_p(a.ctypes.data)
+
+
+# --------------------------------------------------------------------------- host: packed format
+def pack_ternary(w: np.ndarray) -> np.ndarray:
+    """(K, N) int8 in {-1,0,+1} -> (K, N/4) uint8.  Same checks and errors as the reference binding
+    (bindings/python/pybind11_wrapper.cpp:21-31)."""
+    w = np.ascontiguousarray(w, dtype=np.int8)
+    if w.ndim != 2:
+        raise ValueError("pack_ternary expects a 2-D (K, N) array")
+    K, N = w.shape
+    if N % 4:
+        raise ValueError("N must be a multiple of 4")
+    if lib.ternix_b200_find_non_ternary(_np_ptr(w), w.size) >= 0:
+        raise ValueError("weights must be in {-1, 0, +1}")
+    out = np.empty((K, N // 4), dtype=np.uint8)
+    lib.ternix_b200_pack_ternary(_np_ptr(out), _np_ptr(w), w.size)
+    return out
+
+
+def unpack_ternary(packed: np.ndarray) -> np.ndarray:
+    """(K, N/4) uint8 -> (K, N) int8 (bindings/python/pybind11_wrapper.cpp:33-39)."""
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    if packed.ndim != 2:
+        raise ValueError("unpack_ternary expects a 2-D (K, N/4) array")
+    K, n4 = packed.shape
+    out = np.empty((K, n4 * 4), dtype=np.int8)
+    lib.ternix_b200_unpack_ternary(_np_ptr(out), _np_ptr(packed), out.size)
+    return out
+
+
+def slice_columns(packed: np.ndarray, n0: int, n_cols: int) -> np.ndarray:
+    """Column shard [n0, n0+n_cols) of a packed matrix, itself a valid packed matrix."""
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    K, n4 = packed.shape
+    out = np.empty((K, n_cols // 4), dtype=np.uint8)
+    _check(lib.ternix_b200_slice_columns(_np_ptr(out), _np_ptr(packed), K, n4 * 4, n0, n_cols), "slice_columns")
+    return out
+
+
+def ternary_matmul_host(a: np.ndarray, b_packed: np.ndarray, kernel: str = "auto") -> np.ndarray:
+    """Host arrays in, host array out, through ternix_b200_matmul_host (upload, kernel, download)."""
+    a = np.ascontiguousarray(a, dtype=np.int8)
+    b_packed = np.ascontiguousarray(b_packed, dtype=np.uint8)
+    if a.ndim != 2 or b_packed.ndim != 2:
+        raise ValueError("A must be (M, K) and B_packed (K, N/4)")
+    M, K = a.shape
+    if b_packed.shape[0] != K:
+        raise ValueError("inner dimensions do not match")
+    N = b_packed.shape[1] * 4
+    c = np.empty((M, N), dtype=np.int32)
+    _check(lib.ternix_b200_matmul_host(_np_ptr(a), _np_ptr(b_packed), _np_ptr(c), M, K, N, KERNELS[kernel]),
+           "ternary_matmul_host")
+    return c
+
+
+# --------------------------------------------------------------------------- host: synthetic inputs
+def synth_activations(shape, seed: int, lo: int = -128) -> np.ndarray:
+    """Seeded int8 activations, uniform on [lo, 127] with lo in {-128, -127}."""
+    if lo not in (-128, -127):
+        raise ValueError("lo must be -128 or -127")
+    out = np.empty(shape, dtype=np.int8)
+    lib.ternix_b200_synth_activations(_np_ptr(out), out.size, seed, 1 if lo == -127 else 0)
+    return out
+
+
+def synth_packed_weights(K: int, N: int, seed: int) -> np.ndarray:
+    """Seeded iid ternary weights, P(0)=0.4, P(+1)=P(-1)=0.3, already packed (K, N/4)."""
+    if N % 4:
+        raise ValueError("N must be a multiple of 4")
+    out = np.empty((K, N // 4), dtype=np.uint8)
+    lib.ternix_b200_synth_packed_weights(_np_ptr(out), K, N, seed)
+    return out
+
+
+def synth_weights(K: int, N: int, seed: int) -> np.ndarray:
+    out = np.empty((K, N), dtype=np.int8)
+    lib.ternix_b200_synth_weights(_np_ptr(out), K, N, seed)
+    return out
+
+
+# --------------------------------------------------------------------------- device path (torch tensors)
+def select_kernel(M: int, K: int, N: int, a_ptr: int = 0, w_ptr: int = 0) -> int:
+    return lib.ternix_b200_select_kernel(a_ptr, w_ptr, 0, M, K, N, N)
+
+
+def matmul(a, w_packed, out=None, kernel: str = "auto", status=None, stream=None):
+    """Device tensors: a (M,K) int8, w_packed (K,N/4) uint8 -> (M,N) int32, asynchronous on the
+    current (or given) CUDA stream.  `out` may be a column slice of a wider row-major matrix."""
+    import torch
+
+    if not (a.is_cuda and w_packed.is_cuda):
+        raise ValueError("matmul() takes CUDA tensors; use ternary_matmul_host() for host arrays")
+    if a.dtype != torch.int8 or w_packed.dtype != torch.uint8 or a.dim() != 2 or w_packed.dim() != 2:
+        raise ValueError("A must be (M, K) int8 and W_packed (K, N/4) uint8")
+    if not (a.is_contiguous() and w_packed.is_contiguous()):
+        raise ValueError("A and W_packed must be contiguous")
+    M, K = a.shape
+    if w_packed.shape[0] != K:
+        raise ValueError("inner dimensions do not match")
+    N = w_packed.shape[1] * 4
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.int32, device=a.device)
+    if out.dtype != torch.int32 or tuple(out.shape) != (M, N) or (N > 1 and out.stride(1) != 1):
+        raise ValueError("out must be (M, N) int32 with unit column stride")
+    ldc = out.stride(0) if M > 1 else max(N, out.stride(0))
+    s = stream if stream is not None else torch.cuda.current_stream(a.device)
+    with torch.cuda.device(a.device):
+        rc = lib.ternix_b200_matmul_ex(a.data_ptr(), w_packed.data_ptr(), out.data_ptr(), M, K, N, ldc,
+                                       KERNELS[kernel], status.data_ptr() if status is not None else None,
+                                       s.cuda_stream)
+    _check(rc, "matmul")
+    return out
+
+
+# --------------------------------------------------------------------------- N-column sharding
+@dataclass(frozen=True)
+class ColumnShard:
+    """Columns [n0, n0 + n_cols) of an N-column matrix owned by `rank` of `world`."""
+    N: int
+    world: int
+    rank: int
+    granule: int
+    n0: int
+    n_cols: int
+
+    @property
+    def n_pad(self) -> int:
+        """Width of the equal-sized block every rank contributes to the all-gather."""
+        return shard_columns(self.N, self.world, 0, self.granule).n_cols
+
+
+def shard_columns(N: int, world: int, rank: int, granule: int = 64) -> ColumnShard:
+    n0, nc = ctypes.c_int(), ctypes.c_int()
+    _check(lib.ternix_b200_shard_columns(N, world, rank, granule, ctypes.byref(n0), ctypes.byref(nc)),
+           "shard_columns")
+    return ColumnShard(N, world, rank, granule, n0.value, nc.value)
+
+
+def should_shard(M: int, K: int, N: int, world: int, granule: int = 64) -> bool:
+    """Small projections stay on one GPU: a shard must keep at least one full 256-column tile per
+    rank and the problem must be in the tensor-core regime."""
+    return world > 1 and M > 16 and N // world >= 256 and N % granule == 0
+
+
+class ShardedTernaryLinear:
+    """One projection W[K,N], N-column-sharded over the ranks of a torch.distributed group.
+
+    Each rank keeps only its packed column shard on its GPU.  forward(a) computes the local
+    C[:, n0:n0+n_cols] with the library's kernel, all-gathers the equal-sized blocks over NCCL
+    and scatters them into the row-major C[M,N] every rank returns.
+    """
+
+    def __init__(self, w_packed_host: np.ndarray, group=None, granule: int = 64, device=None):
+        import torch
+        import torch.distributed as dist
+
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        K, n4 = w_packed_host.shape
+        self.K, self.N = K, n4 * 4
+        self.shard = shard_columns(self.N, self.world, self.rank, granule)
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        local = slice_columns(w_packed_host, self.shard.n0, self.shard.n_cols)
+        self.w_local = torch.from_numpy(local).to(self.device)
+        self._gather = None
+        self._block = None
+
+    def local(self, a, out=None):
+        """This rank's columns only: (M, n_cols) int32."""
+        return matmul(a, self.w_local, out=out)
+
+    def forward(self, a, out=None):
+        import torch
+        import torch.distributed as dist
+
+        M = a.shape[0]
+        if out is None:
+            out = torch.empty((M, self.N), dtype=torch.int32, device=a.device)
+        if self.world == 1:
+            return matmul(a, self.w_local, out=out)
+        n_pad = self.shard.n_pad
+        if self._gather is None or self._gather.shape[1] != M:
+            self._gather = torch.empty((self.world, M, n_pad), dtype=torch.int32, device=a.device)
+            self._block = torch.zeros((M, n_pad), dtype=torch.int32, device=a.device)
+        if self.shard.n_cols:
+            matmul(a, self.w_local, out=self._block[:, : self.shard.n_cols])
+        dist.all_gather_into_tensor(self._gather.view(-1), self._block.view(-1), group=self.group)
+        s = torch.cuda.current_stream(a.device)
+        _check(lib.ternix_b200_unpack_gathered(self._gather.data_ptr(), out.data_ptr(), M, self.N, out.stride(0),
+                                               self.world, self.shard.granule, n_pad, s.cuda_stream),
+               "unpack_gathered")
+        return out

@@ -1,0 +1,382 @@
+// C ABI of the B200 ternary matrix product: shape checks, kernel choice, TMA descriptors, launches.
+// Declared in include/ternix_b200.h.  No CPU fallback: device entry points need a GPU.
+#include "ternix_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "kernel_gemm_tc.cuh"
+#include "kernel_gemv.cuh"
+#include "kernel_generic.cuh"
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+int cuda_fail(cudaError_t e) {
+    g_last_cuda_error = static_cast<int>(e);
+    return TERNIX_B200_ERR_CUDA;
+}
+#define TB_CUDA(call)                                            \
+    do {                                                         \
+        cudaError_t e_ = (call);                                 \
+        if (e_ != cudaSuccess) return cuda_fail(e_);             \
+    } while (0)
+
+// The scaled accumulators of the fast kernels hold 64 * sum; 64 * 128 * K must stay below 2^31.
+constexpr int kMaxScaledK = 262143;
+
+// ---------------------------------------------------------------- driver entry point for TMA maps
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q{};
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// 2-D byte tensor [rows][row_bytes] with `pitch` bytes between rows; box = box_rows x box_bytes.
+int make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t row_bytes, uint64_t rows, uint64_t pitch,
+                 uint32_t box_bytes, uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return cuda_fail(cudaErrorNotSupported);
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {pitch};
+    const cuuint32_t box[2] = {box_bytes, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+    return TERNIX_B200_OK;
+}
+
+bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+int sm_count() {
+    static int n = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+        return v;
+    }();
+    return n;
+}
+
+// ---------------------------------------------------------------- kernel eligibility
+bool gemv_ok(const void* dW, int M, int K, int N) {
+    return M <= 16 && (N % 64) == 0 && aligned(dW, 16) && K <= kMaxScaledK && K <= 8 * (tb200::kGemvMaxASlice / 4);
+}
+bool gemm_tc_ok(const void* dA, const void* dW, int K, int N) {
+    return (N % 64) == 0 && (K % 16) == 0 && aligned(dA, 16) && aligned(dW, 16) && K <= kMaxScaledK;
+}
+
+int select_kernel(const void* dA, const void* dW, int M, int K, int N) {
+    if (gemv_ok(dW, M, K, N)) return TERNIX_B200_KERNEL_GEMV;
+    if (gemm_tc_ok(dA, dW, K, N)) return TERNIX_B200_KERNEL_GEMM_TC;
+    return TERNIX_B200_KERNEL_GENERIC;
+}
+
+// ---------------------------------------------------------------- launches
+int launch_generic(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,
+                   cudaStream_t st) {
+    const int pitch = N / 4;
+    dim3 grid((pitch + tb200::kGenBytes - 1) / tb200::kGenBytes, (M + tb200::kGenRows - 1) / tb200::kGenRows);
+    if (grid.y > 65535) return TERNIX_B200_ERR_INVALID_SHAPE;
+    tb200::ternary_generic_kernel<<<grid, tb200::kGenThreads, 0, st>>>(dA, dW, dC, M, K, N, ldc);
+    TB_CUDA(cudaGetLastError());
+    return TERNIX_B200_OK;
+}
+
+// Split-K plan of the GEMV: words per CTA row (32 -> 512 columns, 16 -> 256 columns) and cluster size.
+struct GemvPlan {
+    int words, ksplit, krange;
+};
+
+GemvPlan plan_gemv(int M, int K, int N) {
+    // TERNIX_B200_GEMV_PLAN="words,ksplit" overrides the heuristic (tuning aid).
+    int force_words = 0, force_split = 0;
+    if (const char* env = std::getenv("TERNIX_B200_GEMV_PLAN")) std::sscanf(env, "%d,%d", &force_words, &force_split);
+    const int row_groups = (M + 3) / 4;
+    const int target = 2 * sm_count();
+    GemvPlan best{0, 0, 0};
+    long best_score = -1;
+    for (int words : {16, 32}) {
+        if (force_words && words != force_words) continue;
+        const int stage_rows = 8 * (32 / words) * 4;
+        const int chunks = (N + words * 16 - 1) / (words * 16);
+        for (int ks : {1, 2, 4, 8}) {
+            if (force_split && ks != force_split) continue;
+            int krange = (K + ks - 1) / ks;
+            krange = (krange + stage_rows - 1) / stage_rows * stage_rows;
+            if (krange * 4 > tb200::kGemvMaxASlice) continue;
+            if (ks > 1 && static_cast<long>(krange) * (ks - 1) >= K) continue;   // a rank would be idle
+            const long ctas = static_cast<long>(chunks) * ks * row_groups;
+            // closest to two resident CTAs per SM without exceeding it much; prefer wider tiles on ties
+            long score = ctas <= target ? ctas * 1000 : (static_cast<long>(target) * 1000 - (ctas - target) * 200);
+            score += words;
+            if (score > best_score) { best_score = score; best = {words, ks, krange}; }
+        }
+    }
+    return best;
+}
+
+template <int MR, int WORDS>
+int launch_gemv_t(const CUtensorMap& tmap, const int8_t* dA, int32_t* dC, int M, int K, int N, long long ldc,
+                  const GemvPlan& p, int32_t* d_status, cudaStream_t st) {
+    auto kern = tb200::ternary_gemv_kernel<MR, WORDS>;
+    const size_t smem = tb200::gemv_smem_bytes<MR, WORDS>(p.krange);
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(tb200::gemv_smem_bytes<MR, WORDS>(tb200::kGemvMaxASlice / MR)));
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    const int chunks = (N + WORDS * 16 - 1) / (WORDS * 16);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(chunks * p.ksplit, (M + MR - 1) / MR, 1);
+    cfg.blockDim = dim3(tb200::kGemvThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.ksplit;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const int a_words_ok = (K % 4 == 0) && aligned(dA, 4);
+    TB_CUDA(cudaLaunchKernelEx(&cfg, kern, tmap, dA, dC, M, K, N, ldc, p.krange, a_words_ok, d_status));
+    return TERNIX_B200_OK;
+}
+
+int launch_gemv(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,
+                int32_t* d_status, cudaStream_t st) {
+    const GemvPlan p = plan_gemv(M, K, N);
+    if (p.words == 0) return TERNIX_B200_ERR_UNSUPPORTED;
+    const int stage_rows = 8 * (32 / p.words) * 4;
+    CUtensorMap tmap;
+    const int rc = make_tmap_2d(&tmap, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K),
+                                static_cast<uint64_t>(N / 4), p.words * 4, stage_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+#define TB_GEMV(MR_, W_) launch_gemv_t<MR_, W_>(tmap, dA, dC, M, K, N, ldc, p, d_status, st)
+    if (p.words == 32) {
+        if (M == 1) return TB_GEMV(1, 32);
+        if (M == 2) return TB_GEMV(2, 32);
+        return TB_GEMV(4, 32);
+    }
+    if (M == 1) return TB_GEMV(1, 16);
+    if (M == 2) return TB_GEMV(2, 16);
+    return TB_GEMV(4, 16);
+#undef TB_GEMV
+}
+
+template <int BN>
+int launch_gemm_tc_t(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,
+                     int32_t* d_status, cudaStream_t st) {
+    using G = tb200::TcGeom<BN>;
+    auto kern = tb200::ternary_gemm_tc_kernel<BN>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(G::kSmemBytes));
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    CUtensorMap tmap_a, tmap_w;
+    int rc = make_tmap_2d(&tmap_a, dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K),
+                          tb200::kTcBK, tb200::kTcBM, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tmap_w, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K),
+                      static_cast<uint64_t>(N / 4), G::kWpRowBytes, tb200::kTcBK, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    const long tiles = static_cast<long>((M + tb200::kTcBM - 1) / tb200::kTcBM) * ((N + BN - 1) / BN);
+    const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+    const int c_vec_ok = (ldc % 4 == 0) && aligned(dC, 16);
+    kern<<<grid, tb200::kTcThreads, G::kSmemBytes, st>>>(tmap_a, tmap_w, dC, M, K, N, ldc, c_vec_ok, d_status);
+    TB_CUDA(cudaGetLastError());
+    return TERNIX_B200_OK;
+}
+
+int launch_gemm_tc(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,
+                   int32_t* d_status, cudaStream_t st) {
+    // TERNIX_B200_TC_BN=128|256 overrides the tile-width heuristic (tuning aid).
+    int bn = 0;
+    if (const char* env = std::getenv("TERNIX_B200_TC_BN")) bn = std::atoi(env);
+    if (bn != 128 && bn != 256) {
+        const long m_tiles = (M + tb200::kTcBM - 1) / tb200::kTcBM;
+        const long tiles256 = m_tiles * ((N + 255) / 256);
+        bn = (N % 256 == 0 || N > 256) && tiles256 >= sm_count() ? 256 : 128;
+    }
+    if (bn == 256) return launch_gemm_tc_t<256>(dA, dW, dC, M, K, N, ldc, d_status, st);
+    return launch_gemm_tc_t<128>(dA, dW, dC, M, K, N, ldc, d_status, st);
+}
+
+// Rank-major gather buffer -> row-major C.
+__global__ void unpack_gathered_kernel(const int32_t* __restrict__ g, int32_t* __restrict__ C, int M, int N,
+                                       long long ldc, int world, int granule, int n_pad) {
+    const int granules = (N + granule - 1) / granule;
+    const int base = granules / world, extra = granules % world;
+    const long long total = static_cast<long long>(M) * N;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int row = static_cast<int>(i / N), col = static_cast<int>(i % N);
+        const int gi = col / granule;
+        // ranks [0, extra) own base+1 granules, the rest own base
+        int rank, first;
+        if (gi < extra * (base + 1)) { rank = gi / (base + 1); first = rank * (base + 1); }
+        else { rank = extra + (base ? (gi - extra * (base + 1)) / base : 0); first = extra * (base + 1) + (rank - extra) * base; }
+        const int local = col - first * granule;
+        C[static_cast<long long>(row) * ldc + col] =
+            g[(static_cast<long long>(rank) * M + row) * n_pad + local];
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* ternix_b200_status_string(int status) {
+    switch (status) {
+        case TERNIX_B200_OK: return "ok";
+        case TERNIX_B200_ERR_INVALID_SHAPE: return "invalid shape (need M,K,N >= 0, N % 4 == 0, sizes within int32)";
+        case TERNIX_B200_ERR_INVALID_ARG: return "invalid argument (null pointer, bad selector or pitch)";
+        case TERNIX_B200_ERR_CUDA: return "CUDA error (see ternix_b200_last_cuda_error)";
+        case TERNIX_B200_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+        case TERNIX_B200_ERR_UNSUPPORTED: return "the requested kernel cannot take this problem";
+        default: return "unknown status";
+    }
+}
+
+int ternix_b200_last_cuda_error(void) { return g_last_cuda_error; }
+const char* ternix_b200_cuda_error_string(int cuda_error) {
+    return cudaGetErrorString(static_cast<cudaError_t>(cuda_error));
+}
+int ternix_b200_version(void) { return 100; }
+
+int ternix_b200_select_kernel(const void* dA, const void* dW, const void* dC, int M, int K, int N, long long ldc) {
+    (void)dC;
+    (void)ldc;
+    if (M < 0 || K < 0 || N < 0 || (N % 4) != 0) return -TERNIX_B200_ERR_INVALID_SHAPE;
+    return select_kernel(dA, dW, M, K, N);
+}
+
+int ternix_b200_matmul_ex(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,
+                          int kernel, int32_t* d_status, void* stream) {
+    // Shape first, before any pointer is looked at (the reference's wrappers promise the same,
+    // tests/test_cuda_matmul.cu:41-43).
+    if (M < 0 || K < 0 || N < 0 || (N % 4) != 0) return TERNIX_B200_ERR_INVALID_SHAPE;
+    if (ldc < N) return TERNIX_B200_ERR_INVALID_ARG;
+    if (kernel < TERNIX_B200_KERNEL_AUTO || kernel > TERNIX_B200_KERNEL_GEMM_TC) return TERNIX_B200_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return TERNIX_B200_OK;
+    if (!dC || (K > 0 && (!dA || !dW))) return TERNIX_B200_ERR_INVALID_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (K == 0) {   // empty sum: C = 0
+        TB_CUDA(cudaMemset2DAsync(dC, static_cast<size_t>(ldc) * 4, 0, static_cast<size_t>(N) * 4, M, st));
+        return TERNIX_B200_OK;
+    }
+    if (kernel == TERNIX_B200_KERNEL_AUTO) kernel = select_kernel(dA, dW, M, K, N);
+    switch (kernel) {
+        case TERNIX_B200_KERNEL_GEMV:
+            if (!gemv_ok(dW, M, K, N)) return TERNIX_B200_ERR_UNSUPPORTED;
+            return launch_gemv(dA, dW, dC, M, K, N, ldc, d_status, st);
+        case TERNIX_B200_KERNEL_GEMM_TC:
+            if (!gemm_tc_ok(dA, dW, K, N)) return TERNIX_B200_ERR_UNSUPPORTED;
+            return launch_gemm_tc(dA, dW, dC, M, K, N, ldc, d_status, st);
+        default:
+            return launch_generic(dA, dW, dC, M, K, N, ldc, st);
+    }
+}
+
+int ternix_b200_matmul(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, void* stream) {
+    return ternix_b200_matmul_ex(dA, dW, dC, M, K, N, N, TERNIX_B200_KERNEL_AUTO, nullptr, stream);
+}
+
+int ternix_b200_matmul_host(const int8_t* A, const uint8_t* Wp, int32_t* C, int M, int K, int N, int kernel) {
+    if (M < 0 || K < 0 || N < 0 || (N % 4) != 0) return TERNIX_B200_ERR_INVALID_SHAPE;
+    if (kernel < TERNIX_B200_KERNEL_AUTO || kernel > TERNIX_B200_KERNEL_GEMM_TC) return TERNIX_B200_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return TERNIX_B200_OK;
+    if (!C || (K > 0 && (!A || !Wp))) return TERNIX_B200_ERR_INVALID_ARG;
+    const size_t a_bytes = static_cast<size_t>(M) * K, w_bytes = static_cast<size_t>(K) * (N / 4),
+                 c_bytes = static_cast<size_t>(M) * N * sizeof(int32_t);
+    int8_t* dA = nullptr;
+    uint8_t* dW = nullptr;
+    int32_t* dC = nullptr;
+    int32_t* dS = nullptr;
+    int rc = TERNIX_B200_OK;
+    cudaError_t e = cudaSuccess;
+    int32_t h_status = 0;
+    // One allocation for everything: [status | A | W | C], each part 256-byte aligned.
+    auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+    uint8_t* blob = nullptr;
+    const size_t total = 256 + up(a_bytes) + up(w_bytes) + up(c_bytes);
+    if ((e = cudaMalloc(&blob, total)) != cudaSuccess) return cuda_fail(e);
+    dS = reinterpret_cast<int32_t*>(blob);
+    dA = reinterpret_cast<int8_t*>(blob + 256);
+    dW = reinterpret_cast<uint8_t*>(blob + 256 + up(a_bytes));
+    dC = reinterpret_cast<int32_t*>(blob + 256 + up(a_bytes) + up(w_bytes));
+    do {
+        if ((e = cudaMemsetAsync(dS, 0, 4, 0)) != cudaSuccess) break;
+        if (K > 0) {
+            if ((e = cudaMemcpyAsync(dA, A, a_bytes, cudaMemcpyHostToDevice, 0)) != cudaSuccess) break;
+            if ((e = cudaMemcpyAsync(dW, Wp, w_bytes, cudaMemcpyHostToDevice, 0)) != cudaSuccess) break;
+        }
+        rc = ternix_b200_matmul_ex(dA, dW, dC, M, K, N, N, kernel, dS, nullptr);
+        if (rc) break;
+        if ((e = cudaMemcpyAsync(C, dC, c_bytes, cudaMemcpyDeviceToHost, 0)) != cudaSuccess) break;
+        if ((e = cudaMemcpyAsync(&h_status, dS, 4, cudaMemcpyDeviceToHost, 0)) != cudaSuccess) break;
+        e = cudaStreamSynchronize(0);
+    } while (false);
+    cudaFree(blob);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (rc) return rc;
+    return h_status ? h_status : TERNIX_B200_OK;
+}
+
+int ternix_b200_shard_columns(int N, int world, int rank, int granule, int* n0, int* n_cols) {
+    if (N < 0 || (N % 4) != 0 || world < 1 || rank < 0 || rank >= world || granule < 4 || (granule % 4) != 0 ||
+        !n0 || !n_cols)
+        return TERNIX_B200_ERR_INVALID_ARG;
+    const int granules = (N + granule - 1) / granule;
+    const int base = granules / world, extra = granules % world;
+    const int first = rank < extra ? rank * (base + 1) : extra * (base + 1) + (rank - extra) * base;
+    const int count = rank < extra ? base + 1 : base;
+    long long c0 = static_cast<long long>(first) * granule, c1 = static_cast<long long>(first + count) * granule;
+    if (c0 > N) c0 = N;
+    if (c1 > N) c1 = N;
+    *n0 = static_cast<int>(c0);
+    *n_cols = static_cast<int>(c1 - c0);
+    return TERNIX_B200_OK;
+}
+
+int ternix_b200_unpack_gathered(const int32_t* d_gathered, int32_t* dC, int M, int N, long long ldc, int world,
+                                int granule, int n_pad, void* stream) {
+    if (M < 0 || N < 0 || (N % 4) != 0) return TERNIX_B200_ERR_INVALID_SHAPE;
+    if (world < 1 || granule < 4 || (granule % 4) != 0 || ldc < N || n_pad < 0) return TERNIX_B200_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return TERNIX_B200_OK;
+    if (!d_gathered || !dC) return TERNIX_B200_ERR_INVALID_ARG;
+    const long long total = static_cast<long long>(M) * N;
+    long long blocks = (total + 255) / 256;
+    const long long cap = static_cast<long long>(sm_count()) * 16;
+    if (blocks > cap) blocks = cap;
+    unpack_gathered_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        d_gathered, dC, M, N, ldc, world, granule, n_pad);
+    TB_CUDA(cudaGetLastError());
+    return TERNIX_B200_OK;
+}
+
+}  // extern "C"

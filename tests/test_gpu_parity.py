@@ -1,0 +1,229 @@
+"""Parity of the CUDA path with the CPU oracle, bit for bit, through the C ABI.  Needs a B200."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+import oracle_lib
+import ternixengine_b200 as tb
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_cases.npz"))
+CASES = [str(n) for n in GOLDEN["names"]]
+
+
+def device_matmul(a, wp, kernel="auto", pad_cols=0):
+    """Upload, run one kernel through ternix_b200_matmul_ex into a poisoned C, download; checks the status word."""
+    import torch
+    da = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    dw = torch.from_numpy(np.ascontiguousarray(wp)).cuda()
+    M, N = a.shape[0], wp.shape[1] * 4
+    full = torch.full((M, N + pad_cols), -999, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tb.matmul(da, dw, out=full[:, :N], kernel=kernel, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded device-side wait ran out"
+    got = full.cpu().numpy()
+    if pad_cols:
+        assert (got[:, N:] == -999).all(), "kernel wrote outside its columns"
+    return got[:, :N]
+
+
+def kernels_for(M, K, N):
+    ks = ["generic"]
+    if N % 64 == 0 and M <= 16:
+        ks.append("gemv")
+    if N % 64 == 0 and K % 16 == 0:
+        ks.append("gemm_tc")
+    return ks + ["auto"]
+
+
+def assert_same(got, expect, what):
+    if not np.array_equal(got, expect):
+        bad = np.argwhere(got != expect)
+        i, j = bad[0]
+        raise AssertionError(f"{what}: {len(bad)} of {got.size} entries differ; first at ({i},{j}): "
+                             f"got {got[i, j]}, expect {expect[i, j]}; rows {sorted(set(bad[:, 0]))[:8]} "
+                             f"cols {sorted(set(bad[:, 1]))[:16]}")
+
+
+# ---------------------------------------------------------------- the reference's own test cases
+@pytest.mark.parametrize("name", CASES)
+def test_golden_cases_all_kernels(name):
+    a, wp, c = GOLDEN[name + "/A"], GOLDEN[name + "/Wp"], GOLDEN[name + "/C"]
+    M, K = a.shape
+    N = wp.shape[1] * 4
+    for kern in kernels_for(M, K, N):
+        assert_same(device_matmul(a, wp, kern), c, f"{name} [{kern}]")
+
+
+def test_host_entry_point_and_python_module():
+    sys.path.insert(0, os.path.join(ROOT, "ternixengine_b200"))
+    import ternix_engine as te
+    rng = np.random.default_rng(3)                       # tests/test_python_binding.py:14-41
+    for (m, k, n) in [(1, 8, 8), (5, 33, 24), (64, 256, 128), (128, 256, 192)]:
+        a = rng.integers(-128, 128, size=(m, k), dtype=np.int8)
+        w = rng.integers(-1, 2, size=(k, n), dtype=np.int8)
+        expect = a.astype(np.int32) @ w.astype(np.int32)
+        packed = te.pack_ternary(w)
+        for impl in ("naive", "scalar", "avx2", "avx2_blocked", "cuda_naive", "cuda_tiled", "b200_generic"):
+            assert_same(te.ternary_matmul(a, packed, impl), expect, f"{impl} {m}x{k}x{n}")
+        assert_same(te.ternary_matmul(a, packed), expect, "default impl")
+        assert_same(tb.ternary_matmul_host(a, packed), expect, "ctypes host entry")
+
+
+# ---------------------------------------------------------------- BASELINE configs
+def synth(M, K, N, seed, lo=-128):
+    return tb.synth_activations((M, K), seed, lo=lo), tb.synth_packed_weights(K, N, seed + 1000)
+
+
+def test_config1_bitnet_gemv():
+    a, wp = synth(1, 2560, 6912, 11)
+    expect = oracle_lib.matmul(a, wp, "scalar")
+    if oracle_lib.have_ref():
+        assert_same(oracle_lib.ref_matmul(a, wp, "avx2_blocked"), expect, "reference avx2_blocked vs oracle")
+    for kern in ("gemv", "gemm_tc", "generic", "auto"):
+        assert_same(device_matmul(a, wp, kern), expect, f"config1 [{kern}]")
+
+
+@pytest.mark.parametrize("plan", ["16,1", "16,2", "16,4", "16,8", "32,1", "32,2", "32,4", "32,8"])
+def test_gemv_every_split_plan(plan, monkeypatch):
+    monkeypatch.setenv("TERNIX_B200_GEMV_PLAN", plan)
+    for (m, k, n) in [(1, 2560, 6912), (3, 1000, 320), (16, 4096, 1024), (2, 64, 64), (5, 8200, 192)]:
+        a, wp = synth(m, k, n, 7 * m + n)
+        assert_same(device_matmul(a, wp, "gemv", pad_cols=8), oracle_lib.matmul(a, wp), f"gemv plan {plan} {m}x{k}x{n}")
+
+
+def test_config2_skinny_gemm():
+    a, wp = synth(32, 4096, 11008, 21, lo=-127)
+    expect = oracle_lib.matmul(a, wp)
+    for kern in ("gemm_tc", "generic", "auto"):
+        assert_same(device_matmul(a, wp, kern), expect, f"config2 [{kern}]")
+
+
+@pytest.mark.parametrize("bn", ["128", "256"])
+def test_gemm_tc_tile_widths_and_ragged_edges(bn, monkeypatch):
+    monkeypatch.setenv("TERNIX_B200_TC_BN", bn)
+    for (m, k, n) in [(128, 128, 256), (128, 512, 128), (256, 1024, 512), (300, 2064, 832), (1, 16, 64),
+                      (129, 144, 320), (640, 4096, 1024), (1000, 272, 1984)]:
+        a, wp = synth(m, k, n, m + k + n)
+        assert_same(device_matmul(a, wp, "gemm_tc", pad_cols=4), oracle_lib.matmul(a, wp), f"gemm_tc bn={bn} {m}x{k}x{n}")
+
+
+@pytest.mark.parametrize("shape", [(1, 3001, 1028), (7, 129, 4), (37, 4099, 2052), (255, 2561, 6916)])
+def test_config4_ragged_and_worst_case(shape):
+    m, k, n = shape
+    a, wp = synth(m, k, n, sum(shape))
+    expect = oracle_lib.matmul(a, wp, "scalar") if m * k * n < 4e8 else oracle_lib.matmul(a, wp)
+    assert_same(device_matmul(a, wp, "auto", pad_cols=4), expect, f"config4 random {shape}")
+    a2 = np.full((m, k), -128, dtype=np.int8)
+    w2 = np.full((k, n // 4), 0xFF, dtype=np.uint8)
+    got = device_matmul(a2, w2, "auto")
+    assert (got == 128 * k).all(), f"config4 worst case {shape}: {np.unique(got)[:5]} != {128 * k}"
+
+
+@pytest.mark.parametrize("shape", [(1, 8192, 1024), (16, 8192, 512), (128, 8192, 256), (256, 8192, 512)])
+def test_worst_case_magnitude_fast_kernels(shape):
+    """A == -128 and W == -1 on the scaled-accumulator kernels: 64 * 128 * K stays inside int32."""
+    m, k, n = shape
+    a = np.full((m, k), -128, dtype=np.int8)
+    wp = np.full((k, n // 4), 0xFF, dtype=np.uint8)
+    for kern in kernels_for(m, k, n):
+        assert (device_matmul(a, wp, kern) == 128 * k).all(), f"{kern} {shape}"
+    a[:] = 127
+    for kern in kernels_for(m, k, n):
+        assert (device_matmul(a, wp, kern) == -127 * k).all(), f"{kern} {shape} (+127)"
+
+
+BITNET_LAYER = [("q", 2560, 2560), ("k", 2560, 640), ("v", 2560, 640), ("o", 2560, 2560),
+                ("gate", 2560, 6912), ("up", 2560, 6912), ("down", 6912, 2560)]
+
+
+@pytest.mark.parametrize("M", [1, 256])
+def test_config5_bitnet_projection_set_one_layer(M):
+    for i, (name, k, n) in enumerate(BITNET_LAYER):
+        a, wp = synth(M, k, n, 100 * M + i)
+        assert_same(device_matmul(a, wp, "auto"), oracle_lib.matmul(a, wp), f"config5 {name} M={M}")
+
+
+def test_config3_prefill_gemm_full_size():
+    """4096 x 8192 x 28672 on one GPU: sampled rows against the oracle, then size-independent properties."""
+    import torch
+    M, K, N = 4096, 8192, 28672
+    a, wp = synth(M, K, N, 31)
+    da, dw = torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    c = tb.matmul(da, dw, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    rows = np.r_[0:8, 127:129, 2040:2056, 4088:4096, np.random.default_rng(0).integers(0, M, 30)]
+    expect = oracle_lib.matmul(a[rows], wp)
+    assert_same(c[torch.from_numpy(rows).cuda()].cpu().numpy(), expect, "config3 sampled rows")
+    # the generic kernel shares no decode or MMA code with the tensor-core kernel: compare every entry
+    c2 = tb.matmul(da, dw, kernel="generic")
+    assert bool((c == c2).all()), "tensor-core and generic kernels disagree"
+    # linearity in A: (A1 + A2) W == A1 W + A2 W for small-magnitude halves (no int8 overflow)
+    a1 = (da >> 1)
+    a2 = da - a1
+    assert bool((tb.matmul(a1, dw) + tb.matmul(a2, dw) == c).all())
+    # column-sum checksum: sum_j C[i,j] == sum_k A[i,k] * rowsum(W)[k]
+    wsum = torch.from_numpy(tb.unpack_ternary(wp).astype(np.int32).sum(axis=1)).cuda()
+    lhs = c.sum(dim=1, dtype=torch.int64)
+    rhs = (da.to(torch.int64) * wsum.to(torch.int64)).sum(dim=1)
+    assert bool((lhs == rhs).all())
+
+
+def test_column_slice_output_pitch():
+    """A shard can be written straight into its columns of a wider C (ldc > N)."""
+    import torch
+    a, wp = synth(130, 512, 1024, 5)
+    expect = oracle_lib.matmul(a, wp)
+    da = torch.from_numpy(a).cuda()
+    wide = torch.full((130, 1024), -7, dtype=torch.int32, device="cuda")
+    for r in range(4):
+        sh = tb.shard_columns(1024, 4, r)
+        dws = torch.from_numpy(tb.slice_columns(wp, sh.n0, sh.n_cols)).cuda()
+        tb.matmul(da, dws, out=wide[:, sh.n0:sh.n0 + sh.n_cols])
+    torch.cuda.synchronize()
+    assert_same(wide.cpu().numpy(), expect, "column shards written in place")
+
+
+def test_unpack_gathered_layout():
+    import torch
+    M, N, world, granule = 37, 6912, 8, 64
+    c = np.random.default_rng(1).integers(-1000, 1000, size=(M, N), dtype=np.int32)
+    n_pad = tb.shard_columns(N, world, 0, granule).n_cols
+    g = np.zeros((world, M, n_pad), dtype=np.int32)
+    for r in range(world):
+        sh = tb.shard_columns(N, world, r, granule)
+        g[r, :, :sh.n_cols] = c[:, sh.n0:sh.n0 + sh.n_cols]
+    dg = torch.from_numpy(g).cuda()
+    out = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+    rc = tb.lib.ternix_b200_unpack_gathered(dg.data_ptr(), out.data_ptr(), M, N, N, world, granule, n_pad,
+                                            torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert_same(out.cpu().numpy(), c, "unpack_gathered")
+
+
+def test_k_zero_and_empty_shapes():
+    import torch
+    out = torch.full((3, 8), 5, dtype=torch.int32, device="cuda")
+    rc = tb.lib.ternix_b200_matmul(None, None, out.data_ptr(), 3, 0, 8, None)
+    torch.cuda.synchronize()
+    assert rc == 0 and bool((out == 0).all())
+    assert tb.lib.ternix_b200_matmul(None, None, None, 0, 5, 8, None) == 0
+
+
+def test_legacy_tiled_contract_rejects_before_touching_memory():
+    # tests/test_cuda_matmul.cu:41-43 through the exported C++ symbol
+    import ctypes
+    raw = ctypes.CDLL(os.path.join(ROOT, "ternixengine_b200", "libternix_b200.so"))
+    sym = [l.split()[-1] for l in os.popen(f"nm -D {ROOT}/ternixengine_b200/libternix_b200.so").read().splitlines()
+           if "mul_mat_ternary_cuda_tiled" in l][0]
+    fn = getattr(raw, sym)
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 3 + [ctypes.c_void_p]
+    assert fn(None, None, None, 65, 64, 64, None) == 1          # cudaErrorInvalidValue
