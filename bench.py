@@ -1,0 +1,372 @@
+#!/usr/bin/env python
+"""Benchmark of the ternary matrix product on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one batch of seeded
+synthetic input: the prefill GEMM  C[4096,28672] = A[4096,8192] x W[8192,28672]  (the Llama-3-70B-shaped
+FFN up projection of the baseline's config list), W ternary and packed.  At N > 1 the packed weights are
+N-column-sharded over the ranks, every rank computes its columns and C is all-gathered over NCCL, so
+total work is fixed ("strong" scaling).  `value` = dense int8 TOPS = 2*M*K*N*steps / time, zeros not
+skipped (the reference's own "effective TOPS" convention, benchmarks/bench_cuda.cu:73).
+
+The same line carries the decode-regime figure (M=1 BitNet-shaped GEMV, HBM GB/s), the roofline of the
+dominant kernel, the CPU baseline (the reference's AVX2 kernel on the host cores) and an end-to-end
+figure through the host-pointer entry point.
+
+`--impl reference` times the reference's own CPU kernel (oracle/_ref, or the oracle port when that
+build is absent) on a bounded row sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M, K, N = 4096, 8192, 28672                 # prefill GEMM (Llama-3-70B-shaped FFN up projection)
+GEMV_K, GEMV_N = 2560, 6912                 # decode GEMV (BitNet-b1.58-2B FFN up shape)
+SEED = 20240531
+L2_BYTES = 126 * 1024 * 1024
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "20", "-i", str(self.idx)], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons, power = [], [], set(), []
+        for line in open(self.path):
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); smax.append(float(parts[2])); power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # the busiest half of the samples is "under load"
+        load = sorted(sm)[len(sm) // 2:] if len(sm) > 3 else sm
+        return {"sm_mhz": float(np.median(sm)), "sm_mhz_min": float(min(sm)), "sm_max_mhz": float(max(smax)),
+                "power_w_max": float(max(power)), "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------- CPU baseline
+def cpu_reference_sample(a, wp, target_s=12.0, rows0=None):
+    """Times the reference's CPU kernel (all host threads, row bands) on the first `rows` rows of A.
+    Returns (tops, seconds, rows, threads, kind)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib
+    threads = os.cpu_count() or 1
+    use_ref = oracle_lib.have_ref()
+
+    def run(rows):
+        t0 = time.perf_counter()
+        if use_ref:
+            oracle_lib.ref_matmul(a[:rows], wp, "avx2_blocked", threads=threads)
+        else:
+            oracle_lib.matmul(a[:rows], wp, "fast", threads=threads)
+        return time.perf_counter() - t0
+
+    k, n = a.shape[1], wp.shape[1] * 4
+    rows = rows0 or min(a.shape[0], 4 * threads)
+    t = run(rows)
+    if rows0 is None and t < target_s / 4 and rows < a.shape[0]:
+        scale = min(a.shape[0] / rows, target_s / max(t, 1e-3))
+        rows = int(min(a.shape[0], max(rows, (int(rows * scale) // (4 * threads)) * 4 * threads)))
+        t = run(rows)
+    return 2.0 * rows * k * n / t / 1e12, t, rows, threads, ("reference" if use_ref else "port")
+
+
+def make_inputs():
+    import ternixengine_b200 as tb
+    a = tb.synth_activations((M, K), SEED)
+    wp = tb.synth_packed_weights(K, N, SEED + 1)
+    return a, wp
+
+
+# ------------------------------------------------------------------------------------- reference arm
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    a, wp = make_inputs()
+    # size one step at a few seconds of CPU work, then time exactly `steps` of them
+    tops0, t0, rows, threads, kind = cpu_reference_sample(a, wp, target_s=4.0)
+    for _ in range(args.warmup):
+        cpu_reference_sample(a, wp, rows0=rows)
+    t_start = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_reference_sample(a, wp, rows0=rows)
+    dt = time.perf_counter() - t_start
+    tops = 2.0 * rows * K * N * args.steps / dt / 1e12
+    sample = f"first {rows} of {M} rows of A, full K and N, per step"
+    line = {
+        "impl": "reference", "metric": "prefill_gemm_int8_tops", "value": tops, "unit": "TOPS", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int8xternary->int32", "data": "synthetic",
+        "config": {"workload": f"config3 prefill GEMM M={M} K={K} N={N} (row sample on CPU)", "sample_rows": rows},
+        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------- B200 arm
+def timed(fn, steps, warmup, barrier):
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    return e0.elapsed_time(e1)           # ms on this rank
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    import ternixengine_b200 as tb
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    peaks = load_peaks()
+    a_host, wp_host = make_inputs()
+    a_pin = torch.from_numpy(a_host).pin_memory()
+    da = a_pin.to(dev)
+    layer = tb.ShardedTernaryLinear(wp_host, device=dev)
+    shard = layer.shard
+    c = torch.empty((M, N), dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    # ---- exactness gate (the reference's benchmark refuses to report an unverified number,
+    #      benchmarks/bench_cuda.cu:69-81): sampled rows of the gathered C against the CPU oracle.
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib
+    layer.forward(da, out=c)
+    torch.cuda.synchronize()
+    rows = np.r_[0:4, 2046:2050, 4092:4096]
+    expect = oracle_lib.matmul(a_host[rows], wp_host)
+    got = c[torch.from_numpy(rows).to(dev)].cpu().numpy()
+    if not np.array_equal(got, expect):
+        raise SystemExit(f"rank {rank}: GPU result differs from the CPU oracle; refusing to report a number")
+
+    # ---- device-resident throughput
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = max_over_ranks(timed(lambda: layer.forward(da, out=c), args.steps, args.warmup, barrier))
+    clocks = sampler.stop() if rank == 0 else None
+    ops = 2.0 * M * K * N
+    tops = ops * args.steps / (ms * 1e-3) / 1e12
+
+    # shard compute alone (no gather): explains the scaling curve
+    local_out = torch.empty((M, max(shard.n_cols, 4)), dtype=torch.int32, device=dev)
+    ms_local = max_over_ranks(timed(lambda: layer.local(da, out=local_out[:, :shard.n_cols]), args.steps, args.warmup,
+                                    barrier))
+
+    # ---- end to end through the host-pointer entry point: pinned host A in, result columns out, every step
+    c_pin = torch.empty((M, max(shard.n_cols, 4)), dtype=torch.int32).pin_memory()
+
+    def e2e_step():
+        da.copy_(a_pin, non_blocking=True)
+        layer.forward(da, out=c)
+        c_pin[:, :shard.n_cols].copy_(c[:, shard.n0:shard.n0 + shard.n_cols], non_blocking=True)
+
+    e2e_steps = max(3, min(20, args.steps))
+    ms_e2e = max_over_ranks(timed(e2e_step, e2e_steps, 3, barrier))
+    e2e_tops = ops * e2e_steps / (ms_e2e * 1e-3) / 1e12
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- decode regime: M=1 GEMV over rotating weight copies larger than L2 (rank 0, one GPU)
+    gemv = bench_gemv(tb, dev, peaks)
+
+    # ---- CPU baseline on the host cores (bounded sample)
+    cpu_tops, cpu_t, cpu_rows, cpu_threads, cpu_kind = cpu_reference_sample(a_host, wp_host, target_s=12.0)
+
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        traffic = json.load(open(tpath)).get("gemm_tc_config3_dram_bytes_per_launch")
+    kernel_ms = ms_local / args.steps
+    local_ops = 2.0 * M * K * shard.n_cols
+    line = {
+        "metric": "prefill_gemm_int8_tops", "value": tops, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8xternary->int32", "data": "synthetic",
+        "config": {"workload": f"config3 prefill GEMM M={M} K={K} N={N}, W ternary packed 2-bit",
+                   "parallelism": f"N-column shards x{world} + NCCL all-gather of C" if world > 1 else "single GPU",
+                   "l2": "A+W+C = 562 MB per step exceeds the 126 MB L2; C (470 MB) is rewritten every step",
+                   "seed": SEED},
+        "shard_compute": {"ms": kernel_ms, "tops_per_gpu": local_ops / (kernel_ms * 1e-3) / 1e12,
+                          "columns_rank0": shard.n_cols},
+        "roofline": {"bound": "tensor", "achieved": local_ops / (kernel_ms * 1e-3) / 1e12, "peak": int8_peak,
+                     "unit": "TOPS", "frac": local_ops / (kernel_ms * 1e-3) / 1e12 / int8_peak, "traffic": traffic,
+                     "kernel": "ternary_gemm_tc_kernel", "peak_source": f"2 x bf16 burst of {peaks['source']} peaks "
+                     "(dense int8 proxy)", "frac_of_nominal_4500": local_ops / (kernel_ms * 1e-3) / 1e12 / 4500.0},
+        "gemv": gemv,
+        "cpu_baseline": {"value": cpu_tops, "unit": "TOPS", "cores": cpu_threads, "kind": cpu_kind,
+                         "sample": f"first {cpu_rows} of {M} rows, full K and N, {cpu_t:.1f} s, avx2_blocked row bands"},
+        "e2e": {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": M * K * world,
+                "d2h_bytes_per_step": 4 * M * N, "ms_per_step": ms_e2e / e2e_steps,
+                "note": "activations copied from pinned host memory and C copied back to pinned host memory every "
+                        "step; packed weights stay resident"},
+        "gpu_launches": args.steps * (1 if world == 1 else 2),
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def bench_gemv(tb, dev, peaks):
+    """config 1: C[1,6912] = A[1,2560] x W[2560,6912], weights streamed from HBM (64 rotating copies = 283 MB)."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib
+    copies = 64
+    a = tb.synth_activations((1, GEMV_K), SEED + 7)
+    ws = [tb.synth_packed_weights(GEMV_K, GEMV_N, SEED + 100 + i) for i in range(4)]
+    da = torch.from_numpy(a).to(dev)
+    dws = [torch.from_numpy(ws[i % 4]).to(dev).clone() for i in range(copies)]
+    outs = [torch.empty((1, GEMV_N), dtype=torch.int32, device=dev) for _ in range(copies)]
+    for i in range(4):
+        tb.matmul(da, dws[i], out=outs[i])
+    torch.cuda.synchronize()
+    for i in range(4):
+        if not np.array_equal(outs[i].cpu().numpy(), oracle_lib.matmul(a, ws[i], "scalar")):
+            raise SystemExit("GEMV result differs from the CPU oracle; refusing to report a number")
+
+    def sweep():
+        for i in range(copies):
+            tb.matmul(da, dws[i], out=outs[i])
+
+    passes = 10
+    ms = timed(sweep, passes, 3, lambda: None)
+    per_launch_us = ms * 1e3 / (passes * copies)
+    bytes_per = GEMV_K * GEMV_N // 4 + GEMV_K + 4 * GEMV_N
+    gbs = bytes_per / (per_launch_us * 1e-6) / 1e9
+    # one CUDA graph of the same 64 launches: removes host launch overhead from the figure
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        sweep()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=s):
+            sweep()
+    ms_g = timed(g.replay, passes, 3, lambda: None)
+    per_graph_us = ms_g * 1e3 / (passes * copies)
+    gbs_g = bytes_per / (per_graph_us * 1e-6) / 1e9
+    best = max(gbs, gbs_g)
+    t_cpu0 = time.perf_counter()
+    reps = 5
+    for _ in range(reps):
+        if oracle_lib.have_ref():
+            oracle_lib.ref_matmul(a, ws[0], "avx2_blocked")
+        else:
+            oracle_lib.matmul(a, ws[0], "scalar")
+    cpu_s = (time.perf_counter() - t_cpu0) / reps
+    return {"workload": f"config1 GEMV M=1 K={GEMV_K} N={GEMV_N}; {copies} rotating weight copies (283 MB > L2)",
+            "metric": "gemv_hbm_gbs", "unit": "GB/s", "value": best, "us_per_launch_stream": per_launch_us,
+            "us_per_launch_graph": per_graph_us, "gbs_stream": gbs, "gbs_graph": gbs_g,
+            "algorithmic_bytes_per_launch": bytes_per,
+            "roofline": {"bound": "hbm", "achieved": best, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": best / peaks["hbm_gbs"], "traffic": None, "kernel": "ternary_gemv_kernel",
+                         "peak_source": f"{peaks['source']} copy bandwidth", "frac_of_nominal_8000": best / 8000.0},
+            "cpu_baseline": {"value": bytes_per / cpu_s / 1e9, "unit": "GB/s", "cores": 1,
+                             "kind": "reference" if oracle_lib.have_ref() else "port",
+                             "sample": f"whole GEMV, mean of {reps}, one thread (the kernel cannot slice M=1)"}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -106,10 +106,7 @@ struct GemvPlan {
     int words, ksplit, krange;
 };
 
-GemvPlan plan_gemv(int M, int K, int N) {
-    // TERNIX_B200_GEMV_PLAN="words,ksplit" overrides the heuristic (tuning aid).
-    int force_words = 0, force_split = 0;
-    if (const char* env = std::getenv("TERNIX_B200_GEMV_PLAN")) std::sscanf(env, "%d,%d", &force_words, &force_split);
+GemvPlan plan_gemv_with(int M, int K, int N, int force_words, int force_split) {
     const int row_groups = (M + 3) / 4;
     const int target = 2 * sm_count();
     GemvPlan best{0, 0, 0};
@@ -132,6 +129,17 @@ GemvPlan plan_gemv(int M, int K, int N) {
         }
     }
     return best;
+}
+
+GemvPlan plan_gemv(int M, int K, int N) {
+    // TERNIX_B200_GEMV_PLAN="words,ksplit" overrides the heuristic where that plan is feasible (tuning aid).
+    int force_words = 0, force_split = 0;
+    if (const char* env = std::getenv("TERNIX_B200_GEMV_PLAN")) std::sscanf(env, "%d,%d", &force_words, &force_split);
+    if (force_words || force_split) {
+        const GemvPlan p = plan_gemv_with(M, K, N, force_words, force_split);
+        if (p.words) return p;
+    }
+    return plan_gemv_with(M, K, N, 0, 0);
 }
 
 template <int MR, int WORDS>
