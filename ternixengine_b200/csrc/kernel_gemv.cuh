@@ -193,12 +193,17 @@ ternary_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const int8_t* __
         for (int i = lo + tid; i < hi; i += kGemvThreads) {
             const int r = i / G::kCols, col = i % G::kCols;
             const uint32_t off = static_cast<uint32_t>(((r * 16 + (col & 15)) * (WORDS + 1) + (col >> 4)) * 4);
-            int32_t sum = 0;
-            for (uint32_t p = 0; p < nrank; ++p) {
-                int32_t v;
-                asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(dsmem_map(part_addr + off, p)) : "memory");
-                sum += v;
+            // all remote loads are issued before any is used (cluster size is at most 8)
+            int32_t v[8];
+#pragma unroll
+            for (uint32_t p = 0; p < 8; ++p) {
+                v[p] = 0;
+                if (p < nrank)
+                    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v[p]) : "r"(dsmem_map(part_addr + off, p)));
             }
+            int32_t sum = 0;
+#pragma unroll
+            for (uint32_t p = 0; p < 8; ++p) sum += v[p];
             const int grow = row0 + r, gcol = n_chunk * G::kCols + col;
             if (grow < M && gcol < N) C[static_cast<size_t>(grow) * ldc + gcol] = sum >> 6;
         }
