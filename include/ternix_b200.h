@@ -85,6 +85,28 @@ int ternix_b200_select_kernel(const void *dA, const void *dW, const void *dC, in
  *           frees, synchronises.  Also the target of the CPU-named ternix::mul_mat_ternary_* shims. */
 int ternix_b200_matmul_host(const int8_t *A, const uint8_t *W_packed, int32_t *C, int M, int K, int N, int kernel);
 
+/* ---- problem groups: many projections per launch ----------------------------------------------
+ * No reference counterpart (the reference launches one product at a time; its README lists
+ * graph-captured projection sets as future work, README.md:213).  A group is built once from a list of
+ * problems on device pointers and then run any number of times.  Decode-regime problems (M <= 16,
+ * K <= 8192, K % 16 == 0, N % 64 == 0, 16-byte aligned A and W) are served by ONE persistent kernel that
+ * streams all their weights back to back; the others are launched one by one behind it.  create()
+ * allocates a small device table (TMA descriptors and the work list) and copies it synchronously;
+ * run() only launches, on `stream`.  The pointers inside the problems must stay valid while the group lives. */
+typedef struct ternix_b200_problem {
+    const int8_t *dA;      /* [M,K] int8 row-major          */
+    const uint8_t *dW;     /* packed K x (N/4)              */
+    int32_t *dC;           /* [M,N] int32, row pitch ldc    */
+    int M, K, N;
+    long long ldc;
+} ternix_b200_problem;
+typedef struct ternix_b200_group ternix_b200_group;
+int ternix_b200_group_create(ternix_b200_group **out, const ternix_b200_problem *problems, int count);
+int ternix_b200_group_run(const ternix_b200_group *group, int32_t *d_status, void *stream);
+/* Kernel launches one run() makes (1 for the persistent kernel + 1 per problem it could not take). */
+int ternix_b200_group_launches(const ternix_b200_group *group);
+void ternix_b200_group_destroy(ternix_b200_group *group);
+
 /* ---- N-column sharding plan (host arithmetic only) ---------------------------------------------
  * Splits N columns over `world` ranks in granules of `granule` columns (a multiple of 4; 64 keeps each
  * shard's packed rows 16-byte aligned).  Writes the first column and the column count of `rank`.

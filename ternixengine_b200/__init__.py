@@ -44,9 +44,16 @@ EXPORTS = (
     "ternix_b200_pack_ternary", "ternix_b200_unpack_ternary", "ternix_b200_interleave_offline",
     "ternix_b200_find_non_ternary", "ternix_b200_slice_columns",
     "ternix_b200_matmul", "ternix_b200_matmul_ex", "ternix_b200_select_kernel", "ternix_b200_matmul_host",
+    "ternix_b200_group_create", "ternix_b200_group_run", "ternix_b200_group_launches", "ternix_b200_group_destroy",
     "ternix_b200_shard_columns", "ternix_b200_unpack_gathered",
     "ternix_b200_synth_activations", "ternix_b200_synth_packed_weights", "ternix_b200_synth_weights",
 )
+
+
+class _Problem(ctypes.Structure):
+    """struct ternix_b200_problem"""
+    _fields_ = [("dA", ctypes.c_void_p), ("dW", ctypes.c_void_p), ("dC", ctypes.c_void_p),
+                ("M", ctypes.c_int), ("K", ctypes.c_int), ("N", ctypes.c_int), ("ldc", ctypes.c_longlong)]
 
 
 class TernixError(RuntimeError):
@@ -77,6 +84,10 @@ def _load() -> ctypes.CDLL:
         "ternix_b200_matmul_ex": (i32, [vp, vp, vp, i32, i32, i32, i64, i32, vp, vp]),
         "ternix_b200_select_kernel": (i32, [vp, vp, vp, i32, i32, i32, i64]),
         "ternix_b200_matmul_host": (i32, [vp, vp, vp, i32, i32, i32, i32]),
+        "ternix_b200_group_create": (i32, [c.POINTER(vp), c.POINTER(_Problem), i32]),
+        "ternix_b200_group_run": (i32, [vp, vp, vp]),
+        "ternix_b200_group_launches": (i32, [vp]),
+        "ternix_b200_group_destroy": (None, [vp]),
         "ternix_b200_shard_columns": (i32, [i32, i32, i32, i32, c.POINTER(i32), c.POINTER(i32)]),
         "ternix_b200_unpack_gathered": (i32, [vp, vp, i32, i32, i64, i32, i32, i32, vp]),
         "ternix_b200_synth_activations": (None, [vp, sz, u64, i32]),
@@ -223,6 +234,53 @@ def matmul(a, w_packed, out=None, kernel: str = "auto", status=None, stream=None
                                        s.cuda_stream)
     _check(rc, "matmul")
     return out
+
+
+class ProjectionGroup:
+    """A fixed list of projections (a, w_packed, out) on one GPU, run with as few launches as possible:
+    decode-regime members share one persistent kernel (ternix_b200_group_create / _run)."""
+
+    def __init__(self, problems):
+        import torch
+
+        self._keep = []
+        arr = (_Problem * len(problems))()
+        for i, (a, w, out) in enumerate(problems):
+            if not (a.is_cuda and w.is_cuda and out.is_cuda):
+                raise ValueError("ProjectionGroup takes CUDA tensors")
+            if a.dtype != torch.int8 or w.dtype != torch.uint8 or out.dtype != torch.int32:
+                raise ValueError("A int8, W_packed uint8, out int32")
+            if not (a.is_contiguous() and w.is_contiguous()) or a.dim() != 2 or w.dim() != 2:
+                raise ValueError("A and W_packed must be contiguous 2-D tensors")
+            M, K = a.shape
+            N = w.shape[1] * 4
+            if w.shape[0] != K or tuple(out.shape) != (M, N) or (N > 1 and out.stride(1) != 1):
+                raise ValueError("shape mismatch")
+            arr[i] = _Problem(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, K, N,
+                              out.stride(0) if M > 1 else max(N, out.stride(0)))
+            self._keep.append((a, w, out))
+        self.device = problems[0][0].device if problems else None
+        handle = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            _check(lib.ternix_b200_group_create(ctypes.byref(handle), arr, len(problems)), "group_create")
+        self._h = handle
+        self.launches = lib.ternix_b200_group_launches(self._h)
+
+    def run(self, status=None, stream=None):
+        import torch
+
+        s = stream if stream is not None else torch.cuda.current_stream(self.device)
+        with torch.cuda.device(self.device):
+            _check(lib.ternix_b200_group_run(self._h, status.data_ptr() if status is not None else None,
+                                             s.cuda_stream), "group_run")
+
+    def close(self):
+        if getattr(self, "_h", None) and lib is not None:
+            lib.ternix_b200_group_destroy(self._h)
+        self._h = None
+
+    def __del__(self):
+        self.close()
 
 
 # --------------------------------------------------------------------------- N-column sharding

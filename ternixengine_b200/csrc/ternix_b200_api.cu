@@ -8,10 +8,15 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <algorithm>
 #include <mutex>
+#include <new>
+#include <queue>
+#include <vector>
 
 #include "kernel_gemm_tc.cuh"
 #include "kernel_gemv.cuh"
+#include "kernel_gemv_group.cuh"
 #include "kernel_generic.cuh"
 
 namespace {
@@ -254,6 +259,44 @@ __global__ void unpack_gathered_kernel(const int32_t* __restrict__ g, int32_t* _
     }
 }
 
+// ---------------------------------------------------------------- problem groups (many projections per launch)
+bool group_gemv_ok(const ternix_b200_problem& q) {
+    return q.M >= 1 && q.M <= 16 && q.K >= 1 && q.K <= tb200::kGroupMaxK && (q.K % 16) == 0 && (q.N % 64) == 0 &&
+           q.N >= 64 && aligned(q.dA, 16) && aligned(q.dW, 16) && q.ldc >= q.N;
+}
+
+template <int MR>
+int launch_gemv_group_t(const ternix_b200_group* g, int32_t* d_status, cudaStream_t st);
+
+}  // namespace
+
+struct ternix_b200_group {
+    std::vector<ternix_b200_problem> singles;   // problems launched one by one
+    void* d_blob = nullptr;                     // [GroupProblem[] | GroupItem[] | int cta_first[]]
+    const tb200::GroupProblem* d_probs = nullptr;
+    const tb200::GroupItem* d_items = nullptr;
+    const int* d_cta_first = nullptr;
+    int grid = 0, mr = 0, device = 0;
+    size_t grouped = 0;
+};
+
+namespace {
+
+template <int MR>
+int launch_gemv_group_t(const ternix_b200_group* g, int32_t* d_status, cudaStream_t st) {
+    auto kern = tb200::ternary_gemv_group_kernel<MR>;
+    constexpr size_t smem = tb200::gemv_group_smem_bytes<MR>();
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    kern<<<g->grid, tb200::kGemvThreads, smem, st>>>(g->d_probs, g->d_items, g->d_cta_first, d_status);
+    TB_CUDA(cudaGetLastError());
+    return TERNIX_B200_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -385,6 +428,119 @@ int ternix_b200_unpack_gathered(const int32_t* d_gathered, int32_t* dC, int M, i
         d_gathered, dC, M, N, ldc, world, granule, n_pad);
     TB_CUDA(cudaGetLastError());
     return TERNIX_B200_OK;
+}
+
+int ternix_b200_group_create(ternix_b200_group** out, const ternix_b200_problem* problems, int count) {
+    if (!out || count < 0 || (count > 0 && !problems)) return TERNIX_B200_ERR_INVALID_ARG;
+    *out = nullptr;
+    for (int i = 0; i < count; ++i) {
+        const ternix_b200_problem& q = problems[i];
+        if (q.M < 0 || q.K < 0 || q.N < 0 || (q.N % 4) != 0) return TERNIX_B200_ERR_INVALID_SHAPE;
+        if (q.ldc < q.N) return TERNIX_B200_ERR_INVALID_ARG;
+        if (q.M > 0 && q.N > 0 && (!q.dC || (q.K > 0 && (!q.dA || !q.dW)))) return TERNIX_B200_ERR_INVALID_ARG;
+    }
+    ternix_b200_group* g = new (std::nothrow) ternix_b200_group();
+    if (!g) return TERNIX_B200_ERR_INVALID_ARG;
+    if (cudaGetDevice(&g->device) != cudaSuccess) g->device = 0;
+
+    std::vector<tb200::GroupProblem> probs;
+    struct HostItem { tb200::GroupItem item; long cost; };
+    std::vector<HostItem> items;
+    int max_m = 0;
+    for (int i = 0; i < count; ++i) {
+        const ternix_b200_problem& q = problems[i];
+        if (q.M == 0 || q.N == 0) continue;
+        if (!group_gemv_ok(q)) { g->singles.push_back(q); continue; }
+        tb200::GroupProblem gp{};
+        const int rc = make_tmap_2d(&gp.tmap_w, q.dW, static_cast<uint64_t>(q.N / 4), static_cast<uint64_t>(q.K),
+                                    static_cast<uint64_t>(q.N / 4), tb200::kGroupWords * 4, tb200::kGroupStageRows,
+                                    CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) { delete g; return rc; }
+        gp.A = q.dA; gp.C = q.dC; gp.ldc = q.ldc; gp.M = q.M; gp.K = q.K; gp.N = q.N;
+        const int pi = static_cast<int>(probs.size());
+        probs.push_back(gp);
+        max_m = std::max(max_m, q.M);
+        ++g->grouped;
+    }
+    g->mr = max_m <= 1 ? 1 : max_m <= 2 ? 2 : 4;
+    for (int pi = 0; pi < static_cast<int>(probs.size()); ++pi) {
+        const tb200::GroupProblem& gp = probs[pi];
+        const int chunks = (gp.N + tb200::kGroupWords * 16 - 1) / (tb200::kGroupWords * 16);
+        for (int row0 = 0; row0 < gp.M; row0 += g->mr)
+            for (int c = 0; c < chunks; ++c) items.push_back({{pi, c, row0, 0}, static_cast<long>(gp.K) + 256});
+    }
+    if (!items.empty()) {
+        // longest-processing-time-first: heaviest items first, each to the least-loaded CTA
+        const int per_sm = g->mr <= 2 ? 2 : 1;
+        const int ctas = static_cast<int>(std::min<size_t>(items.size(), static_cast<size_t>(sm_count()) * per_sm));
+        std::stable_sort(items.begin(), items.end(), [](const HostItem& a, const HostItem& b) { return a.cost > b.cost; });
+        using Load = std::pair<long, int>;
+        std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
+        for (int c = 0; c < ctas; ++c) heap.push({0, c});
+        std::vector<std::vector<tb200::GroupItem>> per_cta(ctas);
+        for (const HostItem& h : items) {
+            Load l = heap.top();
+            heap.pop();
+            per_cta[l.second].push_back(h.item);
+            heap.push({l.first + h.cost, l.second});
+        }
+        std::vector<tb200::GroupItem> flat;
+        std::vector<int> first(ctas + 1, 0);
+        for (int c = 0; c < ctas; ++c) {
+            first[c] = static_cast<int>(flat.size());
+            flat.insert(flat.end(), per_cta[c].begin(), per_cta[c].end());
+        }
+        first[ctas] = static_cast<int>(flat.size());
+        const size_t b_probs = probs.size() * sizeof(tb200::GroupProblem);
+        const size_t b_items = (flat.size() * sizeof(tb200::GroupItem) + 63) & ~size_t(63);
+        const size_t b_first = first.size() * sizeof(int);
+        cudaError_t e = cudaMalloc(&g->d_blob, b_probs + b_items + b_first);
+        if (e != cudaSuccess) { delete g; return cuda_fail(e); }
+        uint8_t* d = static_cast<uint8_t*>(g->d_blob);
+        if ((e = cudaMemcpy(d, probs.data(), b_probs, cudaMemcpyHostToDevice)) != cudaSuccess ||
+            (e = cudaMemcpy(d + b_probs, flat.data(), flat.size() * sizeof(tb200::GroupItem), cudaMemcpyHostToDevice)) !=
+                cudaSuccess ||
+            (e = cudaMemcpy(d + b_probs + b_items, first.data(), b_first, cudaMemcpyHostToDevice)) != cudaSuccess) {
+            cudaFree(g->d_blob);
+            delete g;
+            return cuda_fail(e);
+        }
+        g->d_probs = reinterpret_cast<const tb200::GroupProblem*>(d);
+        g->d_items = reinterpret_cast<const tb200::GroupItem*>(d + b_probs);
+        g->d_cta_first = reinterpret_cast<const int*>(d + b_probs + b_items);
+        g->grid = ctas;
+    }
+    *out = g;
+    return TERNIX_B200_OK;
+}
+
+int ternix_b200_group_run(const ternix_b200_group* g, int32_t* d_status, void* stream) {
+    if (!g) return TERNIX_B200_ERR_INVALID_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (g->grid > 0) {
+        int rc;
+        if (g->mr == 1) rc = launch_gemv_group_t<1>(g, d_status, st);
+        else if (g->mr == 2) rc = launch_gemv_group_t<2>(g, d_status, st);
+        else rc = launch_gemv_group_t<4>(g, d_status, st);
+        if (rc) return rc;
+    }
+    for (const ternix_b200_problem& q : g->singles) {
+        const int rc = ternix_b200_matmul_ex(q.dA, q.dW, q.dC, q.M, q.K, q.N, q.ldc, TERNIX_B200_KERNEL_AUTO, d_status,
+                                             stream);
+        if (rc) return rc;
+    }
+    return TERNIX_B200_OK;
+}
+
+int ternix_b200_group_launches(const ternix_b200_group* g) {
+    if (!g) return 0;
+    return (g->grid > 0 ? 1 : 0) + static_cast<int>(g->singles.size());
+}
+
+void ternix_b200_group_destroy(ternix_b200_group* g) {
+    if (!g) return;
+    if (g->d_blob) cudaFree(g->d_blob);
+    delete g;
 }
 
 }  // extern "C"

@@ -227,3 +227,48 @@ def test_legacy_tiled_contract_rejects_before_touching_memory():
     fn.restype = ctypes.c_int
     fn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 3 + [ctypes.c_void_p]
     assert fn(None, None, None, 65, 64, 64, None) == 1          # cudaErrorInvalidValue
+
+
+def test_projection_group_bitnet_layers_m1():
+    """config 5 at M=1: two BitNet-shaped layers (14 projections) in one persistent launch."""
+    import torch
+    probs, expect = [], []
+    for layer in range(2):
+        for i, (name, k, n) in enumerate(BITNET_LAYER):
+            a, wp = synth(1, k, n, 1000 * layer + i)
+            expect.append(oracle_lib.matmul(a, wp, "scalar"))
+            probs.append((torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda(),
+                          torch.full((1, n), -999, dtype=torch.int32, device="cuda")))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    group = tb.ProjectionGroup(probs)
+    assert group.launches == 1
+    for _ in range(2):                       # a group can be run again and again
+        group.run(status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for (a, w, out), e in zip(probs, expect):
+        assert_same(out.cpu().numpy(), e, "grouped GEMV")
+    group.close()
+
+
+@pytest.mark.parametrize("M", [2, 3, 7, 16])
+def test_projection_group_mixed_rows_and_fallbacks(M):
+    """Row groups, ragged K tails, a column tail, and members the persistent kernel cannot take."""
+    import torch
+    shapes = [(M, 2560, 640), (1, 1040, 320), (M, 6912, 2560), (M, 144, 64), (3, 4099, 2052), (64, 256, 128),
+              (M, 8208, 128)]
+    probs, expect = [], []
+    for i, (m, k, n) in enumerate(shapes):
+        a, wp = synth(m, k, n, 77 * M + i)
+        expect.append(oracle_lib.matmul(a, wp))
+        wide = torch.full((m, n + 8), -999, dtype=torch.int32, device="cuda")
+        probs.append((torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda(), wide[:, :n]))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    group = tb.ProjectionGroup(probs)
+    assert group.launches == 1 + 3           # the ragged, the M=64 and the K>8192 members run on their own
+    group.run(status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for (a, w, out), e in zip(probs, expect):
+        assert_same(out.cpu().numpy(), e, f"group member {tuple(a.shape)}")
+        assert bool((out.base[:, out.shape[1]:] == -999).all()) if hasattr(out, "base") else True
