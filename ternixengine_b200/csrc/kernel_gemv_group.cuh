@@ -1,14 +1,27 @@
 // Decode regime, many projections per launch: a persistent GEMV kernel over a list of problems.
 //
-// One launch walks a host-built work list.  A work item is (problem, 256-column chunk, row group):
-// the full K of one chunk, so there is no split-K and nothing to reduce across CTAs.  Every CTA
-// owns a fixed, load-balanced slice of the list and streams the packed weights of item after
-// item through the same 16-stage TMA ring without draining it between items: per SM tens of KB
-// are always in flight, which is what a 4 MB GEMV launched on its own cannot do.  The per-problem
-// TMA descriptors live in a table in global memory.
+// One launch walks a host-built work list.  A work item is (problem, column chunk, row group): the
+// full K of one chunk of 16*WORDS columns (WORDS = 32: 512 columns, 128-byte rows; WORDS = 16: 256
+// columns), so there is no split-K and nothing to reduce across CTAs.  Every CTA owns a fixed,
+// load-balanced slice of the list and streams the packed weights of item after item through the
+// same TMA ring (8 stages of 8 KB) without draining it between items: per SM tens of KB are always in flight, which is what a 4 MB GEMV launched on
+// its own cannot do.  The per-problem TMA descriptors live in a table in global memory.
 //
-// The decode is the one of ternary_gemv_kernel (4x4 byte transpose, (T << s) & 0xC0C0C0C0, dp4a);
-// activations of the next item are prefetched with a 1-D bulk copy into the second of two
+// This kernel is bound by integer instruction issue, not by HBM, so the decode is the leanest
+// exact form found:
+//   * 4x4 byte transpose of four k-rows' words (8 PRMT), as in ternary_gemv_kernel;
+//   * T ^= 0xAAAAAAAA turns every 2-bit code c in {0,1,3} into c^2 in {2,3,1} = w + 2, so a field
+//     can be used IN PLACE, unsigned, with one AND and no shift or sign extension:
+//     dp4a.u32.s32(T & (0x03030303 << 2j), a) adds 4^j * sum_k a_k (w_k + 2);
+//   * the epilogue takes (acc >> 2j) - 2 * sum_k a_k.  The row sum of the activations is the same
+//     for every column and is computed once per item by one warp (dp4a against 0x01010101 and a
+//     warp-shuffle reduction).  Bound: 4^3 * 3 * 128 * K < 2^31, K <= 8192 here.
+//   45 integer instructions per 64 weights at M = 1 instead of 52.
+// With 64-byte rows (WORDS = 16) the two half-warps read k-rows in the orders 0,1,2,3 and 1,0,3,2 so that
+// their rows fall in different halves of the 32 banks; the activation bytes of the second half are
+// permuted to match.  With 128-byte rows a warp reads one whole row per load.
+//
+// Activations of the next item are prefetched with a 1-D bulk copy into the second of two
 // buffers while the current item is consumed; the per-item epilogue is one named barrier.
 #pragma once
 #include <cuda.h>
@@ -18,12 +31,13 @@
 
 namespace tb200 {
 
-constexpr int kGroupWords = 16;                 // 256 output columns per item
 constexpr int kGroupMaxK = 8192;                // activation bytes staged per row
-constexpr int kGroupStageRows = GemvGeom<kGroupWords>::kStageRows;   // 64
+constexpr int kGroupStageBytes = 8192;          // one TMA box
+constexpr int kGroupStages = 8;
+constexpr int group_stage_rows(int words) { return kGroupStageBytes / (words * 4); }   // 128 or 64 k-rows
 
 struct alignas(64) GroupProblem {
-    CUtensorMap tmap_w;        // packed W: [K rows][N/4 bytes], box 64 B x 64 rows
+    CUtensorMap tmap_w;        // packed W: [K rows][N/4 bytes], box (4*WORDS) B x group_stage_rows(WORDS)
     const int8_t* A;
     int32_t* C;
     long long ldc;
@@ -33,10 +47,10 @@ struct GroupItem {
     int problem, chunk, row0, pad;
 };
 
-template <int MR>
+template <int MR, int WORDS>
 constexpr size_t gemv_group_smem_bytes() {
-    return 128 + size_t(kGemvStages) * kGemvStageBytes + 2 * size_t(MR) * kGroupMaxK +
-           2 * size_t(MR) * 16 * (kGroupWords + 1) * 4 + (2 * kGemvStages + 4) * 8 + 16;
+    return 128 + size_t(kGroupStages) * kGroupStageBytes + 2 * size_t(MR) * kGroupMaxK +
+           2 * size_t(MR) * 16 * (WORDS + 1) * 4 + (2 * kGroupStages + 4) * 8 + 2 * MR * 4 + 16;
 }
 
 __device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
@@ -46,28 +60,36 @@ __device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gmem_s
                  : "memory");
 }
 
-template <int MR>
+__device__ __forceinline__ int dp4a_u8s8(uint32_t a_unsigned, int b_signed, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_unsigned), "r"(b_signed), "r"(c));
+    return d;
+}
+
+template <int MR, int WORDS>
 __global__ void __launch_bounds__(kGemvThreads)
 ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupItem* __restrict__ items,
                           const int* __restrict__ cta_first, int32_t* __restrict__ status) {
-    constexpr int WORDS = kGroupWords;
+    constexpr int kGroupStageRows = kGroupStageBytes / (WORDS * 4);
+    constexpr int kHalves = 32 / WORDS;                 // k-groups a warp covers per load
     constexpr int kPartInts = MR * 16 * (WORDS + 1);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     uint8_t* stages = base;
-    int8_t* a_buf = reinterpret_cast<int8_t*>(base + kGemvStages * kGemvStageBytes);     // [2][MR][kGroupMaxK]
+    int8_t* a_buf = reinterpret_cast<int8_t*>(base + kGroupStages * kGroupStageBytes);   // [2][MR][kGroupMaxK]
     int32_t* part = reinterpret_cast<int32_t*>(a_buf + 2 * MR * kGroupMaxK);             // [2][MR][16][WORDS+1]
     uint64_t* full = reinterpret_cast<uint64_t*>(part + 2 * kPartInts);
-    uint64_t* empty = full + kGemvStages;
-    uint64_t* a_full = empty + kGemvStages;      // [2]
+    uint64_t* empty = full + kGroupStages;
+    uint64_t* a_full = empty + kGroupStages;     // [2]
     uint64_t* a_empty = a_full + 2;              // [2]
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(a_empty + 2);
+    int32_t* row_sum = reinterpret_cast<int32_t*>(a_empty + 2);                          // [2][MR]
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(row_sum + 2 * MR);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int item_lo = cta_first[blockIdx.x], item_hi = cta_first[blockIdx.x + 1];
 
     if (tid == 0) {
-        for (int s = 0; s < kGemvStages; ++s) {
+        for (int s = 0; s < kGroupStages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kGemvConsumerWarps);
         }
@@ -100,24 +122,27 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
                                   &a_full[buf]);
                 const int ntiles = (K + kGroupStageRows - 1) / kGroupStageRows;
                 for (int tt = 0; tt < ntiles; ++tt, ++t) {
-                    const uint32_t s = t % kGemvStages;
-                    if (!mbar_wait(&empty[s], ((t / kGemvStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                    mbar_arrive_expect_tx(&full[s], kGemvStageBytes);
-                    tma_load_2d(stages + s * kGemvStageBytes, &p->tmap_w, it.chunk * WORDS * 4, tt * kGroupStageRows,
+                    const uint32_t s = t % kGroupStages;
+                    if (!mbar_wait(&empty[s], ((t / kGroupStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&full[s], kGroupStageBytes);
+                    tma_load_2d(stages + s * kGroupStageBytes, &p->tmap_w, it.chunk * WORDS * 4, tt * kGroupStageRows,
                                 &full[s]);
                 }
             }
             if (*abort_flag) {
-                const uint32_t first = t > kGemvStages ? t - kGemvStages : 0;
-                for (uint32_t j = first; j < t; ++j) mbar_drain(&full[j % kGemvStages], (j / kGemvStages) & 1);
+                const uint32_t first = t > kGroupStages ? t - kGroupStages : 0;
+                for (uint32_t j = first; j < t; ++j) mbar_drain(&full[j % kGroupStages], (j / kGroupStages) & 1);
                 mbar_drain(&a_full[0], 0);
                 mbar_drain(&a_full[1], 0);
             }
         }
     } else {
         // ------------------------------------------------------------ consumers
-        const int word = lane % WORDS;
-        const int kg = warp * (32 / WORDS) + lane / WORDS;     // 4-row group inside a stage
+        const int word = lane & (WORDS - 1);
+        const int half = lane / WORDS;                         // 64-byte rows: second half-warp reads rows 1,0,3,2
+        const int kg = warp * kHalves + half;                  // 4-row groups kg and kg + 8*kHalves of each stage
+        const uint32_t a_sel = half ? 0x2301u : 0x3210u;       // activation bytes in the same order
+        const int r0 = half, r1 = half ^ 1, r2 = 2 + half, r3 = 3 - half;
         uint32_t t = 0;
         bool ok = true;
         for (int i = item_lo; ok && i < item_hi; ++i) {
@@ -129,6 +154,19 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
             if (!mbar_wait(&a_full[buf], (n >> 1) & 1, abort_flag)) break;
             const int8_t* a_s = a_buf + buf * MR * kGroupMaxK;
 
+            if (warp == 0) {
+                // row sums of the activations: dp4a against ones, then a warp-shuffle reduction
+#pragma unroll
+                for (int r = 0; r < MR; ++r) {
+                    int sum = 0;
+                    for (int k4 = lane; k4 < (K >> 2); k4 += 32)
+                        sum = __dp4a(0x01010101, *reinterpret_cast<const int*>(a_s + r * kGroupMaxK + 4 * k4), sum);
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                    if (lane == 0) row_sum[buf * MR + r] = sum;
+                }
+            }
+
             int32_t acc[MR][16];
 #pragma unroll
             for (int r = 0; r < MR; ++r)
@@ -136,35 +174,48 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
                 for (int c = 0; c < 16; ++c) acc[r][c] = 0;
 
             for (int tt = 0; tt < ntiles; ++tt, ++t) {
-                const uint32_t s = t % kGemvStages;
-                if (!mbar_wait(&full[s], (t / kGemvStages) & 1, abort_flag)) { ok = false; break; }
-                const uint32_t* st = reinterpret_cast<const uint32_t*>(stages + s * kGemvStageBytes);
-                const uint32_t w0 = st[(kg * 4 + 0) * WORDS + word];
-                const uint32_t w1 = st[(kg * 4 + 1) * WORDS + word];
-                const uint32_t w2 = st[(kg * 4 + 2) * WORDS + word];
-                const uint32_t w3 = st[(kg * 4 + 3) * WORDS + word];
-                int a4[MR];
+                const uint32_t s = t % kGroupStages;
+                if (!mbar_wait(&full[s], (t / kGroupStages) & 1, abort_flag)) { ok = false; break; }
+                const uint32_t* st = reinterpret_cast<const uint32_t*>(stages + s * kGroupStageBytes);
+                uint32_t w[2][4];
+                int a4[2][MR];
 #pragma unroll
-                for (int r = 0; r < MR; ++r)
-                    a4[r] = *reinterpret_cast<const int*>(a_s + r * kGroupMaxK + tt * kGroupStageRows + kg * 4);
+                for (int g = 0; g < 2; ++g) {
+                    const int row = (kg + 8 * kHalves * g) * 4;
+                    w[g][0] = st[(row + r0) * WORDS + word];
+                    w[g][1] = st[(row + r1) * WORDS + word];
+                    w[g][2] = st[(row + r2) * WORDS + word];
+                    w[g][3] = st[(row + r3) * WORDS + word];
+                    const int k = tt * kGroupStageRows + row;
+#pragma unroll
+                    for (int r = 0; r < MR; ++r) {
+                        const int raw = *reinterpret_cast<const int*>(a_s + r * kGroupMaxK + k);
+                        const int ordered = kHalves > 1 ? static_cast<int>(__byte_perm(raw, 0, a_sel)) : raw;
+                        a4[g][r] = k < K ? ordered : 0;                    // nothing beyond K
+                    }
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
 
-                const uint32_t lo01 = __byte_perm(w0, w1, 0x5140), hi01 = __byte_perm(w0, w1, 0x7362);
-                const uint32_t lo23 = __byte_perm(w2, w3, 0x5140), hi23 = __byte_perm(w2, w3, 0x7362);
-                uint32_t T[4];
-                T[0] = __byte_perm(lo01, lo23, 0x5410);
-                T[1] = __byte_perm(lo01, lo23, 0x7632);
-                T[2] = __byte_perm(hi01, hi23, 0x5410);
-                T[3] = __byte_perm(hi01, hi23, 0x7632);
 #pragma unroll
-                for (int b = 0; b < 4; ++b)
+                for (int g = 0; g < 2; ++g) {
+                    const uint32_t x0 = w[g][0], x1 = w[g][1], x2 = w[g][2], x3 = w[g][3];
+                    const uint32_t lo01 = __byte_perm(x0, x1, 0x5140), hi01 = __byte_perm(x0, x1, 0x7362);
+                    const uint32_t lo23 = __byte_perm(x2, x3, 0x5140), hi23 = __byte_perm(x2, x3, 0x7362);
+                    uint32_t T[4];
+                    T[0] = __byte_perm(lo01, lo23, 0x5410);
+                    T[1] = __byte_perm(lo01, lo23, 0x7632);
+                    T[2] = __byte_perm(hi01, hi23, 0x5410);
+                    T[3] = __byte_perm(hi01, hi23, 0x7632);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int x = static_cast<int>((T[b] << (6 - 2 * j)) & 0xC0C0C0C0u);
+                    for (int b = 0; b < 4; ++b)
 #pragma unroll
-                        for (int r = 0; r < MR; ++r) acc[r][4 * b + j] = __dp4a(x, a4[r], acc[r][4 * b + j]);
-                    }
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t x = (T[b] ^ 0xAAAAAAAAu) & (0x03030303u << (2 * j));   // (w + 2) * 4^j, in place
+#pragma unroll
+                            for (int r = 0; r < MR; ++r) acc[r][4 * b + j] = dp4a_u8s8(x, a4[g][r], acc[r][4 * b + j]);
+                        }
+                }
             }
             if (!ok) break;
             __syncwarp();
@@ -183,7 +234,8 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
                 const int32_t v = *slot;
                 *slot = 0;
                 const int grow = it.row0 + r, gcol = it.chunk * WORDS * 16 + col;
-                if (grow < M && gcol < N) p->C[static_cast<size_t>(grow) * p->ldc + gcol] = v >> 6;
+                if (grow < M && gcol < N)
+                    p->C[static_cast<size_t>(grow) * p->ldc + gcol] = (v >> (2 * (col & 3))) - 2 * row_sum[buf * MR + r];
             }
         }
     }

@@ -265,7 +265,7 @@ bool group_gemv_ok(const ternix_b200_problem& q) {
            q.N >= 64 && aligned(q.dA, 16) && aligned(q.dW, 16) && q.ldc >= q.N;
 }
 
-template <int MR>
+template <int MR, int WORDS>
 int launch_gemv_group_t(const ternix_b200_group* g, int32_t* d_status, cudaStream_t st);
 
 }  // namespace
@@ -276,16 +276,16 @@ struct ternix_b200_group {
     const tb200::GroupProblem* d_probs = nullptr;
     const tb200::GroupItem* d_items = nullptr;
     const int* d_cta_first = nullptr;
-    int grid = 0, mr = 0, device = 0;
+    int grid = 0, mr = 0, words = 0, device = 0;
     size_t grouped = 0;
 };
 
 namespace {
 
-template <int MR>
+template <int MR, int WORDS>
 int launch_gemv_group_t(const ternix_b200_group* g, int32_t* d_status, cudaStream_t st) {
-    auto kern = tb200::ternary_gemv_group_kernel<MR>;
-    constexpr size_t smem = tb200::gemv_group_smem_bytes<MR>();
+    auto kern = tb200::ternary_gemv_group_kernel<MR, WORDS>;
+    constexpr size_t smem = tb200::gemv_group_smem_bytes<MR, WORDS>();
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [&] {
@@ -443,6 +443,10 @@ int ternix_b200_group_create(ternix_b200_group** out, const ternix_b200_problem*
     if (!g) return TERNIX_B200_ERR_INVALID_ARG;
     if (cudaGetDevice(&g->device) != cudaSuccess) g->device = 0;
 
+    // Item width: 512 columns (128-byte rows) unless TERNIX_B200_GROUP_WORDS=16 asks for 256 (tuning aid).
+    g->words = 32;
+    if (const char* env = std::getenv("TERNIX_B200_GROUP_WORDS")) g->words = std::atoi(env) == 16 ? 16 : 32;
+    const int item_cols = g->words * 16;
     std::vector<tb200::GroupProblem> probs;
     struct HostItem { tb200::GroupItem item; long cost; };
     std::vector<HostItem> items;
@@ -453,7 +457,7 @@ int ternix_b200_group_create(ternix_b200_group** out, const ternix_b200_problem*
         if (!group_gemv_ok(q)) { g->singles.push_back(q); continue; }
         tb200::GroupProblem gp{};
         const int rc = make_tmap_2d(&gp.tmap_w, q.dW, static_cast<uint64_t>(q.N / 4), static_cast<uint64_t>(q.K),
-                                    static_cast<uint64_t>(q.N / 4), tb200::kGroupWords * 4, tb200::kGroupStageRows,
+                                    static_cast<uint64_t>(q.N / 4), g->words * 4, tb200::group_stage_rows(g->words),
                                     CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc) { delete g; return rc; }
         gp.A = q.dA; gp.C = q.dC; gp.ldc = q.ldc; gp.M = q.M; gp.K = q.K; gp.N = q.N;
@@ -465,7 +469,7 @@ int ternix_b200_group_create(ternix_b200_group** out, const ternix_b200_problem*
     g->mr = max_m <= 1 ? 1 : max_m <= 2 ? 2 : 4;
     for (int pi = 0; pi < static_cast<int>(probs.size()); ++pi) {
         const tb200::GroupProblem& gp = probs[pi];
-        const int chunks = (gp.N + tb200::kGroupWords * 16 - 1) / (tb200::kGroupWords * 16);
+        const int chunks = (gp.N + item_cols - 1) / item_cols;
         for (int row0 = 0; row0 < gp.M; row0 += g->mr)
             for (int c = 0; c < chunks; ++c) items.push_back({{pi, c, row0, 0}, static_cast<long>(gp.K) + 256});
     }
@@ -519,9 +523,15 @@ int ternix_b200_group_run(const ternix_b200_group* g, int32_t* d_status, void* s
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (g->grid > 0) {
         int rc;
-        if (g->mr == 1) rc = launch_gemv_group_t<1>(g, d_status, st);
-        else if (g->mr == 2) rc = launch_gemv_group_t<2>(g, d_status, st);
-        else rc = launch_gemv_group_t<4>(g, d_status, st);
+        if (g->words == 32) {
+            if (g->mr == 1) rc = launch_gemv_group_t<1, 32>(g, d_status, st);
+            else if (g->mr == 2) rc = launch_gemv_group_t<2, 32>(g, d_status, st);
+            else rc = launch_gemv_group_t<4, 32>(g, d_status, st);
+        } else {
+            if (g->mr == 1) rc = launch_gemv_group_t<1, 16>(g, d_status, st);
+            else if (g->mr == 2) rc = launch_gemv_group_t<2, 16>(g, d_status, st);
+            else rc = launch_gemv_group_t<4, 16>(g, d_status, st);
+        }
         if (rc) return rc;
     }
     for (const ternix_b200_problem& q : g->singles) {
