@@ -307,6 +307,19 @@ def shard_columns(N: int, world: int, rank: int, granule: int = 64) -> ColumnSha
     return ColumnShard(N, world, rank, granule, n0.value, nc.value)
 
 
+def gathered_to_row_major(gathered: np.ndarray, N: int, granule: int = 64) -> np.ndarray:
+    """Host-side mirror of ternix_b200_unpack_gathered for arrays already on the host: rank-major
+    [world][M][n_pad] blocks -> row-major [M][N].  Layout bookkeeping only, no arithmetic."""
+    world, M, n_pad = gathered.shape
+    out = np.empty((M, N), dtype=gathered.dtype)
+    for r in range(world):
+        sh = shard_columns(N, world, r, granule)
+        if sh.n_cols > n_pad:
+            raise ValueError("gather blocks are narrower than the widest shard")
+        out[:, sh.n0:sh.n0 + sh.n_cols] = gathered[r, :, :sh.n_cols]
+    return out
+
+
 def should_shard(M: int, K: int, N: int, world: int, granule: int = 64) -> bool:
     """Small projections stay on one GPU: a shard must keep at least one full 256-column tile per
     rank and the problem must be in the tensor-core regime."""

@@ -177,6 +177,28 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     } else if (warp < kTcFirstEpilogueWarp) {
         // ================================================================ expanders
         const int e = threadIdx.x - kTcFirstExpandWarp * 32;          // 0..255
+        // Per-thread constants: where each of this thread's packed quads is read, and where the
+        // four 16-byte chunks it expands to are written (offsets inside a stage).
+        uint32_t src_off[G::kQuadsPerThread], dst_off[G::kQuadsPerThread][4];
+        bool rot[G::kQuadsPerThread];
+#pragma unroll
+        for (int i = 0; i < G::kQuadsPerThread; ++i) {
+            const int idx = e + i * (kTcExpandWarps * 32);
+            const int q = idx % G::kQuadsPerRow;               // which 64-column quad of the k-row
+            const int k = idx / G::kQuadsPerRow;               // k-row inside the block
+            src_off[i] = idx * 16;
+            // For BN = 256 the upper two quads of a row rotate their store order by two words, so
+            // that the eight lanes of a quarter-warp hit eight different 16-byte bank groups.
+            rot[i] = (G::kQuadsPerRow == 4) && (q & 2);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int uu = rot[i] ? (u ^ 2) : u;           // which word of the quad is stored u-th
+                const int col16 = q * 4 + uu;                  // 16-column chunk inside the tile
+                const int g = col16 >> 3, c = col16 & 7;
+                dst_off[i][u] = g * G::kGroupBytes + k * 128 + ((c ^ (k & 7)) << 4);
+            }
+        }
+        const uint32_t wp_sa = smem_u32(sWp), b_sa = smem_u32(sB);
         uint32_t it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
@@ -184,31 +206,22 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 const uint32_t sa = it % kTcStagesA, sb = it % kTcStagesB;
                 if (!mbar_wait(&full_a[sa], (it / kTcStagesA) & 1, abort_flag) ||
                     !mbar_wait(&empty_b[sb], ((it / kTcStagesB) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                const uint4* wp = reinterpret_cast<const uint4*>(sWp + sa * G::kWpBytes);
-                uint8_t* bt = sB + sb * G::kBBytes;
+                const uint32_t wp = wp_sa + sa * G::kWpBytes;
+                const uint32_t bt = b_sa + sb * G::kBBytes;
 #pragma unroll
                 for (int i = 0; i < G::kQuadsPerThread; ++i) {
-                    const int idx = e + i * (kTcExpandWarps * 32);
-                    const int q = idx % G::kQuadsPerRow;               // which 64-column quad of the k-row
-                    const int k = idx / G::kQuadsPerRow;               // k-row inside the block
-                    uint4 v = wp[idx];
-                    // For BN = 256 the upper two quads of a row rotate their store order by two words,
-                    // so that the eight lanes of a quarter-warp hit eight different 16-byte bank groups.
-                    const bool rot = (G::kQuadsPerRow == 4) && (q & 2);
-                    if (rot) { uint32_t t0 = v.x; v.x = v.z; v.z = t0; t0 = v.y; v.y = v.w; v.w = t0; }
+                    uint4 v = lds_v4(wp + src_off[i]);
+                    if (rot[i]) { uint32_t t0 = v.x; v.x = v.z; v.z = t0; t0 = v.y; v.y = v.w; v.w = t0; }
                     const uint32_t words[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
-                        const int uu = rot ? (u ^ 2) : u;              // which word of the quad this is
-                        const int col16 = q * 4 + uu;                  // 16-column chunk inside the tile
-                        const int g = col16 >> 3, c = col16 & 7;
                         const uint32_t w = words[u];
                         uint4 o;
                         o.x = (w << 6) & 0xC0C0C0C0u;
                         o.y = (w << 4) & 0xC0C0C0C0u;
                         o.z = (w << 2) & 0xC0C0C0C0u;
                         o.w = w & 0xC0C0C0C0u;
-                        *reinterpret_cast<uint4*>(bt + g * G::kGroupBytes + k * 128 + ((c ^ (k & 7)) << 4)) = o;
+                        sts_v4(bt + dst_off[i][u], o);
                     }
                 }
                 fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core
@@ -261,6 +274,7 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         }
     }
 
+    __syncwarp();
     if (*abort_flag && lane == 0 && status) atomicMax(status, kStatusTimeout);
     tc_fence_before_sync();
     __syncthreads();

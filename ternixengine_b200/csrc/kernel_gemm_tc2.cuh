@@ -1,0 +1,301 @@
+// Prefill-regime kernel, paired CTAs: tcgen05.mma.cta_group::2 on 256 x 256 output tiles.
+//
+// Why pairs.  With one CTA per tile the main loop moves about 112 KB through shared memory per
+// 128-deep k-block (TMA fills, expander read + write, tensor-core operand reads) and that, not
+// the tensor pipe, is what bounds ternary_gemm_tc_kernel.  Two CTAs of a cluster (the two SMs of
+// a TPC) share one 256 x 256 tile: each loads its own 128 rows of A, and each loads, expands
+// and serves only ITS 128 columns of W; the pair's MMA reads both halves.  Expander work and
+// expanded-tile traffic per SM halve.
+//
+// Roles per CTA (448 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA only; both
+// CTAs' warp 1 allocate and free TMEM), warps 2..9 expanders, warps 10..13 epilogue.
+// Cross-CTA signalling:
+//   peer expanders  -> leader full_b[s]      remote mbarrier arrive (16 arrivals = 8 local + 8 remote;
+//                                              a peer arrival also implies the peer's A box of that
+//                                              k-block has landed, because its expanders waited on
+//                                              the same TMA barrier)
+//   peer epilogue   -> leader tmem_empty[a]  remote mbarrier arrive (8 arrivals)
+//   leader MMA      -> empty_a / empty_b / tmem_full of BOTH CTAs: one tcgen05.commit per barrier whose
+//                      arrive is delivered to the same barrier offset in both CTAs of the pair.
+// TMA loads are ordinary per-CTA loads into the CTA's own shared memory.
+//
+// Decode, layouts, exactness and bounded waits are those of ternary_gemm_tc_kernel.
+#pragma once
+#include <cuda.h>
+#include <cstdint>
+#include "kernel_gemm_tc.cuh"
+#include "ptx_sm100.cuh"
+
+namespace tb200 {
+
+constexpr int kTc2StagesA = 8;
+constexpr int kTc2StagesB = 3;
+constexpr int kTc2Threads = (kTcFirstEpilogueWarp + 4) * 32;     // 448
+constexpr int kTc2TileN = 256;                                   // pair tile: 256 rows x 256 columns
+constexpr int kTc2HalfN = 128;                                   // columns expanded per CTA
+
+struct Tc2Geom {
+    static constexpr int kABytes = kTcBM * kTcBK;                // 16384: this CTA's 128 rows
+    static constexpr int kWpRowBytes = kTc2HalfN / 4;            // 32
+    static constexpr int kWpBytes = kTcBK * kWpRowBytes;         // 4096
+    static constexpr int kBBytes = kTc2HalfN * kTcBK;            // 16384: this CTA's 128 columns
+    static constexpr int kQuads = kTcBK * (kTc2HalfN / 64);      // 256 packed quads per k-block: one per expander
+    static constexpr uint32_t kTmemCols = 2 * kTc2TileN;         // two accumulator buffers of 256 columns
+    static constexpr size_t kSmemBytes = 1024 + size_t(kTc2StagesA) * (kABytes + kWpBytes) +
+                                         size_t(kTc2StagesB) * kBBytes + 512;
+    // D = s32, A = B = s8, A K-major, B MN-major, N = 256, M = 256 (pair)
+    static constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) |
+                                       (uint32_t(kTc2TileN >> 3) << 17) | (uint32_t(256 >> 4) << 24);
+    static_assert(kQuads == kTcExpandWarps * 32, "one packed quad per expander thread");
+};
+
+// ---- cta_group::2 forms of the tcgen05 helpers
+template <uint32_t kCols>
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+                 "n"(kCols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+template <uint32_t kCols>
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "n"(kCols) : "memory");
+}
+// Arrives, once the pair's MMAs issued so far have finished, on the barrier at this offset in this CTA only ...
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// ... and in both CTAs of the pair (CTA mask 0b11).
+__device__ __forceinline__ void tc_commit_pair_both(uint64_t* bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::
+                     "r"(smem_u32(bar)), "h"(mask)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive on the mbarrier at the same shared-memory offset in CTA `rank` of the cluster.
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(dsmem_map(smem_u32(bar), rank))
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(kTc2Threads, 1)
+ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                        int32_t* __restrict__ C, int M, int K, int N, long long ldc, int c_vec_ok,
+                        int32_t* __restrict__ status) {
+    using G = Tc2Geom;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sA = base;                                              // [StagesA][128][128]  swizzled
+    uint8_t* sB = sA + kTc2StagesA * G::kABytes;                     // [StagesB][128 k][128]  swizzled
+    uint8_t* sWp = sB + kTc2StagesB * G::kBBytes;                    // [StagesA][128 k][32]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sWp + kTc2StagesA * G::kWpBytes);
+    uint64_t* full_a = bars;                                         // TMA -> expanders (+ MMA in the leader)
+    uint64_t* empty_a = full_a + kTc2StagesA;                        // expanders + MMA -> TMA
+    uint64_t* full_b = empty_a + kTc2StagesA;                        // both CTAs' expanders -> leader MMA
+    uint64_t* empty_b = full_b + kTc2StagesB;                        // MMA -> expanders
+    uint64_t* tmem_full = empty_b + kTc2StagesB;                     // MMA -> epilogue  [2]
+    uint64_t* tmem_empty = tmem_full + 2;                            // both CTAs' epilogues -> leader MMA [2]
+    uint64_t* drain = tmem_empty + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();                         // 0 = leader, 1 = peer
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int m_tiles = (M + 2 * kTcBM - 1) / (2 * kTcBM);
+    const int n_tiles = (N + kTc2TileN - 1) / kTc2TileN;
+    const int num_tiles = m_tiles * n_tiles;
+    const int k_blocks = (K + kTcBK - 1) / kTcBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTc2StagesA; ++s) {
+            mbar_init(&full_a[s], 1);
+            mbar_init(&empty_a[s], kTcExpandWarps + 1);
+        }
+        for (int s = 0; s < kTc2StagesB; ++s) {
+            mbar_init(&full_b[s], 2 * kTcExpandWarps);
+            mbar_init(&empty_b[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&tmem_full[a], 1);
+            mbar_init(&tmem_empty[a], 8);
+        }
+        mbar_init(drain, 1);
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair<G::kTmemCols>(tmem_slot);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    cluster_sync_all();              // barriers of both CTAs are initialised before anyone arrives remotely
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ================================================================ TMA producer (each CTA for itself)
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_a);
+            tma_prefetch_desc(&tmap_w);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                const int m_t = tile % m_tiles, n_t = tile / m_tiles;
+                const int row0 = m_t * 2 * kTcBM + rank * kTcBM;
+                const int wp_x = n_t * (kTc2TileN / 4) + rank * G::kWpRowBytes;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % kTc2StagesA;
+                    if (!mbar_wait(&empty_a[s], ((it / kTc2StagesA) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&full_a[s], G::kABytes + G::kWpBytes);
+                    tma_load_2d(sA + s * G::kABytes, &tmap_a, kb * kTcBK, row0, &full_a[s]);
+                    tma_load_2d(sWp + s * G::kWpBytes, &tmap_w, wp_x, kb * kTcBK, &full_a[s]);
+                }
+            }
+            if (!ok) {
+                const uint32_t first = it > kTc2StagesA ? it - kTc2StagesA : 0;
+                for (uint32_t j = first; j < it; ++j) mbar_drain(&full_a[j % kTc2StagesA], (j / kTc2StagesA) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        // ================================================================ MMA issuer (leader CTA only)
+        if (leader && lane == 0) {
+            uint32_t it = 0, lt = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++lt) {
+                const uint32_t acc = lt & 1;
+                if (!mbar_wait(&tmem_empty[acc], ((lt >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * kTc2TileN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t sa = it % kTc2StagesA, sb = it % kTc2StagesB;
+                    if (!mbar_wait(&full_a[sa], (it / kTc2StagesA) & 1, abort_flag) ||
+                        !mbar_wait(&full_b[sb], (it / kTc2StagesB) & 1, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(sA + sa * G::kABytes);
+                    const uint32_t b_addr = smem_u32(sB + sb * G::kBBytes);
+#pragma unroll
+                    for (int k4 = 0; k4 < kTcBK / 32; ++k4) {
+                        const uint64_t da = umma_desc_sw128(a_addr + k4 * 32, 16, 1024);
+                        const uint64_t db = umma_desc_sw128(b_addr + k4 * 4096, G::kBBytes, 1024);
+                        tc_mma_i8_pair(d_tmem, da, db, G::kIdesc, (kb | k4) != 0 ? 1u : 0u);
+                    }
+                    tc_commit_pair_both(&empty_a[sa]);
+                    tc_commit_pair_both(&empty_b[sb]);
+                }
+                if (ok) tc_commit_pair_both(&tmem_full[acc]);
+            }
+            tc_commit_pair(drain);
+            mbar_wait(drain, 0, abort_flag);
+        }
+    } else if (warp < kTcFirstEpilogueWarp) {
+        // ================================================================ expanders: this CTA's 128 columns
+        const int e = threadIdx.x - kTcFirstExpandWarp * 32;          // 0..255: one packed quad per k-block
+        const int q = e & 1, k = e >> 1;                               // 64-column quad, k-row
+        uint32_t dst_off[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int c = q * 4 + u;                                   // 16-column chunk inside the 128-column half
+            dst_off[u] = k * 128 + ((c ^ (k & 7)) << 4);
+        }
+        const uint32_t wp_sa = smem_u32(sWp) + e * 16, b_sa = smem_u32(sB);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const uint32_t sa = it % kTc2StagesA, sb = it % kTc2StagesB;
+                if (!mbar_wait(&full_a[sa], (it / kTc2StagesA) & 1, abort_flag) ||
+                    !mbar_wait(&empty_b[sb], ((it / kTc2StagesB) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                const uint4 v = lds_v4(wp_sa + sa * G::kWpBytes);
+                const uint32_t bt = b_sa + sb * G::kBBytes;
+                const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t w = words[u];
+                    uint4 o;
+                    o.x = (w << 6) & 0xC0C0C0C0u;
+                    o.y = (w << 4) & 0xC0C0C0C0u;
+                    o.z = (w << 2) & 0xC0C0C0C0u;
+                    o.w = w & 0xC0C0C0C0u;
+                    sts_v4(bt + dst_off[u], o);
+                }
+                fence_proxy_async_smem();          // generic-proxy stores -> visible to the pair's tensor cores
+                __syncwarp();
+                if (lane == 0) {
+                    if (leader) mbar_arrive(&full_b[sb]);
+                    else mbar_arrive_remote(&full_b[sb], 0);
+                    mbar_arrive(&empty_a[sa]);
+                }
+            }
+        }
+    } else {
+        // ================================================================ epilogue: this CTA's 128 rows x 256 columns
+        const int quad = warp & 3;
+        uint32_t lt = 0;
+        bool ok = true;
+        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++lt) {
+            const int m_t = tile % m_tiles, n_t = tile / m_tiles;
+            const uint32_t acc = lt & 1;
+            if (!mbar_wait(&tmem_full[acc], (lt >> 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            const int row = m_t * 2 * kTcBM + rank * kTcBM + quad * 32 + lane;
+            int32_t* crow = C + static_cast<size_t>(row) * ldc + static_cast<size_t>(n_t) * kTc2TileN;
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kTc2TileN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kTc2TileN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(t_addr + c0, r);
+                tmem_ld_wait();
+                if (row < M && n_t * kTc2TileN + c0 < N) {
+                    int32_t o[32];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            o[h * 16 + 4 * (i & 3) + (i >> 2)] = static_cast<int32_t>(r[h * 16 + i]) >> 6;
+                    if (c_vec_ok) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            *reinterpret_cast<int4*>(crow + c0 + 4 * v) =
+                                make_int4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < 32; ++v) crow[c0 + v] = o[v];
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if (leader) mbar_arrive(&tmem_empty[acc]);
+                else mbar_arrive_remote(&tmem_empty[acc], 0);
+            }
+        }
+    }
+
+    __syncwarp();                    // the role branches above diverge inside warps; reconverge before aligned barriers
+    if (*abort_flag && lane == 0 && status) atomicMax(status, kStatusTimeout);
+    tc_fence_before_sync();
+    cluster_sync_all();              // no CTA frees TMEM or exits while its partner may still signal or read it
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair<G::kTmemCols>(tmem_base);
+    }
+}
+
+}  // namespace tb200

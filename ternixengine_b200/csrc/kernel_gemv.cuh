@@ -180,6 +180,7 @@ ternary_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const int8_t* __
             for (int c = 0; c < 16; ++c) atomicAdd(&part[(r * 16 + c) * (WORDS + 1) + word], acc[r][c]);
     }
 
+    __syncwarp();
     if (tid == 0 && *abort_flag && status) atomicMax(status, kStatusTimeout);
 
     // ---------------------------------------------------------------- split-K reduce across the cluster

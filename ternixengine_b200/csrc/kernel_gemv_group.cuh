@@ -142,7 +142,13 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
         const int half = lane / WORDS;                         // 64-byte rows: second half-warp reads rows 1,0,3,2
         const int kg = warp * kHalves + half;                  // 4-row groups kg and kg + 8*kHalves of each stage
         const uint32_t a_sel = half ? 0x2301u : 0x3210u;       // activation bytes in the same order
-        const int r0 = half, r1 = half ^ 1, r2 = 2 + half, r3 = 3 - half;
+        // byte offsets inside a stage of the four rows of this thread's first k-group, in load order
+        const uint32_t row_bytes = WORDS * 4;
+        const uint32_t o_base = (kg * 4) * row_bytes + word * 4;
+        const uint32_t o0 = o_base + half * row_bytes, o1 = o_base + (half ^ 1) * row_bytes;
+        const uint32_t o2 = o_base + (2 + half) * row_bytes, o3 = o_base + (3 - half) * row_bytes;
+        constexpr uint32_t kSecondGroup = 8 * kHalves * 4 * WORDS * 4;   // second k-group of the stage: 4 KB further
+        const uint32_t stages_sa = smem_u32(stages), a_sa = smem_u32(a_buf), part_sa = smem_u32(part);
         uint32_t t = 0;
         bool ok = true;
         for (int i = item_lo; ok && i < item_hi; ++i) {
@@ -152,7 +158,7 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
             const uint32_t n = i - item_lo, buf = n & 1;
             const int ntiles = (K + kGroupStageRows - 1) / kGroupStageRows;
             if (!mbar_wait(&a_full[buf], (n >> 1) & 1, abort_flag)) break;
-            const int8_t* a_s = a_buf + buf * MR * kGroupMaxK;
+            const int8_t* a_s = a_buf + buf * MR * kGroupMaxK;   // (row sums only; the main loop uses a_sa)
 
             if (warp == 0) {
                 // row sums of the activations: dp4a against ones, then a warp-shuffle reduction
@@ -176,21 +182,20 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
             for (int tt = 0; tt < ntiles; ++tt, ++t) {
                 const uint32_t s = t % kGroupStages;
                 if (!mbar_wait(&full[s], (t / kGroupStages) & 1, abort_flag)) { ok = false; break; }
-                const uint32_t* st = reinterpret_cast<const uint32_t*>(stages + s * kGroupStageBytes);
+                const uint32_t st = stages_sa + s * kGroupStageBytes;
                 uint32_t w[2][4];
                 int a4[2][MR];
 #pragma unroll
                 for (int g = 0; g < 2; ++g) {
-                    const int row = (kg + 8 * kHalves * g) * 4;
-                    w[g][0] = st[(row + r0) * WORDS + word];
-                    w[g][1] = st[(row + r1) * WORDS + word];
-                    w[g][2] = st[(row + r2) * WORDS + word];
-                    w[g][3] = st[(row + r3) * WORDS + word];
-                    const int k = tt * kGroupStageRows + row;
+                    w[g][0] = lds_u32(st + o0 + g * kSecondGroup);
+                    w[g][1] = lds_u32(st + o1 + g * kSecondGroup);
+                    w[g][2] = lds_u32(st + o2 + g * kSecondGroup);
+                    w[g][3] = lds_u32(st + o3 + g * kSecondGroup);
+                    const int k = tt * kGroupStageRows + (kg + 8 * kHalves * g) * 4;
 #pragma unroll
                     for (int r = 0; r < MR; ++r) {
-                        const int raw = *reinterpret_cast<const int*>(a_s + r * kGroupMaxK + k);
-                        const int ordered = kHalves > 1 ? static_cast<int>(__byte_perm(raw, 0, a_sel)) : raw;
+                        const uint32_t raw = lds_u32(a_sa + (buf * MR + r) * kGroupMaxK + k);
+                        const int ordered = static_cast<int>(kHalves > 1 ? __byte_perm(raw, 0, a_sel) : raw);
                         a4[g][r] = k < K ? ordered : 0;                    // nothing beyond K
                     }
                 }
@@ -221,18 +226,18 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
             __syncwarp();
             if (lane == 0) mbar_arrive(&a_empty[buf]);           // the activation buffer may be refilled
 
-            int32_t* pt = part + buf * kPartInts;
+            const uint32_t pt = part_sa + buf * kPartInts * 4;
 #pragma unroll
             for (int r = 0; r < MR; ++r)
 #pragma unroll
-                for (int c = 0; c < 16; ++c) atomicAdd(&pt[(r * 16 + c) * (WORDS + 1) + word], acc[r][c]);
+                for (int c = 0; c < 16; ++c) red_shared_add(pt + ((r * 16 + c) * (WORDS + 1) + word) * 4, acc[r][c]);
             asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumerWarps * 32) : "memory");
             // store this item's columns and leave the buffer zeroed for the item after next
             for (int idx = tid; idx < MR * WORDS * 16; idx += kGemvConsumerWarps * 32) {
                 const int r = idx / (WORDS * 16), col = idx % (WORDS * 16);
-                int32_t* slot = &pt[(r * 16 + (col & 15)) * (WORDS + 1) + (col >> 4)];
-                const int32_t v = *slot;
-                *slot = 0;
+                const uint32_t slot = pt + ((r * 16 + (col & 15)) * (WORDS + 1) + (col >> 4)) * 4;
+                const int32_t v = static_cast<int32_t>(lds_u32(slot));
+                sts_u32(slot, 0u);
                 const int grow = it.row0 + r, gcol = it.chunk * WORDS * 16 + col;
                 if (grow < M && gcol < N)
                     p->C[static_cast<size_t>(grow) * p->ldc + gcol] = (v >> (2 * (col & 3))) - 2 * row_sum[buf * MR + r];

@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "kernel_gemm_tc.cuh"
+#include "kernel_gemm_tc2.cuh"
 #include "kernel_gemv.cuh"
 #include "kernel_gemv_group.cuh"
 #include "kernel_generic.cuh"
@@ -225,11 +226,52 @@ int launch_gemm_tc_t(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, in
     return TERNIX_B200_OK;
 }
 
+// Paired-CTA kernel: clusters of two CTAs, one 256 x 256 tile per cluster at a time.
+int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,
+                    int32_t* d_status, cudaStream_t st) {
+    using G = tb200::Tc2Geom;
+    auto kern = tb200::ternary_gemm_tc2_kernel;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(G::kSmemBytes));
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    CUtensorMap tmap_a, tmap_w;
+    int rc = make_tmap_2d(&tmap_a, dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K),
+                          tb200::kTcBK, tb200::kTcBM, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tmap_w, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K),
+                      static_cast<uint64_t>(N / 4), G::kWpRowBytes, tb200::kTcBK, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    const long tiles = static_cast<long>((M + 255) / 256) * ((N + 255) / 256);
+    const long max_pairs = sm_count() / 2;
+    const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
+    const int c_vec_ok = (ldc % 4 == 0) && aligned(dC, 16);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(tb200::kTc2Threads, 1, 1);
+    cfg.dynamicSmemBytes = G::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    TB_CUDA(cudaLaunchKernelEx(&cfg, kern, tmap_a, tmap_w, dC, M, K, N, ldc, c_vec_ok, d_status));
+    return TERNIX_B200_OK;
+}
+
 int launch_gemm_tc(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,
                    int32_t* d_status, cudaStream_t st) {
-    // TERNIX_B200_TC_BN=128|256 overrides the tile-width heuristic (tuning aid).
+    // TERNIX_B200_TC_BN=128|256 forces the single-CTA kernel at that tile width, TERNIX_B200_TC_BN=2 the
+    // paired-CTA kernel (tuning aids).  Default: pairs whenever there are rows for both CTAs of a pair.
     int bn = 0;
     if (const char* env = std::getenv("TERNIX_B200_TC_BN")) bn = std::atoi(env);
+    if (bn == 2 || (bn == 0 && M > 128 && N >= 256)) return launch_gemm_tc2(dA, dW, dC, M, K, N, ldc, d_status, st);
     if (bn != 128 && bn != 256) {
         const long m_tiles = (M + tb200::kTcBM - 1) / tb200::kTcBM;
         const long tiles256 = m_tiles * ((N + 255) / 256);

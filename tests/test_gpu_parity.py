@@ -104,7 +104,7 @@ def test_config2_skinny_gemm():
         assert_same(device_matmul(a, wp, kern), expect, f"config2 [{kern}]")
 
 
-@pytest.mark.parametrize("bn", ["128", "256"])
+@pytest.mark.parametrize("bn", ["128", "256", "2"])
 def test_gemm_tc_tile_widths_and_ragged_edges(bn, monkeypatch):
     monkeypatch.setenv("TERNIX_B200_TC_BN", bn)
     for (m, k, n) in [(128, 128, 256), (128, 512, 128), (256, 1024, 512), (300, 2064, 832), (1, 16, 64),
