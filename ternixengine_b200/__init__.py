@@ -22,7 +22,7 @@ from typing import Optional
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_LIB_PATH = os.path.join(_HERE, "libternix_b200.so")
+_LIB_PATH = os.environ.get("TERNIX_B200_LIB") or os.path.join(_HERE, "libternix_b200.so")
 
 OK = 0
 ERR_INVALID_SHAPE = 1

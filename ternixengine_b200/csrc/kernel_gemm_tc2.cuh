@@ -28,8 +28,17 @@
 
 namespace tb200 {
 
-constexpr int kTc2StagesA = 8;
-constexpr int kTc2StagesB = 3;
+#ifndef TB200_TC2_STAGES_A
+#define TB200_TC2_STAGES_A 6
+#endif
+#ifndef TB200_TC2_STAGES_B
+#define TB200_TC2_STAGES_B 5
+#endif
+#ifndef TB200_TC2_EXPAND_GROUPS
+#define TB200_TC2_EXPAND_GROUPS 4
+#endif
+constexpr int kTc2StagesA = TB200_TC2_STAGES_A;     // ring of {A box, packed-W box}: 20 KB per stage
+constexpr int kTc2StagesB = TB200_TC2_STAGES_B;     // ring of expanded B halves: 16 KB per stage
 constexpr int kTc2Threads = (kTcFirstEpilogueWarp + 4) * 32;     // 448
 constexpr int kTc2TileN = 256;                                   // pair tile: 256 rows x 256 columns
 constexpr int kTc2HalfN = 128;                                   // columns expanded per CTA
@@ -46,7 +55,13 @@ struct Tc2Geom {
     // D = s32, A = B = s8, A K-major, B MN-major, N = 256, M = 256 (pair)
     static constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) |
                                        (uint32_t(kTc2TileN >> 3) << 17) | (uint32_t(256 >> 4) << 24);
-    static_assert(kQuads == kTcExpandWarps * 32, "one packed quad per expander thread");
+    // The expander warps are split into groups; group g owns the k-blocks with index % kGroups == g, so the
+    // latency of one expansion (load, decode, store, proxy fence, arrive) is spread over kGroups k-blocks.
+    static constexpr int kGroups = TB200_TC2_EXPAND_GROUPS;
+    static constexpr int kGroupThreads = kTcExpandWarps * 32 / kGroups;
+    static constexpr int kGroupWarps = kTcExpandWarps / kGroups;
+    static constexpr int kQuadsPerThread = kQuads / kGroupThreads;
+    static_assert(kTcExpandWarps % kGroups == 0 && kQuads % kGroupThreads == 0, "expander grouping");
 };
 
 // ---- cta_group::2 forms of the tcgen05 helpers
@@ -88,7 +103,7 @@ __device__ __forceinline__ void tc_mma_i8_pair(uint32_t tmem_d, uint64_t desc_a,
 }
 // Arrive on the mbarrier at the same shared-memory offset in CTA `rank` of the cluster.
 __device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(dsmem_map(smem_u32(bar), rank))
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(dsmem_map(smem_u32(bar), rank))
                  : "memory");
 }
 
@@ -125,10 +140,10 @@ ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTc2StagesA; ++s) {
             mbar_init(&full_a[s], 1);
-            mbar_init(&empty_a[s], kTcExpandWarps + 1);
+            mbar_init(&empty_a[s], G::kGroupWarps + 1);
         }
         for (int s = 0; s < kTc2StagesB; ++s) {
-            mbar_init(&full_b[s], 2 * kTcExpandWarps);
+            mbar_init(&full_b[s], 2 * G::kGroupWarps);
             mbar_init(&empty_b[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -205,34 +220,48 @@ ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         }
     } else if (warp < kTcFirstEpilogueWarp) {
         // ================================================================ expanders: this CTA's 128 columns
-        const int e = threadIdx.x - kTcFirstExpandWarp * 32;          // 0..255: one packed quad per k-block
-        const int q = e & 1, k = e >> 1;                               // 64-column quad, k-row
-        uint32_t dst_off[4];
+        const int e = threadIdx.x - kTcFirstExpandWarp * 32;          // 0..255
+        const uint32_t group = e / G::kGroupThreads;                   // which k-blocks this warp expands
+        const int eg = e % G::kGroupThreads;
+        uint32_t src_off[G::kQuadsPerThread], dst_off[G::kQuadsPerThread][4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int c = q * 4 + u;                                   // 16-column chunk inside the 128-column half
-            dst_off[u] = k * 128 + ((c ^ (k & 7)) << 4);
+        for (int i = 0; i < G::kQuadsPerThread; ++i) {
+            const int idx = eg + i * G::kGroupThreads;                 // packed quad of the k-block
+            const int q = idx & 1, k = idx >> 1;                       // 64-column quad, k-row
+            src_off[i] = idx * 16;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int c = q * 4 + u;                               // 16-column chunk inside the 128-column half
+                dst_off[i][u] = k * 128 + ((c ^ (k & 7)) << 4);
+            }
         }
-        const uint32_t wp_sa = smem_u32(sWp) + e * 16, b_sa = smem_u32(sB);
+        const uint32_t wp_sa = smem_u32(sWp), b_sa = smem_u32(sB);
         uint32_t it = 0;
         bool ok = true;
         for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
             for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                if (it % G::kGroups != group) continue;
                 const uint32_t sa = it % kTc2StagesA, sb = it % kTc2StagesB;
                 if (!mbar_wait(&full_a[sa], (it / kTc2StagesA) & 1, abort_flag) ||
                     !mbar_wait(&empty_b[sb], ((it / kTc2StagesB) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                const uint4 v = lds_v4(wp_sa + sa * G::kWpBytes);
+                const uint32_t wp = wp_sa + sa * G::kWpBytes;
                 const uint32_t bt = b_sa + sb * G::kBBytes;
-                const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+                uint4 v[G::kQuadsPerThread];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const uint32_t w = words[u];
-                    uint4 o;
-                    o.x = (w << 6) & 0xC0C0C0C0u;
-                    o.y = (w << 4) & 0xC0C0C0C0u;
-                    o.z = (w << 2) & 0xC0C0C0C0u;
-                    o.w = w & 0xC0C0C0C0u;
-                    sts_v4(bt + dst_off[u], o);
+                for (int i = 0; i < G::kQuadsPerThread; ++i) v[i] = lds_v4(wp + src_off[i]);
+#pragma unroll
+                for (int i = 0; i < G::kQuadsPerThread; ++i) {
+                    const uint32_t words[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t w = words[u];
+                        uint4 o;
+                        o.x = (w << 6) & 0xC0C0C0C0u;
+                        o.y = (w << 4) & 0xC0C0C0C0u;
+                        o.z = (w << 2) & 0xC0C0C0C0u;
+                        o.w = w & 0xC0C0C0C0u;
+                        sts_v4(bt + dst_off[i][u], o);
+                    }
                 }
                 fence_proxy_async_smem();          // generic-proxy stores -> visible to the pair's tensor cores
                 __syncwarp();
