@@ -107,6 +107,24 @@ int ternix_b200_group_run(const ternix_b200_group *group, int32_t *d_status, voi
 int ternix_b200_group_launches(const ternix_b200_group *group);
 void ternix_b200_group_destroy(ternix_b200_group *group);
 
+/* ---- one product, several destinations (fused gather) -------------------------------------------
+ * No reference counterpart.  Computes C[M,N] once and writes it to every pointer in dC_list (all with row
+ * pitch ldc): the caller's own C first and, for N-column-sharded weights, the same columns of C in each
+ * peer GPU's memory, through peer-mapped pointers.  For tensor-core-sized problems the stores are issued
+ * by the GEMM epilogue itself, tile by tile, so the transfer overlaps the main loop and no separate
+ * all-gather is needed; other problems are computed into dC_list[0] and copied.  n_dest <= 8.  The caller
+ * synchronises the GPUs (e.g. a barrier on the same stream) before anyone reads the gathered C. */
+int ternix_b200_matmul_bcast(const int8_t *dA, const uint8_t *dW, int32_t *const *dC_list, int n_dest, int M, int K,
+                             int N, long long ldc, int32_t *d_status, void *stream);
+
+/* Device buffers that other processes on the same node can map (CUDA IPC): allocate, export a 64-byte
+ * handle, import a peer's handle (enables peer access), close, free. */
+int ternix_b200_peer_alloc(void **dptr, size_t bytes);
+int ternix_b200_peer_free(void *dptr);
+int ternix_b200_peer_export(void *dptr, unsigned char handle[64]);
+int ternix_b200_peer_import(const unsigned char handle[64], void **dptr);
+int ternix_b200_peer_close(void *dptr);
+
 /* ---- N-column sharding plan (host arithmetic only) ---------------------------------------------
  * Splits N columns over `world` ranks in granules of `granule` columns (a multiple of 4; 64 keeps each
  * shard's packed rows 16-byte aligned).  Writes the first column and the column count of `rank`.

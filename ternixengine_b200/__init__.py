@@ -45,6 +45,8 @@ EXPORTS = (
     "ternix_b200_find_non_ternary", "ternix_b200_slice_columns",
     "ternix_b200_matmul", "ternix_b200_matmul_ex", "ternix_b200_select_kernel", "ternix_b200_matmul_host",
     "ternix_b200_group_create", "ternix_b200_group_run", "ternix_b200_group_launches", "ternix_b200_group_destroy",
+    "ternix_b200_matmul_bcast", "ternix_b200_peer_alloc", "ternix_b200_peer_free", "ternix_b200_peer_export",
+    "ternix_b200_peer_import", "ternix_b200_peer_close",
     "ternix_b200_shard_columns", "ternix_b200_unpack_gathered",
     "ternix_b200_synth_activations", "ternix_b200_synth_packed_weights", "ternix_b200_synth_weights",
 )
@@ -88,6 +90,12 @@ def _load() -> ctypes.CDLL:
         "ternix_b200_group_run": (i32, [vp, vp, vp]),
         "ternix_b200_group_launches": (i32, [vp]),
         "ternix_b200_group_destroy": (None, [vp]),
+        "ternix_b200_matmul_bcast": (i32, [vp, vp, c.POINTER(vp), i32, i32, i32, i32, i64, vp, vp]),
+        "ternix_b200_peer_alloc": (i32, [c.POINTER(vp), sz]),
+        "ternix_b200_peer_free": (i32, [vp]),
+        "ternix_b200_peer_export": (i32, [vp, c.c_char_p]),
+        "ternix_b200_peer_import": (i32, [c.c_char_p, c.POINTER(vp)]),
+        "ternix_b200_peer_close": (i32, [vp]),
         "ternix_b200_shard_columns": (i32, [i32, i32, i32, i32, c.POINTER(i32), c.POINTER(i32)]),
         "ternix_b200_unpack_gathered": (i32, [vp, vp, i32, i32, i64, i32, i32, i32, vp]),
         "ternix_b200_synth_activations": (None, [vp, sz, u64, i32]),
@@ -326,15 +334,56 @@ def should_shard(M: int, K: int, N: int, world: int, granule: int = 64) -> bool:
     return world > 1 and M > 16 and N // world >= 256 and N % granule == 0
 
 
-class ShardedTernaryLinear:
-    """One projection W[K,N], N-column-sharded over the ranks of a torch.distributed group.
+class _DeviceBuffer:
+    """A cudaMalloc'ed buffer owned by the library, viewable as a torch tensor and exportable to the
+    other processes of the node (CUDA IPC)."""
 
-    Each rank keeps only its packed column shard on its GPU.  forward(a) computes the local
-    C[:, n0:n0+n_cols] with the library's kernel, all-gathers the equal-sized blocks over NCCL
-    and scatters them into the row-major C[M,N] every rank returns.
+    def __init__(self, nbytes: int):
+        p = ctypes.c_void_p()
+        _check(lib.ternix_b200_peer_alloc(ctypes.byref(p), nbytes), "peer_alloc")
+        self.ptr, self.nbytes = p.value, nbytes
+
+    def export(self) -> bytes:
+        buf = ctypes.create_string_buffer(64)
+        _check(lib.ternix_b200_peer_export(self.ptr, buf), "peer_export")
+        return buf.raw
+
+    def as_tensor(self, shape, dtype, device):
+        import torch
+
+        itemsize = torch.empty((), dtype=dtype).element_size()
+        typestr = {torch.int32: "<i4", torch.int8: "|i1", torch.uint8: "|u1"}[dtype]
+        strides = []
+        acc = itemsize
+        for d in reversed(shape):
+            strides.insert(0, acc)
+            acc *= d
+        view = type("_View", (), {"__cuda_array_interface__": {
+            "shape": tuple(shape), "typestr": typestr, "data": (self.ptr, False), "version": 3,
+            "strides": tuple(strides)}})()
+        t = torch.as_tensor(view, device=device)
+        t._ternix_owner = self          # keep the allocation alive as long as the view
+        return t
+
+    def free(self):
+        if self.ptr and lib is not None:
+            lib.ternix_b200_peer_free(self.ptr)
+        self.ptr = None
+
+
+class ShardedTernaryLinear:
+    """One projection W[K,N], N-column-sharded over the ranks of a torch.distributed group (one process
+    per GPU).  Each rank keeps only its packed column shard on its GPU; forward(a) returns the full
+    row-major C[M,N] on every rank.
+
+    mode="peer" (default when world > 1): C lives in a buffer every rank maps from every other rank; the
+        GEMM epilogue of each rank stores its columns into all of them (ternix_b200_matmul_bcast) and a
+        tiny all-reduce on the same stream is the barrier.  The transfer overlaps the main loop.
+    mode="nccl": the baseline -- compute the local block, ncclAllGather equal-sized blocks, scatter to
+        row-major with ternix_b200_unpack_gathered.
     """
 
-    def __init__(self, w_packed_host: np.ndarray, group=None, granule: int = 64, device=None):
+    def __init__(self, w_packed_host: np.ndarray, group=None, granule: int = 64, device=None, mode: str = "peer"):
         import torch
         import torch.distributed as dist
 
@@ -347,28 +396,78 @@ class ShardedTernaryLinear:
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         local = slice_columns(w_packed_host, self.shard.n0, self.shard.n_cols)
         self.w_local = torch.from_numpy(local).to(self.device)
+        self.mode = mode if self.world > 1 else "local"
         self._gather = None
         self._block = None
+        self._M = None
+        self._c_buf = None
+        self._c = None
+        self._peer_ptrs = None
+        self._token = None
 
     def local(self, a, out=None):
         """This rank's columns only: (M, n_cols) int32."""
         return matmul(a, self.w_local, out=out)
 
-    def forward(self, a, out=None):
+    # ---- peer mode plumbing: one C buffer per rank, mapped by all ranks
+    def _setup_peer(self, M):
+        import torch
+        import torch.distributed as dist
+
+        with torch.cuda.device(self.device):
+            self._c_buf = _DeviceBuffer(M * self.N * 4)
+            self._c = self._c_buf.as_tensor((M, self.N), torch.int32, self.device)
+            handles = [None] * self.world
+            dist.all_gather_object(handles, self._c_buf.export(), group=self.group)
+            ptrs = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    ptrs.append(self._c_buf.ptr)
+                else:
+                    p = ctypes.c_void_p()
+                    _check(lib.ternix_b200_peer_import(h, ctypes.byref(p)), "peer_import")
+                    ptrs.append(p.value)
+        # own buffer first, then the peers, each offset to this rank's first column
+        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        self._peer_ptrs = (ctypes.c_void_p * self.world)(*[ptrs[r] + 4 * self.shard.n0 for r in order])
+        self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._M = M
+
+    def forward(self, a, out=None, status=None):
         import torch
         import torch.distributed as dist
 
         M = a.shape[0]
+        if self.mode == "local":
+            if out is None:
+                out = torch.empty((M, self.N), dtype=torch.int32, device=a.device)
+            return matmul(a, self.w_local, out=out, status=status)
+        if self.mode == "peer":
+            if self._M != M:
+                if self._M is not None:
+                    raise ValueError("peer mode keeps one C buffer: M must not change between calls")
+                self._setup_peer(M)
+            s = torch.cuda.current_stream(a.device)
+            if self.shard.n_cols:
+                with torch.cuda.device(a.device):
+                    _check(lib.ternix_b200_matmul_bcast(a.data_ptr(), self.w_local.data_ptr(), self._peer_ptrs,
+                                                        self.world, M, self.K, self.shard.n_cols, self.N,
+                                                        status.data_ptr() if status is not None else None,
+                                                        s.cuda_stream), "matmul_bcast")
+            dist.all_reduce(self._token, group=self.group)      # barrier on the stream: every rank's stores are done
+            if out is not None:
+                out.copy_(self._c)
+                return out
+            return self._c
+        # ---- NCCL baseline
         if out is None:
             out = torch.empty((M, self.N), dtype=torch.int32, device=a.device)
-        if self.world == 1:
-            return matmul(a, self.w_local, out=out)
         n_pad = self.shard.n_pad
         if self._gather is None or self._gather.shape[1] != M:
             self._gather = torch.empty((self.world, M, n_pad), dtype=torch.int32, device=a.device)
             self._block = torch.zeros((M, n_pad), dtype=torch.int32, device=a.device)
         if self.shard.n_cols:
-            matmul(a, self.w_local, out=self._block[:, : self.shard.n_cols])
+            matmul(a, self.w_local, out=self._block[:, : self.shard.n_cols], status=status)
         dist.all_gather_into_tensor(self._gather.view(-1), self._block.view(-1), group=self.group)
         s = torch.cuda.current_stream(a.device)
         _check(lib.ternix_b200_unpack_gathered(self._gather.data_ptr(), out.data_ptr(), M, self.N, out.stride(0),

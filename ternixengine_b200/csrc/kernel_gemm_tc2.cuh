@@ -19,6 +19,13 @@
 //                      arrive is delivered to the same barrier offset in both CTAs of the pair.
 // TMA loads are ordinary per-CTA loads into the CTA's own shared memory.
 //
+// Epilogue.  Each epilogue warp turns its 32 rows x 64 columns of the accumulator into row-contiguous
+// 256-byte segments through a small swizzled staging tile in shared memory, so that a warp store
+// covers whole 256-byte pieces of two rows instead of 16 bytes of 32 rows.  The same segments can be
+// written to several destinations: the local C and, when the weights are column-sharded over GPUs, the
+// same columns of C in every peer GPU's memory (plain stores through peer-mapped pointers), which
+// replaces a separate all-gather and overlaps the transfer with the next tile's main loop.
+//
 // Decode, layouts, exactness and bounded waits are those of ternary_gemm_tc_kernel.
 #pragma once
 #include <cuda.h>
@@ -29,7 +36,7 @@
 namespace tb200 {
 
 #ifndef TB200_TC2_STAGES_A
-#define TB200_TC2_STAGES_A 6
+#define TB200_TC2_STAGES_A 5
 #endif
 #ifndef TB200_TC2_STAGES_B
 #define TB200_TC2_STAGES_B 5
@@ -50,8 +57,9 @@ struct Tc2Geom {
     static constexpr int kBBytes = kTc2HalfN * kTcBK;            // 16384: this CTA's 128 columns
     static constexpr int kQuads = kTcBK * (kTc2HalfN / 64);      // 256 packed quads per k-block: one per expander
     static constexpr uint32_t kTmemCols = 2 * kTc2TileN;         // two accumulator buffers of 256 columns
+    static constexpr int kEpiBytes = 32 * 64 * 4;                // staging tile of one epilogue warp
     static constexpr size_t kSmemBytes = 1024 + size_t(kTc2StagesA) * (kABytes + kWpBytes) +
-                                         size_t(kTc2StagesB) * kBBytes + 512;
+                                         size_t(kTc2StagesB) * kBBytes + 4 * kEpiBytes + 512;
     // D = s32, A = B = s8, A K-major, B MN-major, N = 256, M = 256 (pair)
     static constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) |
                                        (uint32_t(kTc2TileN >> 3) << 17) | (uint32_t(256 >> 4) << 24);
@@ -62,6 +70,13 @@ struct Tc2Geom {
     static constexpr int kGroupWarps = kTcExpandWarps / kGroups;
     static constexpr int kQuadsPerThread = kQuads / kGroupThreads;
     static_assert(kTcExpandWarps % kGroups == 0 && kQuads % kGroupThreads == 0, "expander grouping");
+};
+
+// Where the finished columns go: the local C first, then the same place in each peer's C.
+constexpr int kTc2MaxDest = 8;
+struct Tc2Dest {
+    int32_t* c[kTc2MaxDest];
+    int count;
 };
 
 // ---- cta_group::2 forms of the tcgen05 helpers
@@ -109,7 +124,7 @@ __device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank)
 
 __global__ void __launch_bounds__(kTc2Threads, 1)
 ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                        int32_t* __restrict__ C, int M, int K, int N, long long ldc, int c_vec_ok,
+                        const Tc2Dest dest, int M, int K, int N, long long ldc, int c_vec_ok,
                         int32_t* __restrict__ status) {
     using G = Tc2Geom;
     extern __shared__ uint8_t smem_raw[];
@@ -117,7 +132,8 @@ ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     uint8_t* sA = base;                                              // [StagesA][128][128]  swizzled
     uint8_t* sB = sA + kTc2StagesA * G::kABytes;                     // [StagesB][128 k][128]  swizzled
     uint8_t* sWp = sB + kTc2StagesB * G::kBBytes;                    // [StagesA][128 k][32]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sWp + kTc2StagesA * G::kWpBytes);
+    uint8_t* sEpi = sWp + kTc2StagesA * G::kWpBytes;                 // [4 warps][32 rows][64 cols] int32, swizzled
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + 4 * G::kEpiBytes);
     uint64_t* full_a = bars;                                         // TMA -> expanders (+ MMA in the leader)
     uint64_t* empty_a = full_a + kTc2StagesA;                        // expanders + MMA -> TMA
     uint64_t* full_b = empty_a + kTc2StagesA;                        // both CTAs' expanders -> leader MMA
@@ -275,6 +291,8 @@ ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     } else {
         // ================================================================ epilogue: this CTA's 128 rows x 256 columns
         const int quad = warp & 3;
+        const uint32_t stage_sa = smem_u32(sEpi) + (warp - kTcFirstEpilogueWarp) * G::kEpiBytes;
+        const uint32_t my_row_sa = stage_sa + lane * 256;              // this lane's accumulator row in the staging tile
         uint32_t lt = 0;
         bool ok = true;
         for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++lt) {
@@ -282,31 +300,54 @@ ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             const uint32_t acc = lt & 1;
             if (!mbar_wait(&tmem_full[acc], (lt >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            const int row = m_t * 2 * kTcBM + rank * kTcBM + quad * 32 + lane;
-            int32_t* crow = C + static_cast<size_t>(row) * ldc + static_cast<size_t>(n_t) * kTc2TileN;
+            const int row_base = m_t * 2 * kTcBM + rank * kTcBM + quad * 32;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kTc2TileN;
 #pragma unroll 1
-            for (int c0 = 0; c0 < kTc2TileN; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld_32x32(t_addr + c0, r);
-                tmem_ld_wait();
-                if (row < M && n_t * kTc2TileN + c0 < N) {
+            for (int c0 = 0; c0 < kTc2TileN; c0 += 64) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(t_addr + c0 + 32 * h, r);
+                    tmem_ld_wait();
                     int32_t o[32];
 #pragma unroll
-                    for (int h = 0; h < 2; ++h)
+                    for (int g = 0; g < 2; ++g)
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            o[h * 16 + 4 * (i & 3) + (i >> 2)] = static_cast<int32_t>(r[h * 16 + i]) >> 6;
-                    if (c_vec_ok) {
+                            o[g * 16 + 4 * (i & 3) + (i >> 2)] = static_cast<int32_t>(r[g * 16 + i]) >> 6;
 #pragma unroll
-                        for (int v = 0; v < 8; ++v)
-                            *reinterpret_cast<int4*>(crow + c0 + 4 * v) =
-                                make_int4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
-                    } else {
-#pragma unroll
-                        for (int v = 0; v < 32; ++v) crow[c0 + v] = o[v];
+                    for (int j = 0; j < 8; ++j) {
+                        const int chunk = h * 8 + j;                   // 16-byte chunk of the 64-column row
+                        sts_v4(my_row_sa + ((chunk ^ (lane & 7)) << 4),
+                               make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
                     }
                 }
+                __syncwarp();
+                // read back row-contiguous: 16 lanes cover the 256 bytes of one row, a warp covers two rows
+                const int col = n_t * kTc2TileN + c0 + (lane & 15) * 4;
+#pragma unroll 4
+                for (int i = 0; i < 16; ++i) {
+                    const int rr = 2 * i + (lane >> 4);
+                    const uint4 v = lds_v4(stage_sa + rr * 256 + (((lane & 15) ^ (rr & 7)) << 4));
+                    const int row = row_base + rr;
+                    if (row < M && col < N) {
+                        const size_t off = static_cast<size_t>(row) * ldc + col;
+#pragma unroll
+                        for (int d = 0; d < kTc2MaxDest; ++d) {
+                            if (d >= dest.count) break;
+                            int32_t* out = dest.c[d] + off;
+                            if (c_vec_ok) {
+                                *reinterpret_cast<uint4*>(out) = v;
+                            } else {
+                                out[0] = static_cast<int32_t>(v.x);
+                                out[1] = static_cast<int32_t>(v.y);
+                                out[2] = static_cast<int32_t>(v.z);
+                                out[3] = static_cast<int32_t>(v.w);
+                            }
+                        }
+                    }
+                }
+                __syncwarp();                                          // before the staging tile is rewritten
             }
             tc_fence_before_sync();
             __syncwarp();

@@ -90,6 +90,10 @@ bool gemm_tc_ok(const void* dA, const void* dW, int K, int N) {
     return (N % 64) == 0 && (K % 16) == 0 && aligned(dA, 16) && aligned(dW, 16) && K <= kMaxScaledK;
 }
 
+bool gemm_tc2_ok(const void* dA, const void* dW, int M, int K, int N) {
+    return gemm_tc_ok(dA, dW, K, N) && M > 128 && N >= 256;
+}
+
 int select_kernel(const void* dA, const void* dW, int M, int K, int N) {
     if (gemv_ok(dW, M, K, N)) return TERNIX_B200_KERNEL_GEMV;
     if (gemm_tc_ok(dA, dW, K, N)) return TERNIX_B200_KERNEL_GEMM_TC;
@@ -227,8 +231,8 @@ int launch_gemm_tc_t(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, in
 }
 
 // Paired-CTA kernel: clusters of two CTAs, one 256 x 256 tile per cluster at a time.
-int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,
-                    int32_t* d_status, cudaStream_t st) {
+int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
+                    long long ldc, int32_t* d_status, cudaStream_t st) {
     using G = tb200::Tc2Geom;
     auto kern = tb200::ternary_gemm_tc2_kernel;
     static std::once_flag once;
@@ -248,7 +252,13 @@ int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int
     const long tiles = static_cast<long>((M + 255) / 256) * ((N + 255) / 256);
     const long max_pairs = sm_count() / 2;
     const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
-    const int c_vec_ok = (ldc % 4 == 0) && aligned(dC, 16);
+    tb200::Tc2Dest dest{};
+    dest.count = n_dest;
+    int c_vec_ok = (ldc % 4 == 0);
+    for (int d = 0; d < n_dest; ++d) {
+        dest.c[d] = dC_list[d];
+        c_vec_ok = c_vec_ok && aligned(dC_list[d], 16);
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     cfg.blockDim = dim3(tb200::kTc2Threads, 1, 1);
@@ -261,7 +271,7 @@ int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    TB_CUDA(cudaLaunchKernelEx(&cfg, kern, tmap_a, tmap_w, dC, M, K, N, ldc, c_vec_ok, d_status));
+    TB_CUDA(cudaLaunchKernelEx(&cfg, kern, tmap_a, tmap_w, dest, M, K, N, ldc, c_vec_ok, d_status));
     return TERNIX_B200_OK;
 }
 
@@ -271,7 +281,7 @@ int launch_gemm_tc(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int 
     // paired-CTA kernel (tuning aids).  Default: pairs whenever there are rows for both CTAs of a pair.
     int bn = 0;
     if (const char* env = std::getenv("TERNIX_B200_TC_BN")) bn = std::atoi(env);
-    if (bn == 2 || (bn == 0 && M > 128 && N >= 256)) return launch_gemm_tc2(dA, dW, dC, M, K, N, ldc, d_status, st);
+    if (bn == 2 || (bn == 0 && M > 128 && N >= 256)) return launch_gemm_tc2(dA, dW, &dC, 1, M, K, N, ldc, d_status, st);
     if (bn != 128 && bn != 256) {
         const long m_tiles = (M + tb200::kTcBM - 1) / tb200::kTcBM;
         const long tiles256 = m_tiles * ((N + 255) / 256);
@@ -593,6 +603,54 @@ void ternix_b200_group_destroy(ternix_b200_group* g) {
     if (!g) return;
     if (g->d_blob) cudaFree(g->d_blob);
     delete g;
+}
+
+int ternix_b200_matmul_bcast(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K,
+                             int N, long long ldc, int32_t* d_status, void* stream) {
+    if (M < 0 || K < 0 || N < 0 || (N % 4) != 0) return TERNIX_B200_ERR_INVALID_SHAPE;
+    if (ldc < N || n_dest < 1 || n_dest > tb200::kTc2MaxDest || !dC_list) return TERNIX_B200_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return TERNIX_B200_OK;
+    for (int d = 0; d < n_dest; ++d)
+        if (!dC_list[d]) return TERNIX_B200_ERR_INVALID_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (K > 0 && dA && dW && gemm_tc2_ok(dA, dW, M, K, N))
+        return launch_gemm_tc2(dA, dW, dC_list, n_dest, M, K, N, ldc, d_status, st);
+    // Any other problem: compute into the first destination, then copy it to the others.
+    const int rc = ternix_b200_matmul_ex(dA, dW, dC_list[0], M, K, N, ldc, TERNIX_B200_KERNEL_AUTO, d_status, stream);
+    if (rc) return rc;
+    for (int d = 1; d < n_dest; ++d)
+        TB_CUDA(cudaMemcpy2DAsync(dC_list[d], static_cast<size_t>(ldc) * 4, dC_list[0], static_cast<size_t>(ldc) * 4,
+                                  static_cast<size_t>(N) * 4, M, cudaMemcpyDefault, st));
+    return TERNIX_B200_OK;
+}
+
+int ternix_b200_peer_alloc(void** dptr, size_t bytes) {
+    if (!dptr) return TERNIX_B200_ERR_INVALID_ARG;
+    TB_CUDA(cudaMalloc(dptr, bytes ? bytes : 1));
+    return TERNIX_B200_OK;
+}
+int ternix_b200_peer_free(void* dptr) {
+    TB_CUDA(cudaFree(dptr));
+    return TERNIX_B200_OK;
+}
+int ternix_b200_peer_export(void* dptr, unsigned char handle[64]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    if (!dptr || !handle) return TERNIX_B200_ERR_INVALID_ARG;
+    cudaIpcMemHandle_t h;
+    TB_CUDA(cudaIpcGetMemHandle(&h, dptr));
+    std::memcpy(handle, &h, 64);
+    return TERNIX_B200_OK;
+}
+int ternix_b200_peer_import(const unsigned char handle[64], void** dptr) {
+    if (!dptr || !handle) return TERNIX_B200_ERR_INVALID_ARG;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, 64);
+    TB_CUDA(cudaIpcOpenMemHandle(dptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return TERNIX_B200_OK;
+}
+int ternix_b200_peer_close(void* dptr) {
+    TB_CUDA(cudaIpcCloseMemHandle(dptr));
+    return TERNIX_B200_OK;
 }
 
 }  // extern "C"

@@ -272,3 +272,25 @@ def test_projection_group_mixed_rows_and_fallbacks(M):
     for (a, w, out), e in zip(probs, expect):
         assert_same(out.cpu().numpy(), e, f"group member {tuple(a.shape)}")
         assert bool((out.base[:, out.shape[1]:] == -999).all()) if hasattr(out, "base") else True
+
+
+def test_bcast_two_destinations_one_gpu():
+    """The fused-gather entry point with two destination buffers on one GPU: both get the same exact C,
+    neighbouring columns stay untouched (paired-CTA epilogue), and the copy fallback for small problems."""
+    import ctypes
+    import torch
+    for (m, k, n) in [(300, 1024, 832), (512, 2048, 1024), (7, 129, 4), (16, 256, 128)]:
+        a, wp = synth(m, k, n, m + n)
+        expect = oracle_lib.matmul(a, wp)
+        da, dw = torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda()
+        wide = [torch.full((m, n + 64), -5, dtype=torch.int32, device="cuda") for _ in range(2)]
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ptrs = (ctypes.c_void_p * 2)(*[w.data_ptr() + 4 * 32 for w in wide])      # columns 32 .. 32+n of each
+        rc = tb.lib.ternix_b200_matmul_bcast(da.data_ptr(), dw.data_ptr(), ptrs, 2, m, k, n, n + 64,
+                                             status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert rc == 0 and int(status.item()) == 0
+        for w in wide:
+            got = w.cpu().numpy()
+            assert_same(got[:, 32:32 + n], expect, f"bcast {m}x{k}x{n}")
+            assert (got[:, :32] == -5).all() and (got[:, 32 + n:] == -5).all()
