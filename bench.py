@@ -256,7 +256,15 @@ def run_b200(args):
         base.forward(da, out=c2)
         torch.cuda.synchronize()
         if not bool((c2 == c).all()):
-            raise SystemExit(f"rank {rank}: NCCL-gathered C differs from the peer-store C")
+            bad = (c2 != c)
+            rows_bad = bad.any(dim=1).nonzero().flatten()
+            cols_bad = bad.any(dim=0).nonzero().flatten()
+            truth = tb.matmul(da[rows_bad[:8]].contiguous(), torch.from_numpy(wp_host).to(dev), kernel="generic")
+            raise SystemExit(f"rank {rank}: NCCL-gathered C differs from the peer-store C in {int(bad.sum())} entries, "
+                             f"rows {rows_bad[:6].tolist()}..{int(rows_bad[-1])} ({rows_bad.numel()}), cols "
+                             f"{cols_bad[:6].tolist()}..{int(cols_bad[-1])} ({cols_bad.numel()}); vs generic kernel: "
+                             f"peer-store wrong={int((c[rows_bad[:8]] != truth).sum())}, "
+                             f"nccl wrong={int((c2[rows_bad[:8]] != truth).sum())}")
         nccl_ms = max_over_ranks(timed(lambda: base.forward(da, out=c2), max(5, args.steps // 4), 3, barrier))
         nccl_ms /= max(5, args.steps // 4)
         del base, c2

@@ -256,10 +256,12 @@ ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         bool ok = true;
         for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
             for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                if (it % G::kGroups != group) continue;
                 const uint32_t sa = it % kTc2StagesA, sb = it % kTc2StagesB;
-                if (!mbar_wait(&full_a[sa], (it / kTc2StagesA) & 1, abort_flag) ||
-                    !mbar_wait(&empty_b[sb], ((it / kTc2StagesB) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                // Every expander warp observes every phase of full_a, also for k-blocks of other groups: a
+                // parity wait is only meaningful for a waiter that is at most one phase behind the barrier.
+                if (!mbar_wait(&full_a[sa], (it / kTc2StagesA) & 1, abort_flag)) { ok = false; break; }
+                if (it % G::kGroups != group) continue;
+                if (!mbar_wait(&empty_b[sb], ((it / kTc2StagesB) & 1) ^ 1, abort_flag)) { ok = false; break; }
                 const uint32_t wp = wp_sa + sa * G::kWpBytes;
                 const uint32_t bt = b_sa + sb * G::kBBytes;
                 uint4 v[G::kQuadsPerThread];

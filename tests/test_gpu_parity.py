@@ -294,3 +294,43 @@ def test_bcast_two_destinations_one_gpu():
             got = w.cpu().numpy()
             assert_same(got[:, 32:32 + n], expect, f"bcast {m}x{k}x{n}")
             assert (got[:, :32] == -5).all() and (got[:, 32 + n:] == -5).all()
+
+
+@pytest.mark.parametrize("kernel,shape,launches", [("gemm_tc", (1024, 8192, 3584), 150), ("gemm_tc", (128, 4096, 2048), 100),
+                                                   ("gemv", (1, 2560, 6912), 200), ("gemv", (4, 4096, 1024), 100)])
+def test_repeated_launches_are_bit_identical(kernel, shape, launches):
+    """Pipeline races show up as rare, launch-dependent errors: every one of many launches must equal the oracle."""
+    import torch
+    m, k, n = shape
+    a, wp = synth(m, k, n, 3 * m + n)
+    expect = torch.from_numpy(oracle_lib.matmul(a, wp)).cuda()
+    da, dw = torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    outs = [torch.empty((m, n), dtype=torch.int32, device="cuda") for _ in range(2)]
+    bad_launches = 0
+    for i in range(launches):
+        c = outs[i & 1]
+        c.fill_(-1)
+        tb.matmul(da, dw, out=c, kernel=kernel, status=status)
+        bad_launches += int(bool((c != expect).any()))
+    assert int(status.item()) == 0
+    assert bad_launches == 0, f"{bad_launches} of {launches} launches differ from the oracle"
+
+
+def test_repeated_group_runs_are_bit_identical():
+    import torch
+    probs, expect = [], []
+    for i, (name, k, n) in enumerate(BITNET_LAYER * 3):
+        a, wp = synth(1, k, n, 500 + i)
+        expect.append(torch.from_numpy(oracle_lib.matmul(a, wp, "scalar")).cuda())
+        probs.append((torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda(),
+                      torch.empty((1, n), dtype=torch.int32, device="cuda")))
+    group = tb.ProjectionGroup(probs)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    bad = 0
+    for _ in range(100):
+        for p in probs:
+            p[2].fill_(-1)
+        group.run(status=status)
+        bad += sum(int(bool((p[2] != e).any())) for p, e in zip(probs, expect))
+    assert int(status.item()) == 0 and bad == 0
