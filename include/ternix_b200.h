@@ -32,6 +32,7 @@ extern "C" {
 #define TERNIX_B200_ERR_CUDA           3  /* a CUDA call failed; see ternix_b200_last_cuda_error()   */
 #define TERNIX_B200_ERR_TIMEOUT        4  /* a bounded device-side wait ran out (kernel returned)    */
 #define TERNIX_B200_ERR_UNSUPPORTED    5  /* the kernel that was asked for cannot take this problem  */
+#define TERNIX_B200_ERR_TOO_LARGE      6  /* beyond the fixed capacity of an allocation-free entry   */
 
 /* ---- kernel selectors ------------------------------------------------------------------------ */
 #define TERNIX_B200_KERNEL_AUTO     0  /* pick by shape and alignment                                 */
@@ -106,6 +107,27 @@ int ternix_b200_group_run(const ternix_b200_group *group, int32_t *d_status, voi
 /* Kernel launches one run() makes (1 for the persistent kernel + 1 per problem it could not take). */
 int ternix_b200_group_launches(const ternix_b200_group *group);
 void ternix_b200_group_destroy(ternix_b200_group *group);
+
+/* ---- a decode batch for callers that must not allocate ---------------------------------------------
+ * No counterpart in the reference.  Some callers cannot have the library call cudaMalloc on their behalf:
+ * an inference server whose device memory is owned entirely by its own pool allocator, a caller inside a
+ * memory-budgeted or real-time section, a plugin host that forbids allocation after start-up.  For them
+ * this entry point runs the same persistent decode kernel as ternix_b200_group_run, but the tables that
+ * kernel reads (TMA descriptors, work list) sit in a fixed array inside the library image instead of a
+ * cudaMalloc'ed block, and the host side uses fixed buffers too: no cudaMalloc, cudaFree or other
+ * allocating call is made.  The caller passes inputs and outputs exactly as for a group.
+ *   - Limits: at most 256 problems and 4096 work items (one item per 512-column chunk per group of up to
+ *     4 rows) per call; beyond that TERNIX_B200_ERR_TOO_LARGE.  Only decode-regime problems are taken
+ *     (M <= 16, K <= 8192, K % 16 == 0, N % 64 == 0, 16-byte aligned A and W), else
+ *     TERNIX_B200_ERR_UNSUPPORTED.  The fixed array is 116,992 bytes and every GPU that loads the library
+ *     holds it until the process exits (ternix_b200_gemv_batch_noalloc_limits reports the numbers).
+ *   - The first call on a device looks up the array's device address (with that device current); make that
+ *     first call outside any stream capture.
+ *   - All calls share the one array and each call rewrites the tables it uses, so nothing needs clearing,
+ *     but two calls whose work overlaps on the GPU (different streams, or a second call issued before the
+ *     first one's kernel has finished on another stream) race on it.  Calls on one stream are safe. */
+int ternix_b200_gemv_batch_noalloc(const ternix_b200_problem *problems, int count, int32_t *d_status, void *stream);
+int ternix_b200_gemv_batch_noalloc_limits(int *max_problems, int *max_items, long long *scratch_bytes);
 
 /* ---- one product, several destinations (fused gather) -------------------------------------------
  * No reference counterpart.  Computes C[M,N] once and writes it to every pointer in dC_list (all with row

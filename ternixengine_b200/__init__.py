@@ -30,6 +30,7 @@ ERR_INVALID_ARG = 2
 ERR_CUDA = 3
 ERR_TIMEOUT = 4
 ERR_UNSUPPORTED = 5
+ERR_TOO_LARGE = 6
 
 KERNEL_AUTO = 0
 KERNEL_GENERIC = 1
@@ -45,6 +46,7 @@ EXPORTS = (
     "ternix_b200_find_non_ternary", "ternix_b200_slice_columns",
     "ternix_b200_matmul", "ternix_b200_matmul_ex", "ternix_b200_select_kernel", "ternix_b200_matmul_host",
     "ternix_b200_group_create", "ternix_b200_group_run", "ternix_b200_group_launches", "ternix_b200_group_destroy",
+    "ternix_b200_gemv_batch_noalloc", "ternix_b200_gemv_batch_noalloc_limits",
     "ternix_b200_matmul_bcast", "ternix_b200_peer_alloc", "ternix_b200_peer_free", "ternix_b200_peer_export",
     "ternix_b200_peer_import", "ternix_b200_peer_close",
     "ternix_b200_shard_columns", "ternix_b200_unpack_gathered",
@@ -90,6 +92,8 @@ def _load() -> ctypes.CDLL:
         "ternix_b200_group_run": (i32, [vp, vp, vp]),
         "ternix_b200_group_launches": (i32, [vp]),
         "ternix_b200_group_destroy": (None, [vp]),
+        "ternix_b200_gemv_batch_noalloc": (i32, [c.POINTER(_Problem), i32, vp, vp]),
+        "ternix_b200_gemv_batch_noalloc_limits": (i32, [c.POINTER(i32), c.POINTER(i32), c.POINTER(i64)]),
         "ternix_b200_matmul_bcast": (i32, [vp, vp, c.POINTER(vp), i32, i32, i32, i32, i64, vp, vp]),
         "ternix_b200_peer_alloc": (i32, [c.POINTER(vp), sz]),
         "ternix_b200_peer_free": (i32, [vp]),
@@ -123,7 +127,7 @@ def _check(status: int, where: str) -> None:
     if status == ERR_CUDA:
         e = lib.ternix_b200_last_cuda_error()
         msg += f" [cudaError {e}: {lib.ternix_b200_cuda_error_string(e).decode()}]"
-    if status in (ERR_INVALID_SHAPE, ERR_INVALID_ARG, ERR_UNSUPPORTED):
+    if status in (ERR_INVALID_SHAPE, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_TOO_LARGE):
         raise ValueError(msg)
     raise TernixError(status, msg)
 

@@ -349,6 +349,67 @@ int launch_gemv_group_t(const ternix_b200_group* g, int32_t* d_status, cudaStrea
     return TERNIX_B200_OK;
 }
 
+// ---------------------------------------------------------------- decode batch without any allocation
+// Scratch of ternix_b200_gemv_batch_noalloc: the tables the persistent GEMV kernel reads (per-problem TMA
+// descriptors, the work list and each CTA's slice of it) live in this file-scope device array instead of a
+// cudaMalloc'ed block.  Every GPU that loads the library carries it until the process exits.
+constexpr int kNoAllocMaxProblems = 256;
+constexpr int kNoAllocMaxItems = 4096;
+constexpr int kNoAllocMaxCtas = 512;
+constexpr size_t kNoAllocProbBytes = size_t(kNoAllocMaxProblems) * sizeof(tb200::GroupProblem);
+constexpr size_t kNoAllocItemBytes = size_t(kNoAllocMaxItems) * sizeof(tb200::GroupItem);
+constexpr size_t kNoAllocFirstBytes = ((size_t(kNoAllocMaxCtas) + 1) * sizeof(int) + 255) & ~size_t(255);
+constexpr size_t kNoAllocBytes = kNoAllocProbBytes + kNoAllocItemBytes + kNoAllocFirstBytes;   // 116,992 bytes
+static_assert(kNoAllocProbBytes % 256 == 0 && kNoAllocItemBytes % 256 == 0, "sub-tables stay 256-byte aligned");
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+// In host code `g_noalloc_scratch` is only a stand-in for the symbol, not a device address.  The address is
+// looked up once per device, with that device current, and cached here.
+constexpr int kNoAllocMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+unsigned char* g_noalloc_dev_ptr[kNoAllocMaxDevices] = {};
+
+int noalloc_scratch_for_current_device(unsigned char** out) {
+    int dev = 0;
+    TB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kNoAllocMaxDevices) return TERNIX_B200_ERR_UNSUPPORTED;
+    if (!g_noalloc_dev_ptr[dev]) {
+        void* p = nullptr;
+        TB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        g_noalloc_dev_ptr[dev] = static_cast<unsigned char*>(p);
+    }
+    *out = g_noalloc_dev_ptr[dev];
+    return TERNIX_B200_OK;
+}
+
+// Host-side staging of the same tables: fixed size, no heap.
+struct NoAllocHostTables {
+    tb200::GroupProblem probs[kNoAllocMaxProblems];
+    tb200::GroupItem items[kNoAllocMaxItems];       // in CTA order
+    tb200::GroupItem pending[kNoAllocMaxItems];     // before assignment, heaviest first
+    unsigned short cta_of[kNoAllocMaxItems];
+    int first[kNoAllocMaxCtas + 1];
+    long load[kNoAllocMaxCtas];
+};
+NoAllocHostTables g_noalloc_host;
+
+template <int MR, int WORDS>
+int launch_gemv_group_tables(const tb200::GroupProblem* d_probs, const tb200::GroupItem* d_items, const int* d_first,
+                             int grid, int32_t* d_status, cudaStream_t st) {
+    auto kern = tb200::ternary_gemv_group_kernel<MR, WORDS>;
+    constexpr size_t smem = tb200::gemv_group_smem_bytes<MR, WORDS>();
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    kern<<<grid, tb200::kGemvThreads, smem, st>>>(d_probs, d_items, d_first, d_status);
+    TB_CUDA(cudaGetLastError());
+    return TERNIX_B200_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -361,6 +422,7 @@ const char* ternix_b200_status_string(int status) {
         case TERNIX_B200_ERR_CUDA: return "CUDA error (see ternix_b200_last_cuda_error)";
         case TERNIX_B200_ERR_TIMEOUT: return "a bounded device-side wait ran out";
         case TERNIX_B200_ERR_UNSUPPORTED: return "the requested kernel cannot take this problem";
+        case TERNIX_B200_ERR_TOO_LARGE: return "the request exceeds the fixed capacity of this entry point";
         default: return "unknown status";
     }
 }
@@ -650,6 +712,98 @@ int ternix_b200_peer_import(const unsigned char handle[64], void** dptr) {
 }
 int ternix_b200_peer_close(void* dptr) {
     TB_CUDA(cudaIpcCloseMemHandle(dptr));
+    return TERNIX_B200_OK;
+}
+
+int ternix_b200_gemv_batch_noalloc(const ternix_b200_problem* problems, int count, int32_t* d_status, void* stream) {
+    if (count < 0 || (count > 0 && !problems)) return TERNIX_B200_ERR_INVALID_ARG;
+    if (count > kNoAllocMaxProblems) return TERNIX_B200_ERR_TOO_LARGE;
+    for (int i = 0; i < count; ++i) {
+        const ternix_b200_problem& q = problems[i];
+        if (q.M < 0 || q.K < 0 || q.N < 0 || (q.N % 4) != 0) return TERNIX_B200_ERR_INVALID_SHAPE;
+        if (q.ldc < q.N) return TERNIX_B200_ERR_INVALID_ARG;
+        if (q.M == 0 || q.N == 0) continue;
+        if (!q.dC || !q.dA || !q.dW) return TERNIX_B200_ERR_INVALID_ARG;
+        if (!group_gemv_ok(q)) return TERNIX_B200_ERR_UNSUPPORTED;     // decode-regime problems only
+    }
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);     // one caller at a time builds, copies and launches
+    unsigned char* d_scratch = nullptr;
+    int rc = noalloc_scratch_for_current_device(&d_scratch);
+    if (rc) return rc;
+    NoAllocHostTables& h = g_noalloc_host;
+    const int words = 32, item_cols = words * 16;
+    int n_probs = 0, max_m = 0;
+    for (int i = 0; i < count; ++i) {
+        const ternix_b200_problem& q = problems[i];
+        if (q.M == 0 || q.N == 0) continue;
+        tb200::GroupProblem& gp = h.probs[n_probs];
+        gp = tb200::GroupProblem{};
+        rc = make_tmap_2d(&gp.tmap_w, q.dW, static_cast<uint64_t>(q.N / 4), static_cast<uint64_t>(q.K),
+                          static_cast<uint64_t>(q.N / 4), words * 4, tb200::group_stage_rows(words),
+                          CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return rc;
+        gp.A = q.dA; gp.C = q.dC; gp.ldc = q.ldc; gp.M = q.M; gp.K = q.K; gp.N = q.N;
+        max_m = std::max(max_m, q.M);
+        ++n_probs;
+    }
+    if (n_probs == 0) return TERNIX_B200_OK;
+    const int mr = max_m <= 1 ? 1 : max_m <= 2 ? 2 : 4;
+    int n_items = 0;
+    for (int pi = 0; pi < n_probs; ++pi) {
+        const tb200::GroupProblem& gp = h.probs[pi];
+        const int chunks = (gp.N + item_cols - 1) / item_cols;
+        for (int row0 = 0; row0 < gp.M; row0 += mr)
+            for (int c = 0; c < chunks; ++c) {
+                if (n_items == kNoAllocMaxItems) return TERNIX_B200_ERR_TOO_LARGE;
+                h.pending[n_items++] = tb200::GroupItem{pi, c, row0, gp.K};     // pad carries the cost (K)
+            }
+    }
+    // heaviest first (ties by problem, chunk, row so the plan is deterministic), each to the least-loaded CTA
+    std::sort(h.pending, h.pending + n_items, [](const tb200::GroupItem& x, const tb200::GroupItem& y) {
+        if (x.pad != y.pad) return x.pad > y.pad;
+        if (x.problem != y.problem) return x.problem < y.problem;
+        if (x.chunk != y.chunk) return x.chunk < y.chunk;
+        return x.row0 < y.row0;
+    });
+    const int per_sm = mr <= 2 ? 2 : 1;
+    int ctas = std::min(n_items, sm_count() * per_sm);
+    ctas = std::min(ctas, kNoAllocMaxCtas);
+    for (int c = 0; c <= ctas; ++c) h.first[c] = 0;
+    for (int c = 0; c < ctas; ++c) h.load[c] = 0;
+    for (int i = 0; i < n_items; ++i) {
+        int best = 0;
+        for (int c = 1; c < ctas; ++c)
+            if (h.load[c] < h.load[best]) best = c;
+        h.cta_of[i] = static_cast<unsigned short>(best);
+        h.load[best] += h.pending[i].pad + 256;
+        ++h.first[best + 1];
+    }
+    for (int c = 0; c < ctas; ++c) h.first[c + 1] += h.first[c];
+    for (int c = 0; c < ctas; ++c) h.load[c] = h.first[c];               // reuse as the write cursor
+    for (int i = 0; i < n_items; ++i) {
+        tb200::GroupItem it = h.pending[i];
+        it.pad = 0;
+        h.items[h.load[h.cta_of[i]]++] = it;
+    }
+    // The tables are rewritten in full by every call, so nothing in the scratch has to start at zero.
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned char* d_items = d_scratch + kNoAllocProbBytes;
+    unsigned char* d_first = d_items + kNoAllocItemBytes;
+    TB_CUDA(cudaMemcpyAsync(d_scratch, h.probs, size_t(n_probs) * sizeof(tb200::GroupProblem), cudaMemcpyHostToDevice, st));
+    TB_CUDA(cudaMemcpyAsync(d_items, h.items, size_t(n_items) * sizeof(tb200::GroupItem), cudaMemcpyHostToDevice, st));
+    TB_CUDA(cudaMemcpyAsync(d_first, h.first, size_t(ctas + 1) * sizeof(int), cudaMemcpyHostToDevice, st));
+    const auto* p_probs = reinterpret_cast<const tb200::GroupProblem*>(d_scratch);
+    const auto* p_items = reinterpret_cast<const tb200::GroupItem*>(d_items);
+    const auto* p_first = reinterpret_cast<const int*>(d_first);
+    if (mr == 1) return launch_gemv_group_tables<1, 32>(p_probs, p_items, p_first, ctas, d_status, st);
+    if (mr == 2) return launch_gemv_group_tables<2, 32>(p_probs, p_items, p_first, ctas, d_status, st);
+    return launch_gemv_group_tables<4, 32>(p_probs, p_items, p_first, ctas, d_status, st);
+}
+
+int ternix_b200_gemv_batch_noalloc_limits(int* max_problems, int* max_items, long long* scratch_bytes) {
+    if (max_problems) *max_problems = kNoAllocMaxProblems;
+    if (max_items) *max_items = kNoAllocMaxItems;
+    if (scratch_bytes) *scratch_bytes = static_cast<long long>(kNoAllocBytes);
     return TERNIX_B200_OK;
 }
 
