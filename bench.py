@@ -35,6 +35,8 @@ M, K, N = 4096, 8192, 28672                 # prefill GEMM (Llama-3-70B-shaped F
 GEMV_K, GEMV_N = 2560, 6912                 # decode GEMV (BitNet-b1.58-2B FFN up shape)
 SEED = 20240531
 L2_BYTES = 126 * 1024 * 1024
+# one BitNet-b1.58-2B-shaped layer: (K, N) of Q, K, V, O, gate, up, down
+BITNET_LAYER = [(2560, 2560), (2560, 640), (2560, 640), (2560, 2560), (2560, 6912), (2560, 6912), (6912, 2560)]
 
 
 def load_peaks():
@@ -251,6 +253,9 @@ def run_b200(args):
     ms_e2e = max_over_ranks(timed(e2e_step, e2e_steps, 3, barrier))
     e2e_tops = ops * e2e_steps / (ms_e2e * 1e-3) / 1e12
 
+    # config 5 at M=256: the 210 projections of a 30-layer BitNet-2B-shaped model, sharded where it pays off
+    cfg5 = bench_config5_m256(tb, dev, world, rank, barrier, max_over_ranks)
+
     # the NCCL all-gather + unpack baseline for the same job (what the fused epilogue replaces)
     nccl_ms = None
     if world > 1:
@@ -308,6 +313,7 @@ def run_b200(args):
         "nccl_gather_baseline": None if nccl_ms is None else {
             "ms_per_step": nccl_ms, "tops": ops / (nccl_ms * 1e-3) / 1e12,
             "what": "same shards, local GEMM then ncclAllGather of C blocks then unpack to row-major"},
+        "config5_m256": cfg5,
         "gemv": gemv,
         "cpu_baseline": {"value": cpu_tops, "unit": "TOPS", "cores": cpu_threads, "kind": cpu_kind,
                          "sample": f"first {cpu_rows} of {M} rows, full K and N, {cpu_t:.1f} s, avx2_blocked row bands"},
@@ -323,7 +329,37 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
-BITNET_LAYER = [(2560, 2560), (2560, 640), (2560, 640), (2560, 2560), (2560, 6912), (2560, 6912), (6912, 2560)]
+def bench_config5_m256(tb, dev, world, rank, barrier, max_over_ranks):
+    """210 projections (7 per layer x 30 layers) at M=256 in one launch per rank; Q/O/gate/up/down are N-column
+    sharded over the ranks with the fused peer-store gather, K/V (N=640) stay whole on every rank."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib
+    Mb = 256
+    weights, acts, ops, byts = [], [], 0.0, 0
+    for layer in range(30):
+        for i, (k, n) in enumerate(BITNET_LAYER):
+            weights.append(tb.synth_packed_weights(k, n, SEED + 9000 + 10 * layer + i))
+            acts.append(torch.from_numpy(tb.synth_activations((Mb, k), SEED + 7000 + 10 * layer + i)).to(dev))
+            ops += 2.0 * Mb * k * n
+            byts += k * n // 4 + Mb * k + 4 * Mb * n
+    pset = tb.ShardedProjectionSet(weights, acts, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    outs = pset.run(status=status)
+    torch.cuda.synchronize()
+    barrier()
+    if int(status.item()) != 0:
+        raise SystemExit("a bounded device-side wait ran out in the grouped GEMM")
+    for idx in (0, 1, 4, 209):                      # Q, K, gate of layer 0 and `down` of layer 29, every entry
+        expect = oracle_lib.matmul(acts[idx].cpu().numpy(), weights[idx])
+        if not np.array_equal(outs[idx].cpu().numpy(), expect):
+            raise SystemExit(f"rank {rank}: config 5 projection {idx} differs from the CPU oracle")
+    reps = 10
+    ms = max_over_ranks(timed(pset.run, reps, 3, barrier)) / reps
+    return {"workload": "config5: 30 layers x {Q,K,V,O,gate,up,down} of a BitNet-b1.58-2B-shaped model, M=256",
+            "projections": 210, "launches_per_rank": pset.launches, "ms": ms, "projections_per_s": 210 / (ms * 1e-3),
+            "tops": ops / (ms * 1e-3) / 1e12, "gbs_algorithmic": byts / (ms * 1e-3) / 1e9,
+            "sharded": "Q,O,gate,up,down by N columns; K,V whole on every rank" if world > 1 else "single GPU"}
 
 
 def bench_gemv(tb, dev, peaks):

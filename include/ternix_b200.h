@@ -91,7 +91,9 @@ int ternix_b200_matmul_host(const int8_t *A, const uint8_t *W_packed, int32_t *C
  * graph-captured projection sets as future work, README.md:213).  A group is built once from a list of
  * problems on device pointers and then run any number of times.  Decode-regime problems (M <= 16,
  * K <= 8192, K % 16 == 0, N % 64 == 0, 16-byte aligned A and W) are served by ONE persistent kernel that
- * streams all their weights back to back; the others are launched one by one behind it.  create()
+ * streams all their weights back to back; prefill-regime problems (M > 128, N >= 256, K % 16 == 0,
+ * N % 64 == 0, aligned) by ONE launch of the paired-CTA tensor-core GEMM that walks all their tiles; the
+ * others are launched one by one behind them.  create()
  * allocates a small device table (TMA descriptors and the work list) and copies it synchronously;
  * run() only launches, on `stream`.  The pointers inside the problems must stay valid while the group lives. */
 typedef struct ternix_b200_problem {
@@ -103,6 +105,12 @@ typedef struct ternix_b200_problem {
 } ternix_b200_problem;
 typedef struct ternix_b200_group ternix_b200_group;
 int ternix_b200_group_create(ternix_b200_group **out, const ternix_b200_problem *problems, int count);
+/* Same, with n_peers (< 8) extra destinations per problem: peer_dC[i * n_peers + j] receives the same C as
+ * problems[i].dC (same ldc), typically the same columns of C in a peer GPU's memory.  Prefill-regime members
+ * (M > 128, N >= 256, TMA-able) share ONE launch of the paired-CTA GEMM, which stores to all destinations
+ * from its epilogue; other members are computed as usual and copied. */
+int ternix_b200_group_create_ex(ternix_b200_group **out, const ternix_b200_problem *problems, int count,
+                                int32_t *const *peer_dC, int n_peers);
 int ternix_b200_group_run(const ternix_b200_group *group, int32_t *d_status, void *stream);
 /* Kernel launches one run() makes (1 for the persistent kernel + 1 per problem it could not take). */
 int ternix_b200_group_launches(const ternix_b200_group *group);

@@ -45,7 +45,7 @@ EXPORTS = (
     "ternix_b200_pack_ternary", "ternix_b200_unpack_ternary", "ternix_b200_interleave_offline",
     "ternix_b200_find_non_ternary", "ternix_b200_slice_columns",
     "ternix_b200_matmul", "ternix_b200_matmul_ex", "ternix_b200_select_kernel", "ternix_b200_matmul_host",
-    "ternix_b200_group_create", "ternix_b200_group_run", "ternix_b200_group_launches", "ternix_b200_group_destroy",
+    "ternix_b200_group_create", "ternix_b200_group_create_ex", "ternix_b200_group_run", "ternix_b200_group_launches", "ternix_b200_group_destroy",
     "ternix_b200_gemv_batch_noalloc", "ternix_b200_gemv_batch_noalloc_limits",
     "ternix_b200_matmul_bcast", "ternix_b200_peer_alloc", "ternix_b200_peer_free", "ternix_b200_peer_export",
     "ternix_b200_peer_import", "ternix_b200_peer_close",
@@ -89,6 +89,7 @@ def _load() -> ctypes.CDLL:
         "ternix_b200_select_kernel": (i32, [vp, vp, vp, i32, i32, i32, i64]),
         "ternix_b200_matmul_host": (i32, [vp, vp, vp, i32, i32, i32, i32]),
         "ternix_b200_group_create": (i32, [c.POINTER(vp), c.POINTER(_Problem), i32]),
+        "ternix_b200_group_create_ex": (i32, [c.POINTER(vp), c.POINTER(_Problem), i32, c.POINTER(vp), i32]),
         "ternix_b200_group_run": (i32, [vp, vp, vp]),
         "ternix_b200_group_launches": (i32, [vp]),
         "ternix_b200_group_destroy": (None, [vp]),
@@ -252,7 +253,9 @@ class ProjectionGroup:
     """A fixed list of projections (a, w_packed, out) on one GPU, run with as few launches as possible:
     decode-regime members share one persistent kernel (ternix_b200_group_create / _run)."""
 
-    def __init__(self, problems):
+    def __init__(self, problems, peer_ptrs=None):
+        """problems: list of (a, w_packed, out).  peer_ptrs: optional list (one entry per problem) of lists of raw
+        device addresses that receive the same C as `out` (peer GPUs' buffers), all lists of equal length."""
         import torch
 
         self._keep = []
@@ -273,8 +276,14 @@ class ProjectionGroup:
             self._keep.append((a, w, out))
         self.device = problems[0][0].device if problems else None
         handle = ctypes.c_void_p()
+        n_peers = len(peer_ptrs[0]) if peer_ptrs else 0
         with torch.cuda.device(self.device):
-            _check(lib.ternix_b200_group_create(ctypes.byref(handle), arr, len(problems)), "group_create")
+            if n_peers:
+                flat = (ctypes.c_void_p * (len(problems) * n_peers))(*[p for row in peer_ptrs for p in row])
+                _check(lib.ternix_b200_group_create_ex(ctypes.byref(handle), arr, len(problems), flat, n_peers),
+                       "group_create_ex")
+            else:
+                _check(lib.ternix_b200_group_create(ctypes.byref(handle), arr, len(problems)), "group_create")
         self._h = handle
         self.launches = lib.ternix_b200_group_launches(self._h)
 
@@ -478,3 +487,85 @@ class ShardedTernaryLinear:
                                                self.world, self.shard.granule, n_pad, s.cuda_stream),
                "unpack_gathered")
         return out
+
+
+class ShardedProjectionSet:
+    """Many projections at once (e.g. every linear layer of a model), each N-column-sharded over the ranks where
+    that pays off (should_shard) and kept whole otherwise.  One process per GPU.  All outputs of a rank live in one
+    buffer that every other rank maps; run() is one launch per regime on each rank (ternix_b200_group_run): the
+    paired-CTA GEMM writes every sharded projection's columns into all ranks' outputs from its epilogue, and a
+    4-byte all-reduce on the stream is the barrier.  Unsharded projections are computed by every rank for itself.
+    """
+
+    def __init__(self, weights_host, activations, group=None, granule: int = 64, device=None):
+        """weights_host: list of packed (K, N/4) uint8 arrays; activations: list of (M, K) int8 CUDA tensors."""
+        import torch
+        import torch.distributed as dist
+
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.count = len(weights_host)
+        plans, offsets, total = [], [], 0
+        for w, a in zip(weights_host, activations):
+            K, N = w.shape[0], w.shape[1] * 4
+            M = a.shape[0]
+            sharded = should_shard(M, K, N, self.world, granule)
+            sh = shard_columns(N, self.world, self.rank, granule) if sharded else ColumnShard(N, 1, 0, granule, 0, N)
+            plans.append((M, K, N, sharded, sh))
+            offsets.append(total)
+            total += M * N * 4
+            total = (total + 255) & ~255
+        with torch.cuda.device(self.device):
+            self._buf = _DeviceBuffer(max(total, 256))
+            ptrs = [self._buf.ptr]
+            if self.world > 1:
+                handles = [None] * self.world
+                dist.all_gather_object(handles, self._buf.export(), group=self.group)
+                ptrs = []
+                for r, h in enumerate(handles):
+                    if r == self.rank:
+                        ptrs.append(self._buf.ptr)
+                    else:
+                        p = ctypes.c_void_p()
+                        _check(lib.ternix_b200_peer_import(h, ctypes.byref(p)), "peer_import")
+                        ptrs.append(p.value)
+        self.outputs, self._w_local, problems, peer_rows = [], [], [], []
+        others = [r for r in range(self.world) if r != self.rank]
+        for (M, K, N, sharded, sh), off, w, a in zip(plans, offsets, weights_host, activations):
+            view = _OffsetView(self._buf, off).as_tensor((M, N), torch.int32, self.device)
+            self.outputs.append(view)
+            local = slice_columns(w, sh.n0, sh.n_cols) if sharded else w
+            w_dev = torch.from_numpy(np.ascontiguousarray(local)).to(self.device)
+            self._w_local.append(w_dev)
+            if sh.n_cols == 0:
+                continue
+            problems.append((a, w_dev, view[:, sh.n0:sh.n0 + sh.n_cols]))
+            if self.world > 1:
+                # sharded: the same columns in every peer's buffer; unsharded: nobody else needs them, but the
+                # table wants equally many pointers per problem, so point the "peers" at this rank's own C
+                base = [ptrs[r] if sharded else self._buf.ptr for r in others]
+                peer_rows.append([b + off + 4 * sh.n0 for b in base])
+        self.any_sharded = any(p[3] for p in plans)
+        self._group = ProjectionGroup(problems, peer_ptrs=peer_rows if (self.world > 1 and self.any_sharded) else None)
+        self.launches = self._group.launches
+        self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def run(self, status=None):
+        import torch.distributed as dist
+
+        self._group.run(status=status)
+        if self.world > 1 and self.any_sharded:
+            dist.all_reduce(self._token, group=self.group)
+        return self.outputs
+
+
+class _OffsetView:
+    """A window into a _DeviceBuffer (same lifetime), viewable as a torch tensor."""
+
+    def __init__(self, buf: "_DeviceBuffer", offset: int):
+        self._buf, self.ptr = buf, buf.ptr + offset
+
+    def as_tensor(self, shape, dtype, device):
+        return _DeviceBuffer.as_tensor(self, shape, dtype, device)

@@ -79,6 +79,53 @@ struct Tc2Dest {
     int count;
 };
 
+// Grouped mode: one launch walks the tiles of many products (a "problem group"); descriptors and
+// destinations come from tables in global memory, and every pair owns a fixed slice of the tile list.
+struct alignas(64) Tc2Problem {
+    CUtensorMap tmap_a;        // A: [M rows][K bytes], box 128 x 128, 128-byte swizzle
+    CUtensorMap tmap_w;        // packed W: [K rows][N/4 bytes], box 32 B x 128 rows
+    Tc2Dest dest;
+    long long ldc;
+    int M, K, N, c_vec_ok;
+};
+struct Tc2Tile {
+    int problem, m_t, n_t, pad;
+};
+
+// The tile sequence of one CTA pair.  Every warp role constructs its own walker and sees the same sequence.
+template <bool kGrouped>
+struct Tc2Walk {
+    const CUtensorMap* ta;
+    const CUtensorMap* tw;
+    const Tc2Dest* dest;
+    long long ldc;
+    int M, N, c_vec_ok, m_t, n_t, k_blocks;
+    // single product
+    int tile, num_tiles, stride, m_tiles;
+    // group
+    const Tc2Problem* probs;
+    const Tc2Tile* tiles;
+    int idx, end;
+
+    __device__ __forceinline__ bool next() {
+        if constexpr (kGrouped) {
+            if (idx >= end) return false;
+            const Tc2Tile t = tiles[idx++];
+            const Tc2Problem* p = probs + t.problem;
+            ta = &p->tmap_a; tw = &p->tmap_w; dest = &p->dest;
+            ldc = p->ldc; M = p->M; N = p->N; c_vec_ok = p->c_vec_ok;
+            m_t = t.m_t; n_t = t.n_t;
+            k_blocks = (p->K + kTcBK - 1) / kTcBK;
+            return true;
+        } else {
+            if (tile >= num_tiles) return false;
+            m_t = tile % m_tiles; n_t = tile / m_tiles;
+            tile += stride;
+            return true;
+        }
+    }
+};
+
 // ---- cta_group::2 forms of the tcgen05 helpers
 template <uint32_t kCols>
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result) {
@@ -122,10 +169,12 @@ __device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank)
                  : "memory");
 }
 
+template <bool kGrouped>
 __global__ void __launch_bounds__(kTc2Threads, 1)
 ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                        const Tc2Dest dest, int M, int K, int N, long long ldc, int c_vec_ok,
-                        int32_t* __restrict__ status) {
+                        const __grid_constant__ Tc2Dest dest, int M, int K, int N, long long ldc, int c_vec_ok,
+                        const Tc2Problem* __restrict__ probs, const Tc2Tile* __restrict__ tiles,
+                        const int* __restrict__ pair_first, int32_t* __restrict__ status) {
     using G = Tc2Geom;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -148,10 +197,21 @@ ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     const uint32_t rank = cluster_ctarank();                         // 0 = leader, 1 = peer
     const bool leader = rank == 0;
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    const int m_tiles = (M + 2 * kTcBM - 1) / (2 * kTcBM);
-    const int n_tiles = (N + kTc2TileN - 1) / kTc2TileN;
-    const int num_tiles = m_tiles * n_tiles;
-    const int k_blocks = (K + kTcBK - 1) / kTcBK;
+    auto make_walk = [&]() {
+        Tc2Walk<kGrouped> w{};
+        if constexpr (kGrouped) {
+            w.probs = probs; w.tiles = tiles;
+            w.idx = pair_first[pair]; w.end = pair_first[pair + 1];
+        } else {
+            w.ta = &tmap_a; w.tw = &tmap_w; w.dest = &dest;
+            w.ldc = ldc; w.M = M; w.N = N; w.c_vec_ok = c_vec_ok;
+            w.k_blocks = (K + kTcBK - 1) / kTcBK;
+            w.m_tiles = (M + 2 * kTcBM - 1) / (2 * kTcBM);
+            w.num_tiles = w.m_tiles * ((N + kTc2TileN - 1) / kTc2TileN);
+            w.tile = pair; w.stride = num_pairs;
+        }
+        return w;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTc2StagesA; ++s) {
@@ -182,20 +242,22 @@ ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     if (warp == 0) {
         // ================================================================ TMA producer (each CTA for itself)
         if (lane == 0) {
-            tma_prefetch_desc(&tmap_a);
-            tma_prefetch_desc(&tmap_w);
+            if constexpr (!kGrouped) {
+                tma_prefetch_desc(&tmap_a);
+                tma_prefetch_desc(&tmap_w);
+            }
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-                const int m_t = tile % m_tiles, n_t = tile / m_tiles;
-                const int row0 = m_t * 2 * kTcBM + rank * kTcBM;
-                const int wp_x = n_t * (kTc2TileN / 4) + rank * G::kWpRowBytes;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            auto walk = make_walk();
+            while (ok && walk.next()) {
+                const int row0 = walk.m_t * 2 * kTcBM + rank * kTcBM;
+                const int wp_x = walk.n_t * (kTc2TileN / 4) + rank * G::kWpRowBytes;
+                for (int kb = 0; kb < walk.k_blocks; ++kb, ++it) {
                     const uint32_t s = it % kTc2StagesA;
                     if (!mbar_wait(&empty_a[s], ((it / kTc2StagesA) & 1) ^ 1, abort_flag)) { ok = false; break; }
                     mbar_arrive_expect_tx(&full_a[s], G::kABytes + G::kWpBytes);
-                    tma_load_2d(sA + s * G::kABytes, &tmap_a, kb * kTcBK, row0, &full_a[s]);
-                    tma_load_2d(sWp + s * G::kWpBytes, &tmap_w, wp_x, kb * kTcBK, &full_a[s]);
+                    tma_load_2d(sA + s * G::kABytes, walk.ta, kb * kTcBK, row0, &full_a[s]);
+                    tma_load_2d(sWp + s * G::kWpBytes, walk.tw, wp_x, kb * kTcBK, &full_a[s]);
                 }
             }
             if (!ok) {
@@ -208,12 +270,13 @@ ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         if (leader && lane == 0) {
             uint32_t it = 0, lt = 0;
             bool ok = true;
-            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++lt) {
+            auto walk = make_walk();
+            for (; ok && walk.next(); ++lt) {
                 const uint32_t acc = lt & 1;
                 if (!mbar_wait(&tmem_empty[acc], ((lt >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * kTc2TileN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = 0; kb < walk.k_blocks; ++kb, ++it) {
                     const uint32_t sa = it % kTc2StagesA, sb = it % kTc2StagesB;
                     if (!mbar_wait(&full_a[sa], (it / kTc2StagesA) & 1, abort_flag) ||
                         !mbar_wait(&full_b[sb], (it / kTc2StagesB) & 1, abort_flag)) { ok = false; break; }
@@ -254,8 +317,9 @@ ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         const uint32_t wp_sa = smem_u32(sWp), b_sa = smem_u32(sB);
         uint32_t it = 0;
         bool ok = true;
-        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        auto walk = make_walk();
+        while (ok && walk.next()) {
+            for (int kb = 0; kb < walk.k_blocks; ++kb, ++it) {
                 const uint32_t sa = it % kTc2StagesA, sb = it % kTc2StagesB;
                 // Every expander warp observes every phase of full_a, also for k-blocks of other groups: a
                 // parity wait is only meaningful for a waiter that is at most one phase behind the barrier.
@@ -297,8 +361,13 @@ ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         const uint32_t my_row_sa = stage_sa + lane * 256;              // this lane's accumulator row in the staging tile
         uint32_t lt = 0;
         bool ok = true;
-        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++lt) {
-            const int m_t = tile % m_tiles, n_t = tile / m_tiles;
+        auto walk = make_walk();
+        for (; ok && walk.next(); ++lt) {
+            const int m_t = walk.m_t, n_t = walk.n_t;
+            const int M = walk.M, N = walk.N, c_vec_ok = walk.c_vec_ok;
+            const long long ldc = walk.ldc;
+            const Tc2Dest* dst = walk.dest;
+            const int n_dest = dst->count;
             const uint32_t acc = lt & 1;
             if (!mbar_wait(&tmem_full[acc], (lt >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
@@ -336,8 +405,8 @@ ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         const size_t off = static_cast<size_t>(row) * ldc + col;
 #pragma unroll
                         for (int d = 0; d < kTc2MaxDest; ++d) {
-                            if (d >= dest.count) break;
-                            int32_t* out = dest.c[d] + off;
+                            if (d >= n_dest) break;
+                            int32_t* out = dst->c[d] + off;
                             if (c_vec_ok) {
                                 *reinterpret_cast<uint4*>(out) = v;
                             } else {

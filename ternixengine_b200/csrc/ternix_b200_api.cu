@@ -234,7 +234,7 @@ int launch_gemm_tc_t(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, in
 int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
                     long long ldc, int32_t* d_status, cudaStream_t st) {
     using G = tb200::Tc2Geom;
-    auto kern = tb200::ternary_gemm_tc2_kernel;
+    auto kern = tb200::ternary_gemm_tc2_kernel<false>;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [&] {
@@ -271,7 +271,9 @@ int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    TB_CUDA(cudaLaunchKernelEx(&cfg, kern, tmap_a, tmap_w, dest, M, K, N, ldc, c_vec_ok, d_status));
+    TB_CUDA(cudaLaunchKernelEx(&cfg, kern, tmap_a, tmap_w, dest, M, K, N, ldc, c_vec_ok,
+                               static_cast<const tb200::Tc2Problem*>(nullptr), static_cast<const tb200::Tc2Tile*>(nullptr),
+                               static_cast<const int*>(nullptr), d_status));
     return TERNIX_B200_OK;
 }
 
@@ -330,6 +332,16 @@ struct ternix_b200_group {
     const int* d_cta_first = nullptr;
     int grid = 0, mr = 0, words = 0, device = 0;
     size_t grouped = 0;
+    // prefill-regime members: one launch of the paired-CTA GEMM over all their tiles
+    void* d_tc_blob = nullptr;                  // [Tc2Problem[] | Tc2Tile[] | int pair_first[]]
+    const tb200::Tc2Problem* d_tc_probs = nullptr;
+    const tb200::Tc2Tile* d_tc_tiles = nullptr;
+    const int* d_tc_first = nullptr;
+    int tc_pairs = 0;
+    size_t tc_grouped = 0;
+    // members the grouped kernels could not take but that have peer destinations: copied after their launch
+    struct PeerCopy { ternix_b200_problem q; std::vector<int32_t*> peers; };
+    std::vector<PeerCopy> single_peers;
 };
 
 namespace {
@@ -346,6 +358,35 @@ int launch_gemv_group_t(const ternix_b200_group* g, int32_t* d_status, cudaStrea
     if (attr_err != cudaSuccess) return cuda_fail(attr_err);
     kern<<<g->grid, tb200::kGemvThreads, smem, st>>>(g->d_probs, g->d_items, g->d_cta_first, d_status);
     TB_CUDA(cudaGetLastError());
+    return TERNIX_B200_OK;
+}
+
+int launch_gemm_tc2_group(const ternix_b200_group* g, int32_t* d_status, cudaStream_t st) {
+    using G = tb200::Tc2Geom;
+    auto kern = tb200::ternary_gemm_tc2_kernel<true>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(G::kSmemBytes));
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * g->tc_pairs, 1, 1);
+    cfg.blockDim = dim3(tb200::kTc2Threads, 1, 1);
+    cfg.dynamicSmemBytes = G::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CUtensorMap unused{};
+    tb200::Tc2Dest no_dest{};
+    TB_CUDA(cudaLaunchKernelEx(&cfg, kern, unused, unused, no_dest, 0, 0, 0, 0LL, 0, g->d_tc_probs, g->d_tc_tiles,
+                               g->d_tc_first, d_status));
     return TERNIX_B200_OK;
 }
 
@@ -544,8 +585,10 @@ int ternix_b200_unpack_gathered(const int32_t* d_gathered, int32_t* dC, int M, i
     return TERNIX_B200_OK;
 }
 
-int ternix_b200_group_create(ternix_b200_group** out, const ternix_b200_problem* problems, int count) {
+int ternix_b200_group_create_ex(ternix_b200_group** out, const ternix_b200_problem* problems, int count,
+                                int32_t* const* peer_dC, int n_peers) {
     if (!out || count < 0 || (count > 0 && !problems)) return TERNIX_B200_ERR_INVALID_ARG;
+    if (n_peers < 0 || n_peers >= tb200::kTc2MaxDest || (n_peers > 0 && !peer_dC)) return TERNIX_B200_ERR_INVALID_ARG;
     *out = nullptr;
     for (int i = 0; i < count; ++i) {
         const ternix_b200_problem& q = problems[i];
@@ -561,6 +604,7 @@ int ternix_b200_group_create(ternix_b200_group** out, const ternix_b200_problem*
     g->words = 32;
     if (const char* env = std::getenv("TERNIX_B200_GROUP_WORDS")) g->words = std::atoi(env) == 16 ? 16 : 32;
     const int item_cols = g->words * 16;
+    std::vector<tb200::Tc2Problem> tc_probs;
     std::vector<tb200::GroupProblem> probs;
     struct HostItem { tb200::GroupItem item; long cost; };
     std::vector<HostItem> items;
@@ -568,6 +612,34 @@ int ternix_b200_group_create(ternix_b200_group** out, const ternix_b200_problem*
     for (int i = 0; i < count; ++i) {
         const ternix_b200_problem& q = problems[i];
         if (q.M == 0 || q.N == 0) continue;
+        if (q.K > 0 && gemm_tc2_ok(q.dA, q.dW, q.M, q.K, q.N)) {
+            tb200::Tc2Problem tp{};
+            int rc = make_tmap_2d(&tp.tmap_a, q.dA, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.M),
+                                  static_cast<uint64_t>(q.K), tb200::kTcBK, tb200::kTcBM, CU_TENSOR_MAP_SWIZZLE_128B);
+            if (!rc)
+                rc = make_tmap_2d(&tp.tmap_w, q.dW, static_cast<uint64_t>(q.N / 4), static_cast<uint64_t>(q.K),
+                                  static_cast<uint64_t>(q.N / 4), tb200::Tc2Geom::kWpRowBytes, tb200::kTcBK,
+                                  CU_TENSOR_MAP_SWIZZLE_NONE);
+            if (rc) { delete g; return rc; }
+            tp.dest.count = 1 + n_peers;
+            tp.dest.c[0] = q.dC;
+            tp.c_vec_ok = (q.ldc % 4 == 0) && aligned(q.dC, 16);
+            for (int j = 0; j < n_peers; ++j) {
+                int32_t* p = peer_dC[static_cast<size_t>(i) * n_peers + j];
+                if (!p) { delete g; return TERNIX_B200_ERR_INVALID_ARG; }
+                tp.dest.c[1 + j] = p;
+                tp.c_vec_ok = tp.c_vec_ok && aligned(p, 16);
+            }
+            tp.ldc = q.ldc; tp.M = q.M; tp.K = q.K; tp.N = q.N;
+            tc_probs.push_back(tp);
+            ++g->tc_grouped;
+            continue;
+        }
+        if (n_peers > 0) {           // not a paired-GEMM member: run it as usual, then copy its C to the peers
+            ternix_b200_group::PeerCopy pc{q, {}};
+            for (int j = 0; j < n_peers; ++j) pc.peers.push_back(peer_dC[static_cast<size_t>(i) * n_peers + j]);
+            g->single_peers.push_back(pc);
+        }
         if (!group_gemv_ok(q)) { g->singles.push_back(q); continue; }
         tb200::GroupProblem gp{};
         const int rc = make_tmap_2d(&gp.tmap_w, q.dW, static_cast<uint64_t>(q.N / 4), static_cast<uint64_t>(q.K),
@@ -628,9 +700,63 @@ int ternix_b200_group_create(ternix_b200_group** out, const ternix_b200_problem*
         g->d_cta_first = reinterpret_cast<const int*>(d + b_probs + b_items);
         g->grid = ctas;
     }
+    if (!tc_probs.empty()) {
+        // tiles of all prefill members, heaviest (deepest K) first, each to the least-loaded CTA pair
+        struct HostTile { tb200::Tc2Tile tile; long cost; };
+        std::vector<HostTile> tl;
+        for (int pi = 0; pi < static_cast<int>(tc_probs.size()); ++pi) {
+            const tb200::Tc2Problem& tp = tc_probs[pi];
+            const int m_tiles = (tp.M + 255) / 256, n_tiles = (tp.N + 255) / 256;
+            const long kb = (tp.K + tb200::kTcBK - 1) / tb200::kTcBK;
+            for (int n_t = 0; n_t < n_tiles; ++n_t)
+                for (int m_t = 0; m_t < m_tiles; ++m_t) tl.push_back({{pi, m_t, n_t, 0}, kb + 2});
+        }
+        const int pairs = static_cast<int>(std::min<size_t>(tl.size(), static_cast<size_t>(sm_count() / 2)));
+        std::stable_sort(tl.begin(), tl.end(), [](const HostTile& a, const HostTile& b) { return a.cost > b.cost; });
+        using Load = std::pair<long, int>;
+        std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
+        for (int c = 0; c < pairs; ++c) heap.push({0, c});
+        std::vector<std::vector<tb200::Tc2Tile>> per_pair(pairs);
+        for (const HostTile& h : tl) {
+            Load l = heap.top();
+            heap.pop();
+            per_pair[l.second].push_back(h.tile);
+            heap.push({l.first + h.cost, l.second});
+        }
+        std::vector<tb200::Tc2Tile> flat;
+        std::vector<int> first(pairs + 1, 0);
+        for (int c = 0; c < pairs; ++c) {
+            first[c] = static_cast<int>(flat.size());
+            flat.insert(flat.end(), per_pair[c].begin(), per_pair[c].end());
+        }
+        first[pairs] = static_cast<int>(flat.size());
+        const size_t b_probs = tc_probs.size() * sizeof(tb200::Tc2Problem);
+        const size_t b_tiles = (flat.size() * sizeof(tb200::Tc2Tile) + 63) & ~size_t(63);
+        const size_t b_first = first.size() * sizeof(int);
+        cudaError_t e = cudaMalloc(&g->d_tc_blob, b_probs + b_tiles + b_first);
+        if (e != cudaSuccess) { ternix_b200_group_destroy(g); return cuda_fail(e); }
+        uint8_t* d = static_cast<uint8_t*>(g->d_tc_blob);
+        if ((e = cudaMemcpy(d, tc_probs.data(), b_probs, cudaMemcpyHostToDevice)) != cudaSuccess ||
+            (e = cudaMemcpy(d + b_probs, flat.data(), flat.size() * sizeof(tb200::Tc2Tile), cudaMemcpyHostToDevice)) !=
+                cudaSuccess ||
+            (e = cudaMemcpy(d + b_probs + b_tiles, first.data(), b_first, cudaMemcpyHostToDevice)) != cudaSuccess) {
+            ternix_b200_group_destroy(g);
+            return cuda_fail(e);
+        }
+        g->d_tc_probs = reinterpret_cast<const tb200::Tc2Problem*>(d);
+        g->d_tc_tiles = reinterpret_cast<const tb200::Tc2Tile*>(d + b_probs);
+        g->d_tc_first = reinterpret_cast<const int*>(d + b_probs + b_tiles);
+        g->tc_pairs = pairs;
+    }
     *out = g;
     return TERNIX_B200_OK;
 }
+
+int ternix_b200_group_create(ternix_b200_group** out, const ternix_b200_problem* problems, int count) {
+    return ternix_b200_group_create_ex(out, problems, count, nullptr, 0);
+}
+
+
 
 int ternix_b200_group_run(const ternix_b200_group* g, int32_t* d_status, void* stream) {
     if (!g) return TERNIX_B200_ERR_INVALID_ARG;
@@ -648,22 +774,31 @@ int ternix_b200_group_run(const ternix_b200_group* g, int32_t* d_status, void* s
         }
         if (rc) return rc;
     }
+    if (g->tc_pairs > 0) {
+        const int rc = launch_gemm_tc2_group(g, d_status, st);
+        if (rc) return rc;
+    }
     for (const ternix_b200_problem& q : g->singles) {
         const int rc = ternix_b200_matmul_ex(q.dA, q.dW, q.dC, q.M, q.K, q.N, q.ldc, TERNIX_B200_KERNEL_AUTO, d_status,
                                              stream);
         if (rc) return rc;
     }
+    for (const auto& pc : g->single_peers)
+        for (int32_t* peer : pc.peers)
+            TB_CUDA(cudaMemcpy2DAsync(peer, static_cast<size_t>(pc.q.ldc) * 4, pc.q.dC, static_cast<size_t>(pc.q.ldc) * 4,
+                                      static_cast<size_t>(pc.q.N) * 4, pc.q.M, cudaMemcpyDefault, st));
     return TERNIX_B200_OK;
 }
 
 int ternix_b200_group_launches(const ternix_b200_group* g) {
     if (!g) return 0;
-    return (g->grid > 0 ? 1 : 0) + static_cast<int>(g->singles.size());
+    return (g->grid > 0 ? 1 : 0) + (g->tc_pairs > 0 ? 1 : 0) + static_cast<int>(g->singles.size());
 }
 
 void ternix_b200_group_destroy(ternix_b200_group* g) {
     if (!g) return;
     if (g->d_blob) cudaFree(g->d_blob);
+    if (g->d_tc_blob) cudaFree(g->d_tc_blob);
     delete g;
 }
 

@@ -334,3 +334,47 @@ def test_repeated_group_runs_are_bit_identical():
         group.run(status=status)
         bad += sum(int(bool((p[2] != e).any())) for p, e in zip(probs, expect))
     assert int(status.item()) == 0 and bad == 0
+
+
+def test_projection_group_prefill_members_share_one_launch():
+    """config 5 at M=256: the seven projections of a BitNet-shaped layer in one launch of the paired-CTA GEMM,
+    with a second destination per projection (as for a peer GPU) written by the same epilogue."""
+    import torch
+    probs, peers, expect = [], [], []
+    for i, (name, k, n) in enumerate(BITNET_LAYER):
+        a, wp = synth(256, k, n, 300 + i)
+        expect.append(oracle_lib.matmul(a, wp))
+        out = torch.full((256, n), -999, dtype=torch.int32, device="cuda")
+        twin = torch.full((256, n), -998, dtype=torch.int32, device="cuda")
+        probs.append((torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda(), out))
+        peers.append(twin)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    group = tb.ProjectionGroup(probs, peer_ptrs=[[t.data_ptr()] for t in peers])
+    assert group.launches == 1
+    for _ in range(3):
+        group.run(status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for (a, w, out), twin, e in zip(probs, peers, expect):
+        assert_same(out.cpu().numpy(), e, "grouped GEMM")
+        assert_same(twin.cpu().numpy(), e, "grouped GEMM, second destination")
+    group.close()
+
+
+def test_projection_group_mixed_regimes():
+    import torch
+    shapes = [(1, 2560, 6912), (300, 1040, 832), (512, 8192, 256), (3, 4099, 2052), (64, 256, 128), (130, 144, 320)]
+    probs, expect = [], []
+    for i, (m, k, n) in enumerate(shapes):
+        a, wp = synth(m, k, n, 40 + i)
+        expect.append(oracle_lib.matmul(a, wp))
+        probs.append((torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda(),
+                      torch.full((m, n), -999, dtype=torch.int32, device="cuda")))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    group = tb.ProjectionGroup(probs)
+    assert group.launches == 1 + 1 + 2          # decode kernel, paired GEMM, and the ragged and M=64 members
+    group.run(status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for (a, w, out), e in zip(probs, expect):
+        assert_same(out.cpu().numpy(), e, f"group member {tuple(a.shape)}")
