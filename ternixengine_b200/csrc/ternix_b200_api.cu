@@ -16,6 +16,7 @@
 
 #include "kernel_gemm_tc.cuh"
 #include "kernel_gemm_tc2.cuh"
+#include "kernel_gemm_tc2w.cuh"
 #include "kernel_gemv.cuh"
 #include "kernel_gemv_group.cuh"
 #include "kernel_generic.cuh"
@@ -230,16 +231,22 @@ int launch_gemm_tc_t(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, in
     return TERNIX_B200_OK;
 }
 
-// Paired-CTA kernel: clusters of two CTAs, one 256 x 256 tile per cluster at a time.
-int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
-                    long long ldc, int32_t* d_status, cudaStream_t st) {
-    using G = tb200::Tc2Geom;
-    auto kern = tb200::ternary_gemm_tc2_kernel<false>;
+// Paired-CTA kernels: clusters of two CTAs, one 256 x 256 (or, wide, 256 x 512) tile per cluster at a time.
+template <bool kWide>
+int launch_gemm_tc2_t(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
+                      long long ldc, int32_t* d_status, cudaStream_t st) {
+    constexpr size_t smem = kWide ? tb200::TcwGeom::kSmemBytes : tb200::Tc2Geom::kSmemBytes;
+    constexpr int tile_n = kWide ? tb200::kTcwTileN : tb200::kTc2TileN;
+    constexpr int wp_row_bytes = kWide ? tb200::TcwGeom::kWpRowBytes : tb200::Tc2Geom::kWpRowBytes;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(G::kSmemBytes));
+        if constexpr (kWide)
+            attr_err = cudaFuncSetAttribute(tb200::ternary_gemm_tc2w_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            static_cast<int>(smem));
+        else
+            attr_err = cudaFuncSetAttribute(tb200::ternary_gemm_tc2_kernel<false>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     });
     if (attr_err != cudaSuccess) return cuda_fail(attr_err);
     CUtensorMap tmap_a, tmap_w;
@@ -247,9 +254,9 @@ int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list
                           tb200::kTcBK, tb200::kTcBM, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     rc = make_tmap_2d(&tmap_w, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K),
-                      static_cast<uint64_t>(N / 4), G::kWpRowBytes, tb200::kTcBK, CU_TENSOR_MAP_SWIZZLE_NONE);
+                      static_cast<uint64_t>(N / 4), wp_row_bytes, tb200::kTcBK, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
-    const long tiles = static_cast<long>((M + 255) / 256) * ((N + 255) / 256);
+    const long tiles = static_cast<long>((M + 255) / 256) * ((N + tile_n - 1) / tile_n);
     const long max_pairs = sm_count() / 2;
     const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
     tb200::Tc2Dest dest{};
@@ -262,7 +269,7 @@ int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     cfg.blockDim = dim3(tb200::kTc2Threads, 1, 1);
-    cfg.dynamicSmemBytes = G::kSmemBytes;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -271,10 +278,24 @@ int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    TB_CUDA(cudaLaunchKernelEx(&cfg, kern, tmap_a, tmap_w, dest, M, K, N, ldc, c_vec_ok,
-                               static_cast<const tb200::Tc2Problem*>(nullptr), static_cast<const tb200::Tc2Tile*>(nullptr),
-                               static_cast<const int*>(nullptr), d_status));
+    if constexpr (kWide) {
+        TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc2w_kernel, tmap_a, tmap_w, dest, M, K, N, ldc, c_vec_ok,
+                                   d_status));
+    } else {
+        TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc2_kernel<false>, tmap_a, tmap_w, dest, M, K, N, ldc,
+                                   c_vec_ok, static_cast<const tb200::Tc2Problem*>(nullptr),
+                                   static_cast<const tb200::Tc2Tile*>(nullptr), static_cast<const int*>(nullptr), d_status));
+    }
     return TERNIX_B200_OK;
+}
+
+// Wide tiles when there are at least two 512-column tiles per pair row to amortise them; TERNIX_B200_TC_WIDE=0|1 forces.
+int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
+                    long long ldc, int32_t* d_status, cudaStream_t st) {
+    bool wide = N >= 1024 && K >= 1024;
+    if (const char* env = std::getenv("TERNIX_B200_TC_WIDE")) wide = std::atoi(env) != 0;
+    if (wide) return launch_gemm_tc2_t<true>(dA, dW, dC_list, n_dest, M, K, N, ldc, d_status, st);
+    return launch_gemm_tc2_t<false>(dA, dW, dC_list, n_dest, M, K, N, ldc, d_status, st);
 }
 
 int launch_gemm_tc(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,

@@ -104,9 +104,11 @@ def test_config2_skinny_gemm():
         assert_same(device_matmul(a, wp, kern), expect, f"config2 [{kern}]")
 
 
-@pytest.mark.parametrize("bn", ["128", "256", "2"])
+@pytest.mark.parametrize("bn", ["128", "256", "2", "2w"])
 def test_gemm_tc_tile_widths_and_ragged_edges(bn, monkeypatch):
-    monkeypatch.setenv("TERNIX_B200_TC_BN", bn)
+    # 128 / 256: single-CTA tiles; 2: paired CTAs, 256 x 256; 2w: paired CTAs, 256 x 512
+    monkeypatch.setenv("TERNIX_B200_TC_BN", bn[0] if bn.startswith("2") else bn)
+    monkeypatch.setenv("TERNIX_B200_TC_WIDE", "1" if bn == "2w" else "0")
     for (m, k, n) in [(128, 128, 256), (128, 512, 128), (256, 1024, 512), (300, 2064, 832), (1, 16, 64),
                       (129, 144, 320), (640, 4096, 1024), (1000, 272, 1984)]:
         a, wp = synth(m, k, n, m + k + n)
