@@ -308,7 +308,7 @@ def run_b200(args):
                           "columns_rank0": shard.n_cols},
         "roofline": {"bound": "tensor", "achieved": local_ops / (kernel_ms * 1e-3) / 1e12, "peak": int8_peak,
                      "unit": "TOPS", "frac": local_ops / (kernel_ms * 1e-3) / 1e12 / int8_peak, "traffic": traffic,
-                     "kernel": "ternary_gemm_tc2_kernel", "peak_source": f"2 x bf16 burst of {peaks['source']} peaks "
+                     "kernel": "ternary_gemm_tc2w_kernel", "peak_source": f"2 x bf16 burst of {peaks['source']} peaks "
                      "(dense int8 proxy)", "frac_of_nominal_4500": local_ops / (kernel_ms * 1e-3) / 1e12 / 4500.0},
         "nccl_gather_baseline": None if nccl_ms is None else {
             "ms_per_step": nccl_ms, "tops": ops / (nccl_ms * 1e-3) / 1e12,
