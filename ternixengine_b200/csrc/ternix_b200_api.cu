@@ -289,10 +289,12 @@ int launch_gemm_tc2_t(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_li
     return TERNIX_B200_OK;
 }
 
-// Wide tiles when there are at least two 512-column tiles per pair row to amortise them; TERNIX_B200_TC_WIDE=0|1 forces.
+// Wide tiles for large single-destination products.  With peer destinations the 256-wide kernel is used: its
+// accumulator is double-buffered, so the slower NVLink stores of the epilogue hide under the next tile's main
+// loop, which the single-buffered wide kernel cannot do.  TERNIX_B200_TC_WIDE=0|1 forces the choice.
 int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
                     long long ldc, int32_t* d_status, cudaStream_t st) {
-    bool wide = N >= 1024 && K >= 1024;
+    bool wide = n_dest == 1 && N >= 1024 && K >= 1024;
     if (const char* env = std::getenv("TERNIX_B200_TC_WIDE")) wide = std::atoi(env) != 0;
     if (wide) return launch_gemm_tc2_t<true>(dA, dW, dC_list, n_dest, M, K, N, ldc, d_status, st);
     return launch_gemm_tc2_t<false>(dA, dW, dC_list, n_dest, M, K, N, ldc, d_status, st);
