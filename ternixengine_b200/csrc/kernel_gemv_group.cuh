@@ -33,7 +33,11 @@ namespace tb200 {
 
 constexpr int kGroupMaxK = 8192;                // activation bytes staged per row
 constexpr int kGroupStageBytes = 8192;          // one TMA box
-constexpr int kGroupStages = 8;
+// Ring depth and resident CTAs per SM by row-group size.  The kernel is bound by instruction issue, so
+// more resident warps beat a deeper ring: M = 1 runs 4 CTAs per SM with 4 stages each (measured +5 % over
+// 2 CTAs x 8 stages), M = 2 runs 3, and 4-row groups (144 registers per thread) run 1 CTA with 8 stages.
+constexpr int group_stages(int mr) { return mr <= 2 ? 4 : 8; }
+constexpr int group_ctas_per_sm(int mr) { return mr <= 1 ? 4 : mr == 2 ? 3 : 1; }
 constexpr int group_stage_rows(int words) { return kGroupStageBytes / (words * 4); }   // 128 or 64 k-rows
 
 struct alignas(64) GroupProblem {
@@ -49,6 +53,7 @@ struct GroupItem {
 
 template <int MR, int WORDS>
 constexpr size_t gemv_group_smem_bytes() {
+    constexpr int kGroupStages = group_stages(MR);
     return 128 + size_t(kGroupStages) * kGroupStageBytes + 2 * size_t(MR) * kGroupMaxK +
            2 * size_t(MR) * 16 * (WORDS + 1) * 4 + (2 * kGroupStages + 4) * 8 + 2 * MR * 4 + 16;
 }
@@ -71,6 +76,7 @@ __global__ void __launch_bounds__(kGemvThreads)
 ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupItem* __restrict__ items,
                           const int* __restrict__ cta_first, int32_t* __restrict__ status) {
     constexpr int kGroupStageRows = kGroupStageBytes / (WORDS * 4);
+    constexpr int kGroupStages = MR <= 2 ? 4 : 8;               // = group_stages(MR)
     constexpr int kHalves = 32 / WORDS;                 // k-groups a warp covers per load
     constexpr int kPartInts = MR * 16 * (WORDS + 1);
     extern __shared__ uint8_t smem_raw[];

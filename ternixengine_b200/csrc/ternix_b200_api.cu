@@ -684,7 +684,7 @@ int ternix_b200_group_create_ex(ternix_b200_group** out, const ternix_b200_probl
     }
     if (!items.empty()) {
         // longest-processing-time-first: heaviest items first, each to the least-loaded CTA
-        const int per_sm = g->mr <= 2 ? 2 : 1;
+        const int per_sm = tb200::group_ctas_per_sm(g->mr);
         const int ctas = static_cast<int>(std::min<size_t>(items.size(), static_cast<size_t>(sm_count()) * per_sm));
         std::stable_sort(items.begin(), items.end(), [](const HostItem& a, const HostItem& b) { return a.cost > b.cost; });
         using Load = std::pair<long, int>;
@@ -923,7 +923,7 @@ int ternix_b200_gemv_batch_noalloc(const ternix_b200_problem* problems, int coun
         if (x.chunk != y.chunk) return x.chunk < y.chunk;
         return x.row0 < y.row0;
     });
-    const int per_sm = mr <= 2 ? 2 : 1;
+    const int per_sm = tb200::group_ctas_per_sm(mr);
     int ctas = std::min(n_items, sm_count() * per_sm);
     ctas = std::min(ctas, kNoAllocMaxCtas);
     for (int c = 0; c <= ctas; ++c) h.first[c] = 0;
