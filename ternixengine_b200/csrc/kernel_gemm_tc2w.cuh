@@ -10,6 +10,13 @@
 // the B operand of MMA h).  The accumulator is 512 TMEM columns per CTA, single-buffered: the epilogue of
 // a tile runs before the next tile's first MMA (about 7 % of a tile's time at K = 8192).
 //
+// Tail.  Tiles are dealt to the pairs round-robin, so a last, partial round would keep a few pairs busy for
+// a whole tile while the rest idle (896 tiles on 74 pairs: 12.1 rounds).  When the host asks for it, the
+// tiles of that partial round are split along K into slices, one slice per pair; every slice adds its
+// partial result into C with red.global.add.s32 (C of those tiles is zeroed by the host beforehand).
+// Integer addition is associative and each partial accumulator is an exact multiple of 64, so the result is
+// bit-identical.
+//
 // Everything else -- decode, operand layouts, pair signalling, coalesced multi-destination epilogue,
 // bounded waits -- is as in ternary_gemm_tc2_kernel.  Single product only (no problem-group tables).
 #pragma once
@@ -46,7 +53,7 @@ struct TcwGeom {
 __global__ void __launch_bounds__(kTc2Threads, 1)
 ternary_gemm_tc2w_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                          const __grid_constant__ Tc2Dest dest, int M, int K, int N, long long ldc, int c_vec_ok,
-                         int32_t* __restrict__ status) {
+                         int tail_slices, int32_t* __restrict__ status) {
     using G = TcwGeom;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -73,6 +80,22 @@ ternary_gemm_tc2w_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const int n_tiles = (N + kTcwTileN - 1) / kTcwTileN;
     const int num_tiles = m_tiles * n_tiles;
     const int k_blocks = (K + kTcBK - 1) / kTcBK;
+    // Work items of this pair: its whole tiles, then (tail_slices > 0) one K-slice of a tile of the last round.
+    const int whole_tiles = tail_slices > 0 ? (num_tiles / num_pairs) * num_pairs : num_tiles;
+    const int slice_kb = tail_slices > 0 ? (k_blocks + tail_slices - 1) / tail_slices : 0;
+    const bool has_slice = tail_slices > 0 && pair < (num_tiles - whole_tiles) * tail_slices &&
+                           (pair % tail_slices) * slice_kb < k_blocks;
+    const int n_whole = pair < whole_tiles ? (whole_tiles - pair + num_pairs - 1) / num_pairs : 0;
+    const int n_items = n_whole + (has_slice ? 1 : 0);
+    // item i -> tile and k-block range
+    auto item = [&](int i, int& tile, int& kb0, int& kb1) {
+        if (i < n_whole) { tile = pair + i * num_pairs; kb0 = 0; kb1 = k_blocks; }
+        else {
+            tile = whole_tiles + pair / tail_slices;
+            kb0 = (pair % tail_slices) * slice_kb;
+            kb1 = kb0 + slice_kb < k_blocks ? kb0 + slice_kb : k_blocks;
+        }
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTcwStagesA; ++s) {
@@ -105,11 +128,13 @@ ternary_gemm_tc2w_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             tma_prefetch_desc(&tmap_w);
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+            for (int i = 0; ok && i < n_items; ++i) {
+                int tile, kb0, kb1;
+                item(i, tile, kb0, kb1);
                 const int m_t = tile % m_tiles, n_t = tile / m_tiles;
                 const int row0 = m_t * 2 * kTcBM + rank * kTcBM;
                 const int wp_x = n_t * (kTcwTileN / 4) + rank * G::kWpRowBytes;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % kTcwStagesA;
                     if (!mbar_wait(&empty_a[s], ((it / kTcwStagesA) & 1) ^ 1, abort_flag)) { ok = false; break; }
                     mbar_arrive_expect_tx(&full_a[s], G::kABytes + G::kWpBytes);
@@ -127,10 +152,12 @@ ternary_gemm_tc2w_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         if (leader && lane == 0) {
             uint32_t it = 0, lt = 0;
             bool ok = true;
-            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++lt) {
+            for (int i = 0; ok && i < n_items; ++i, ++lt) {
+                int tile, kb0, kb1;
+                item(i, tile, kb0, kb1);
                 if (!mbar_wait(tmem_empty, (lt & 1) ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t sa = it % kTcwStagesA, sb = it % kTcwStagesB;
                     if (!mbar_wait(&full_a[sa], (it / kTcwStagesA) & 1, abort_flag) ||
                         !mbar_wait(&full_b[sb], (it / kTcwStagesB) & 1, abort_flag)) { ok = false; break; }
@@ -143,7 +170,7 @@ ternary_gemm_tc2w_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
                             const uint64_t db = umma_desc_sw128(b_addr + h * G::kGroupBytes + k4 * 4096, G::kGroupBytes, 1024);
-                            tc_mma_i8_pair(tmem_base + h * 256, da, db, G::kIdesc, (kb | k4) != 0 ? 1u : 0u);
+                            tc_mma_i8_pair(tmem_base + h * 256, da, db, G::kIdesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
                         }
                     }
                     tc_commit_pair_both(&empty_a[sa]);
@@ -178,8 +205,10 @@ ternary_gemm_tc2w_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const uint32_t wp_sa = smem_u32(sWp), b_sa = smem_u32(sB);
         uint32_t it = 0;
         bool ok = true;
-        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int i = 0; ok && i < n_items; ++i) {
+            int tile, kb0, kb1;
+            item(i, tile, kb0, kb1);
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const uint32_t sa = it % kTcwStagesA, sb = it % kTcwStagesB;
                 // every expander warp observes every phase of full_a (parity waits must not skip phases)
                 if (!mbar_wait(&full_a[sa], (it / kTcwStagesA) & 1, abort_flag)) { ok = false; break; }
@@ -222,7 +251,10 @@ ternary_gemm_tc2w_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const int n_dest = dest.count;
         uint32_t lt = 0;
         bool ok = true;
-        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++lt) {
+        for (int i = 0; ok && i < n_items; ++i, ++lt) {
+            int tile, kb0, kb1;
+            item(i, tile, kb0, kb1);
+            const bool add_into_c = i >= n_whole;                      // a K-slice: partial result, C was zeroed
             const int m_t = tile % m_tiles, n_t = tile / m_tiles;
             if (!mbar_wait(tmem_full, lt & 1, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
@@ -257,7 +289,13 @@ ternary_gemm_tc2w_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     const int rr = 2 * i + (lane >> 4);
                     const uint4 v = lds_v4(stage_sa + rr * 256 + (((lane & 15) ^ (rr & 7)) << 4));
                     const int row = row_base + rr;
-                    if (row < M && col < N) {
+                    if (row < M && col < N && add_into_c) {
+                        int32_t* out = dest.c[0] + static_cast<size_t>(row) * ldc + col;
+                        asm volatile("red.global.add.s32 [%0], %1;" ::"l"(out), "r"(v.x) : "memory");
+                        asm volatile("red.global.add.s32 [%0], %1;" ::"l"(out + 1), "r"(v.y) : "memory");
+                        asm volatile("red.global.add.s32 [%0], %1;" ::"l"(out + 2), "r"(v.z) : "memory");
+                        asm volatile("red.global.add.s32 [%0], %1;" ::"l"(out + 3), "r"(v.w) : "memory");
+                    } else if (row < M && col < N) {
                         const size_t off = static_cast<size_t>(row) * ldc + col;
 #pragma unroll
                         for (int d = 0; d < kTc2MaxDest; ++d) {

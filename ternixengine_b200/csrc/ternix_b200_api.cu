@@ -279,8 +279,29 @@ int launch_gemm_tc2_t(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_li
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if constexpr (kWide) {
+        // K-sliced tail: when the last round of tiles would occupy at most half of the pairs, split each of its
+        // tiles along K over the pairs (results are added into C, which is zeroed here for those tiles).
+        int tail_slices = 0;
+        const int m_tiles = (M + 255) / 256;
+        const int rest = static_cast<int>(tiles % pairs);
+        const int k_blocks = (K + tb200::kTcBK - 1) / tb200::kTcBK;
+        bool want_tail = n_dest == 1 && tiles > pairs && rest > 0 && rest * 2 <= pairs && k_blocks >= 16;
+        if (const char* env = std::getenv("TERNIX_B200_TC_TAIL")) want_tail = want_tail && std::atoi(env) != 0;
+        if (want_tail) {
+            tail_slices = std::min(pairs / rest, k_blocks / 4);
+            const long first = tiles - rest;
+            for (long tile = first; tile < tiles;) {               // zero C of the tail tiles, one memset per tile column
+                const long n_t = tile / m_tiles, m0 = tile % m_tiles;
+                long m1 = m0;
+                while (tile < tiles && tile / m_tiles == n_t) { m1 = tile % m_tiles; ++tile; }
+                const long r0 = m0 * 256, r1 = std::min<long>(M, (m1 + 1) * 256);
+                const long c0 = n_t * tile_n, c1 = std::min<long>(N, c0 + tile_n);
+                TB_CUDA(cudaMemset2DAsync(dC_list[0] + r0 * ldc + c0, static_cast<size_t>(ldc) * 4, 0,
+                                          static_cast<size_t>(c1 - c0) * 4, static_cast<size_t>(r1 - r0), st));
+            }
+        }
         TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc2w_kernel, tmap_a, tmap_w, dest, M, K, N, ldc, c_vec_ok,
-                                   d_status));
+                                   tail_slices, d_status));
     } else {
         TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc2_kernel<false>, tmap_a, tmap_w, dest, M, K, N, ldc,
                                    c_vec_ok, static_cast<const tb200::Tc2Problem*>(nullptr),

@@ -380,3 +380,22 @@ def test_projection_group_mixed_regimes():
     assert int(status.item()) == 0
     for (a, w, out), e in zip(probs, expect):
         assert_same(out.cpu().numpy(), e, f"group member {tuple(a.shape)}")
+
+
+@pytest.mark.parametrize("shape", [(4096, 2048, 5120), (2304, 2048, 9216), (4000, 4096, 5056)])
+def test_wide_kernel_k_sliced_tail(shape):
+    """Shapes whose last round of 256x512 tiles is split along K and added into a zeroed C: still bit-exact,
+    launch after launch, including ragged M and N edges inside the tail."""
+    import torch
+    m, k, n = shape
+    a, wp = synth(m, k, n, m + n)
+    expect = torch.from_numpy(oracle_lib.matmul(a, wp)).cuda()
+    da, dw = torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    wide = torch.full((m, n + 8), -3, dtype=torch.int32, device="cuda")
+    for i in range(20):
+        wide.fill_(-3)
+        tb.matmul(da, dw, out=wide[:, :n], kernel="gemm_tc", status=status)
+        assert bool((wide[:, :n] == expect).all()), f"launch {i} differs"
+        assert bool((wide[:, n:] == -3).all())
+    assert int(status.item()) == 0
