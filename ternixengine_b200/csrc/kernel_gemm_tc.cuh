@@ -64,7 +64,7 @@ struct TcGeom {
 template <int BN>
 __global__ void __launch_bounds__(kTcThreads, 1)
 ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                       int32_t* __restrict__ C, int M, int K, int N, long long ldc, int c_vec_ok,
+                       int32_t* __restrict__ C, int M, int K, int N, long long ldc, int c_vec_ok, int k_slices,
                        int32_t* __restrict__ status) {
     using G = TcGeom<BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -86,8 +86,13 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tiles = (M + kTcBM - 1) / kTcBM;
     const int n_tiles = (N + BN - 1) / BN;
-    const int num_tiles = m_tiles * n_tiles;
     const int k_blocks = (K + kTcBK - 1) / kTcBK;
+    // With few output tiles (skinny M) every tile is split along K into k_slices work items so that all SMs
+    // stream weights; the items of a tile add their partial results into C (zeroed by the host): integer
+    // adds are associative and every partial accumulator is an exact multiple of 64, so C stays bit-exact.
+    const int slice_kb = (k_blocks + k_slices - 1) / k_slices;
+    const int num_tiles = m_tiles * n_tiles * k_slices;              // work items
+    const bool add_into_c = k_slices > 1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTcStagesA; ++s) {
@@ -123,8 +128,10 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                const int m_t = tile % m_tiles, n_t = tile / m_tiles;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int slice = tile % k_slices, t2 = tile / k_slices;
+                const int m_t = t2 % m_tiles, n_t = t2 / m_tiles;
+                const int kb0 = slice * slice_kb, kb1 = kb0 + slice_kb < k_blocks ? kb0 + slice_kb : k_blocks;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % kTcStagesA;
                     if (!mbar_wait(&empty_a[s], ((it / kTcStagesA) & 1) ^ 1, abort_flag)) { ok = false; break; }
                     mbar_arrive_expect_tx(&full_a[s], G::kABytes + G::kWpBytes);
@@ -149,7 +156,9 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 if (!mbar_wait(&tmem_empty[acc], ((lt >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int slice = tile % k_slices;
+                const int kb0 = slice * slice_kb, kb1 = kb0 + slice_kb < k_blocks ? kb0 + slice_kb : k_blocks;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const uint32_t sa = it % kTcStagesA, sb = it % kTcStagesB;
                     if (!mbar_wait(&full_a[sa], (it / kTcStagesA) & 1, abort_flag) ||
                         !mbar_wait(&full_b[sb], (it / kTcStagesB) & 1, abort_flag)) { ok = false; break; }
@@ -163,7 +172,7 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                         // B: N-major, 128-column groups kGroupBytes apart (leading), 8-k-row groups
                         //    1024 B apart (stride); +32 k-rows = 4096 B per step.
                         const uint64_t db = umma_desc_sw128(b_addr + k4 * 4096, G::kGroupBytes, 1024);
-                        tc_mma_i8(d_tmem, da, db, G::kIdesc, (kb | k4) != 0 ? 1u : 0u);
+                        tc_mma_i8(d_tmem, da, db, G::kIdesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
                     }
                     tc_commit(&empty_a[sa]);
                     tc_commit(&empty_b[sb]);
@@ -202,7 +211,9 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         uint32_t it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            const int slice = tile % k_slices;
+            const int kb0 = slice * slice_kb, kb1 = kb0 + slice_kb < k_blocks ? kb0 + slice_kb : k_blocks;
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const uint32_t sa = it % kTcStagesA, sb = it % kTcStagesB;
                 if (!mbar_wait(&full_a[sa], (it / kTcStagesA) & 1, abort_flag) ||
                     !mbar_wait(&empty_b[sb], ((it / kTcStagesB) & 1) ^ 1, abort_flag)) { ok = false; break; }
@@ -238,7 +249,8 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         uint32_t lt = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++lt) {
-            const int m_t = tile % m_tiles, n_t = tile / m_tiles;
+            const int t2 = tile / k_slices;
+            const int m_t = t2 % m_tiles, n_t = t2 / m_tiles;
             const uint32_t acc = lt & 1;
             if (!mbar_wait(&tmem_full[acc], (lt >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
@@ -257,7 +269,11 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
                             o[h * 16 + 4 * (i & 3) + (i >> 2)] = static_cast<int32_t>(r[h * 16 + i]) >> 6;
-                    if (c_vec_ok) {
+                    if (add_into_c) {
+#pragma unroll
+                        for (int v = 0; v < 32; ++v)
+                            asm volatile("red.global.add.s32 [%0], %1;" ::"l"(crow + c0 + v), "r"(o[v]) : "memory");
+                    } else if (c_vec_ok) {
 #pragma unroll
                         for (int v = 0; v < 8; ++v)
                             *reinterpret_cast<int4*>(crow + c0 + 4 * v) =

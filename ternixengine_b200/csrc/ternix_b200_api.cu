@@ -83,6 +83,30 @@ int sm_count() {
     return n;
 }
 
+// Stream-ordered memory pool of the host-pointer entry point, one per device, created on first use.
+int host_call_pool(cudaMemPool_t* out) {
+    static std::mutex mu;
+    static cudaMemPool_t pools[64] = {};
+    int dev = 0;
+    TB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return TERNIX_B200_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!pools[dev]) {
+        cudaMemPoolProps props{};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = dev;
+        cudaMemPool_t p = nullptr;
+        TB_CUDA(cudaMemPoolCreate(&p, &props));
+        unsigned long long keep = ~0ull;          // keep freed pages for the next call
+        TB_CUDA(cudaMemPoolSetAttribute(p, cudaMemPoolAttrReleaseThreshold, &keep));
+        pools[dev] = p;
+    }
+    *out = pools[dev];
+    return TERNIX_B200_OK;
+}
+
 // ---------------------------------------------------------------- kernel eligibility
 bool gemv_ok(const void* dW, int M, int K, int N) {
     return M <= 16 && (N % 64) == 0 && aligned(dW, 16) && K <= kMaxScaledK && K <= 8 * (tb200::kGemvMaxASlice / 4);
@@ -224,9 +248,17 @@ int launch_gemm_tc_t(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, in
                       static_cast<uint64_t>(N / 4), G::kWpRowBytes, tb200::kTcBK, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
     const long tiles = static_cast<long>((M + tb200::kTcBM - 1) / tb200::kTcBM) * ((N + BN - 1) / BN);
-    const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+    // Skinny problems: split K so that every SM gets a work item; partial results are added into a zeroed C.
+    int k_slices = 1;
+    const int k_blocks = (K + tb200::kTcBK - 1) / tb200::kTcBK;
+    if (tiles * 2 <= sm_count() && k_blocks >= 8) k_slices = static_cast<int>(std::min<long>(sm_count() / tiles, k_blocks / 4));
+    if (const char* env = std::getenv("TERNIX_B200_TC_KSPLIT")) { if (std::atoi(env) == 0) k_slices = 1; }
+    if (k_slices > 1)
+        TB_CUDA(cudaMemset2DAsync(dC, static_cast<size_t>(ldc) * 4, 0, static_cast<size_t>(N) * 4, M, st));
+    const long items = tiles * k_slices;
+    const int grid = static_cast<int>(items < sm_count() ? items : sm_count());
     const int c_vec_ok = (ldc % 4 == 0) && aligned(dC, 16);
-    kern<<<grid, tb200::kTcThreads, G::kSmemBytes, st>>>(tmap_a, tmap_w, dC, M, K, N, ldc, c_vec_ok, d_status);
+    kern<<<grid, tb200::kTcThreads, G::kSmemBytes, st>>>(tmap_a, tmap_w, dC, M, K, N, ldc, c_vec_ok, k_slices, d_status);
     TB_CUDA(cudaGetLastError());
     return TERNIX_B200_OK;
 }
@@ -331,7 +363,12 @@ int launch_gemm_tc(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int 
     if (bn != 128 && bn != 256) {
         const long m_tiles = (M + tb200::kTcBM - 1) / tb200::kTcBM;
         const long tiles256 = m_tiles * ((N + 255) / 256);
-        bn = (N % 256 == 0 || N > 256) && tiles256 >= sm_count() ? 256 : 128;
+        const long tiles128 = m_tiles * ((N + 127) / 128);
+        // 256-wide tiles when they fill the machine, or when 128-wide tiles neither fill it nor leave room for a
+        // K-split while 256-wide tiles do (skinny M: 43 tiles x 3 K-slices beat 86 unsplit tiles)
+        const bool fill256 = tiles256 >= sm_count();
+        const bool split256 = tiles128 * 2 > sm_count() && tiles256 * 2 <= sm_count() && K >= 1024;
+        bn = (N % 256 == 0 || N > 256) && (fill256 || split256) ? 256 : 128;
     }
     if (bn == 256) return launch_gemm_tc_t<256>(dA, dW, dC, M, K, N, ldc, d_status, st);
     return launch_gemm_tc_t<128>(dA, dW, dC, M, K, N, ldc, d_status, st);
@@ -570,11 +607,16 @@ int ternix_b200_matmul_host(const int8_t* A, const uint8_t* Wp, int32_t* C, int 
     int rc = TERNIX_B200_OK;
     cudaError_t e = cudaSuccess;
     int32_t h_status = 0;
-    // One allocation for everything: [status | A | W | C], each part 256-byte aligned.
+    // One allocation for everything: [status | A | W | C], each part 256-byte aligned.  It comes from a
+    // stream-ordered pool owned by this library and goes back to it before the call returns; the pool keeps
+    // the pages, so repeated calls do not pay the driver's allocation cost again.
     auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
     uint8_t* blob = nullptr;
     const size_t total = 256 + up(a_bytes) + up(w_bytes) + up(c_bytes);
-    if ((e = cudaMalloc(&blob, total)) != cudaSuccess) return cuda_fail(e);
+    cudaMemPool_t pool = nullptr;
+    rc = host_call_pool(&pool);
+    if (rc) return rc;
+    if ((e = cudaMallocFromPoolAsync(reinterpret_cast<void**>(&blob), total, pool, 0)) != cudaSuccess) return cuda_fail(e);
     dS = reinterpret_cast<int32_t*>(blob);
     dA = reinterpret_cast<int8_t*>(blob + 256);
     dW = reinterpret_cast<uint8_t*>(blob + 256 + up(a_bytes));
@@ -589,9 +631,10 @@ int ternix_b200_matmul_host(const int8_t* A, const uint8_t* Wp, int32_t* C, int 
         if (rc) break;
         if ((e = cudaMemcpyAsync(C, dC, c_bytes, cudaMemcpyDeviceToHost, 0)) != cudaSuccess) break;
         if ((e = cudaMemcpyAsync(&h_status, dS, 4, cudaMemcpyDeviceToHost, 0)) != cudaSuccess) break;
-        e = cudaStreamSynchronize(0);
     } while (false);
-    cudaFree(blob);
+    cudaFreeAsync(blob, 0);
+    const cudaError_t e_sync = cudaStreamSynchronize(0);
+    if (e == cudaSuccess) e = e_sync;
     if (e != cudaSuccess) return cuda_fail(e);
     if (rc) return rc;
     return h_status ? h_status : TERNIX_B200_OK;

@@ -399,3 +399,30 @@ def test_wide_kernel_k_sliced_tail(shape):
         assert bool((wide[:, :n] == expect).all()), f"launch {i} differs"
         assert bool((wide[:, n:] == -3).all())
     assert int(status.item()) == 0
+
+
+def test_group_run_inside_a_cuda_graph():
+    """A projection set captured once and replayed as a CUDA graph (run() only launches)."""
+    import torch
+    probs, expect = [], []
+    for i, (name, k, n) in enumerate(BITNET_LAYER):
+        for m in (1, 256):
+            a, wp = synth(m, k, n, 600 + 2 * i + m)
+            expect.append(oracle_lib.matmul(a, wp))
+            probs.append((torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda(),
+                          torch.full((m, n), -999, dtype=torch.int32, device="cuda")))
+    group = tb.ProjectionGroup(probs)
+    assert group.launches == 2
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        group.run(stream=s)                     # warm-up outside capture (function attributes, first launches)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            group.run(stream=s)
+    for p in probs:
+        p[2].fill_(-1)
+    g.replay()
+    torch.cuda.synchronize()
+    for (a, w, out), e in zip(probs, expect):
+        assert_same(out.cpu().numpy(), e, "graph replay")
