@@ -113,6 +113,16 @@ int ternix_b200_group_create(ternix_b200_group **out, const ternix_b200_problem 
  * from its epilogue; other members are computed as usual and copied. */
 int ternix_b200_group_create_ex(ternix_b200_group **out, const ternix_b200_problem *problems, int count,
                                 int32_t *const *peer_dC, int n_peers);
+/* Prepacked weights for the decode regime (the reference keeps a placeholder for an offline layout,
+ * interleave_weights_offline, src/bitpack.cpp:29-33, README.md:205; this is a real one, kept beside -- not instead
+ * of -- the packed interchange format).  ternix_b200_prepack_k4 rewrites a packed K x (N/4) matrix on the device so
+ * that the four bytes a decode step needs from four consecutive k-rows sit in one 32-bit word:
+ * word [k/4][b] = { W[4r][b], W[4r+1][b], W[4r+2][b], W[4r+3][b] }, zero beyond K; ceil(K/4) * N bytes.  A group
+ * created with ternix_b200_group_create_prepacked takes problems whose dW point at such matrices (decode-regime
+ * members only, same limits as above) and skips the in-kernel byte transpose.  Results are identical. */
+size_t ternix_b200_prepack_k4_bytes(int K, int N);
+int ternix_b200_prepack_k4(const uint8_t *dW, uint8_t *dW_prepacked, int K, int N, void *stream);
+int ternix_b200_group_create_prepacked(ternix_b200_group **out, const ternix_b200_problem *problems, int count);
 int ternix_b200_group_run(const ternix_b200_group *group, int32_t *d_status, void *stream);
 /* Kernel launches one run() makes (1 for the persistent kernel + 1 per problem it could not take). */
 int ternix_b200_group_launches(const ternix_b200_group *group);

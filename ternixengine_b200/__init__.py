@@ -45,7 +45,8 @@ EXPORTS = (
     "ternix_b200_pack_ternary", "ternix_b200_unpack_ternary", "ternix_b200_interleave_offline",
     "ternix_b200_find_non_ternary", "ternix_b200_slice_columns",
     "ternix_b200_matmul", "ternix_b200_matmul_ex", "ternix_b200_select_kernel", "ternix_b200_matmul_host",
-    "ternix_b200_group_create", "ternix_b200_group_create_ex", "ternix_b200_group_run", "ternix_b200_group_launches", "ternix_b200_group_destroy",
+    "ternix_b200_group_create", "ternix_b200_group_create_ex", "ternix_b200_group_create_prepacked",
+    "ternix_b200_prepack_k4", "ternix_b200_prepack_k4_bytes", "ternix_b200_group_run", "ternix_b200_group_launches", "ternix_b200_group_destroy",
     "ternix_b200_gemv_batch_noalloc", "ternix_b200_gemv_batch_noalloc_limits",
     "ternix_b200_matmul_bcast", "ternix_b200_peer_alloc", "ternix_b200_peer_free", "ternix_b200_peer_export",
     "ternix_b200_peer_import", "ternix_b200_peer_close",
@@ -90,6 +91,9 @@ def _load() -> ctypes.CDLL:
         "ternix_b200_matmul_host": (i32, [vp, vp, vp, i32, i32, i32, i32]),
         "ternix_b200_group_create": (i32, [c.POINTER(vp), c.POINTER(_Problem), i32]),
         "ternix_b200_group_create_ex": (i32, [c.POINTER(vp), c.POINTER(_Problem), i32, c.POINTER(vp), i32]),
+        "ternix_b200_group_create_prepacked": (i32, [c.POINTER(vp), c.POINTER(_Problem), i32]),
+        "ternix_b200_prepack_k4": (i32, [vp, vp, i32, i32, vp]),
+        "ternix_b200_prepack_k4_bytes": (sz, [i32, i32]),
         "ternix_b200_group_run": (i32, [vp, vp, vp]),
         "ternix_b200_group_launches": (i32, [vp]),
         "ternix_b200_group_destroy": (None, [vp]),
@@ -253,8 +257,8 @@ class ProjectionGroup:
     """A fixed list of projections (a, w_packed, out) on one GPU, run with as few launches as possible:
     decode-regime members share one persistent kernel (ternix_b200_group_create / _run)."""
 
-    def __init__(self, problems, peer_ptrs=None):
-        """problems: list of (a, w_packed, out).  peer_ptrs: optional list (one entry per problem) of lists of raw
+    def __init__(self, problems, peer_ptrs=None, prepacked=False):
+        """problems: list of (a, w_packed, out); with prepacked=True the weights are prepack_k4() outputs.  peer_ptrs: optional list (one entry per problem) of lists of raw
         device addresses that receive the same C as `out` (peer GPUs' buffers), all lists of equal length."""
         import torch
 
@@ -268,8 +272,9 @@ class ProjectionGroup:
             if not (a.is_contiguous() and w.is_contiguous()) or a.dim() != 2 or w.dim() != 2:
                 raise ValueError("A and W_packed must be contiguous 2-D tensors")
             M, K = a.shape
-            N = w.shape[1] * 4
-            if w.shape[0] != K or tuple(out.shape) != (M, N) or (N > 1 and out.stride(1) != 1):
+            N = w.shape[1] if prepacked else w.shape[1] * 4
+            if w.shape[0] != ((K + 3) // 4 if prepacked else K) or tuple(out.shape) != (M, N) or \
+                    (N > 1 and out.stride(1) != 1):
                 raise ValueError("shape mismatch")
             arr[i] = _Problem(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, K, N,
                               out.stride(0) if M > 1 else max(N, out.stride(0)))
@@ -278,7 +283,10 @@ class ProjectionGroup:
         handle = ctypes.c_void_p()
         n_peers = len(peer_ptrs[0]) if peer_ptrs else 0
         with torch.cuda.device(self.device):
-            if n_peers:
+            if prepacked:
+                _check(lib.ternix_b200_group_create_prepacked(ctypes.byref(handle), arr, len(problems)),
+                       "group_create_prepacked")
+            elif n_peers:
                 flat = (ctypes.c_void_p * (len(problems) * n_peers))(*[p for row in peer_ptrs for p in row])
                 _check(lib.ternix_b200_group_create_ex(ctypes.byref(handle), arr, len(problems), flat, n_peers),
                        "group_create_ex")
@@ -302,6 +310,21 @@ class ProjectionGroup:
 
     def __del__(self):
         self.close()
+
+
+def prepack_k4(w_packed):
+    """Device tensor (K, N/4) uint8 in the packed format -> (ceil(K/4), N) uint8 in the decode-friendly layout
+    (ternix_b200_prepack_k4): same bytes, the four k-rows of a group interleaved per packed byte column."""
+    import torch
+
+    if not w_packed.is_cuda or w_packed.dtype != torch.uint8 or w_packed.dim() != 2 or not w_packed.is_contiguous():
+        raise ValueError("prepack_k4 takes a contiguous CUDA uint8 (K, N/4) tensor")
+    K, N = w_packed.shape[0], w_packed.shape[1] * 4
+    out = torch.empty(((K + 3) // 4, N), dtype=torch.uint8, device=w_packed.device)
+    with torch.cuda.device(w_packed.device):
+        _check(lib.ternix_b200_prepack_k4(w_packed.data_ptr(), out.data_ptr(), K, N,
+                                          torch.cuda.current_stream(w_packed.device).cuda_stream), "prepack_k4")
+    return out
 
 
 # --------------------------------------------------------------------------- N-column sharding

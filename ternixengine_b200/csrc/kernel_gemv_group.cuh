@@ -21,6 +21,12 @@
 // their rows fall in different halves of the 32 banks; the activation bytes of the second half are
 // permuted to match.  With 128-byte rows a warp reads one whole row per load.
 //
+// Prepacked weights (PRE = true, optional).  The byte transpose costs 8 of the 40 decode instructions and is
+// the same for every call, so it can be done once: ternix_b200_prepack_k4 stores, for every group of four
+// k-rows and every packed byte column, the four bytes of that column together in one 32-bit word (same size as
+// the packed matrix, K rounded up to a multiple of 4).  A lane then loads its four transposed words with one
+// 16-byte shared-memory load and goes straight to the AND + dp4a part: 32 instructions per 64 weights.
+//
 // Activations of the next item are prefetched with a 1-D bulk copy into the second of two
 // buffers while the current item is consumed; the per-item epilogue is one named barrier.
 #pragma once
@@ -71,10 +77,29 @@ __device__ __forceinline__ int dp4a_u8s8(uint32_t a_unsigned, int b_signed, int 
     return d;
 }
 
-template <int MR, int WORDS>
+// dst word [r][b] = { src[4r][b], src[4r+1][b], src[4r+2][b], src[4r+3][b] } (zero beyond K): the 4x4 byte
+// transpose of the GEMV decode, done once.  src is the packed K x (N/4) matrix.
+__global__ void prepack_k4_kernel(const uint8_t* __restrict__ src, uint32_t* __restrict__ dst, int K, int pitch) {
+    const int k4 = (K + 3) / 4;
+    const long long total = static_cast<long long>(k4) * pitch;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(i / pitch), b = static_cast<int>(i % pitch);
+        uint32_t w = 0;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            const int k = 4 * r + kk;
+            if (k < K) w |= static_cast<uint32_t>(src[static_cast<size_t>(k) * pitch + b]) << (8 * kk);
+        }
+        dst[i] = w;
+    }
+}
+
+template <int MR, int WORDS, bool PRE = false>
 __global__ void __launch_bounds__(kGemvThreads)
 ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupItem* __restrict__ items,
                           const int* __restrict__ cta_first, int32_t* __restrict__ status) {
+    static_assert(!PRE || WORDS == 32, "prepacked weights use 512-column items");
     constexpr int kGroupStageRows = kGroupStageBytes / (WORDS * 4);
     constexpr int kGroupStages = MR <= 2 ? 4 : 8;               // = group_stages(MR)
     constexpr int kHalves = 32 / WORDS;                 // k-groups a warp covers per load
@@ -131,8 +156,12 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
                     const uint32_t s = t % kGroupStages;
                     if (!mbar_wait(&empty[s], ((t / kGroupStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
                     mbar_arrive_expect_tx(&full[s], kGroupStageBytes);
-                    tma_load_2d(stages + s * kGroupStageBytes, &p->tmap_w, it.chunk * WORDS * 4, tt * kGroupStageRows,
-                                &full[s]);
+                    if constexpr (PRE)   // [K/4 rows][N/4 words]: 128 words x 16 rows = the same 64 k-rows x 512 columns
+                        tma_load_2d(stages + s * kGroupStageBytes, &p->tmap_w, it.chunk * WORDS * 4, tt * (kGroupStageRows / 4),
+                                    &full[s]);
+                    else
+                        tma_load_2d(stages + s * kGroupStageBytes, &p->tmap_w, it.chunk * WORDS * 4, tt * kGroupStageRows,
+                                    &full[s]);
                 }
             }
             if (*abort_flag) {
@@ -193,10 +222,16 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
                 int a4[2][MR];
 #pragma unroll
                 for (int g = 0; g < 2; ++g) {
-                    w[g][0] = lds_u32(st + o0 + g * kSecondGroup);
-                    w[g][1] = lds_u32(st + o1 + g * kSecondGroup);
-                    w[g][2] = lds_u32(st + o2 + g * kSecondGroup);
-                    w[g][3] = lds_u32(st + o3 + g * kSecondGroup);
+                    if constexpr (PRE) {
+                        // row (4-k group) kg + 8g of the stage, this lane's four transposed words
+                        const uint4 v = lds_v4(st + (kg + 8 * g) * (WORDS * 16) + lane * 16);
+                        w[g][0] = v.x; w[g][1] = v.y; w[g][2] = v.z; w[g][3] = v.w;
+                    } else {
+                        w[g][0] = lds_u32(st + o0 + g * kSecondGroup);
+                        w[g][1] = lds_u32(st + o1 + g * kSecondGroup);
+                        w[g][2] = lds_u32(st + o2 + g * kSecondGroup);
+                        w[g][3] = lds_u32(st + o3 + g * kSecondGroup);
+                    }
                     const int k = tt * kGroupStageRows + (kg + 8 * kHalves * g) * 4;
 #pragma unroll
                     for (int r = 0; r < MR; ++r) {
@@ -210,14 +245,18 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
 
 #pragma unroll
                 for (int g = 0; g < 2; ++g) {
-                    const uint32_t x0 = w[g][0], x1 = w[g][1], x2 = w[g][2], x3 = w[g][3];
-                    const uint32_t lo01 = __byte_perm(x0, x1, 0x5140), hi01 = __byte_perm(x0, x1, 0x7362);
-                    const uint32_t lo23 = __byte_perm(x2, x3, 0x5140), hi23 = __byte_perm(x2, x3, 0x7362);
                     uint32_t T[4];
-                    T[0] = __byte_perm(lo01, lo23, 0x5410);
-                    T[1] = __byte_perm(lo01, lo23, 0x7632);
-                    T[2] = __byte_perm(hi01, hi23, 0x5410);
-                    T[3] = __byte_perm(hi01, hi23, 0x7632);
+                    if constexpr (PRE) {
+                        T[0] = w[g][0]; T[1] = w[g][1]; T[2] = w[g][2]; T[3] = w[g][3];
+                    } else {
+                        const uint32_t x0 = w[g][0], x1 = w[g][1], x2 = w[g][2], x3 = w[g][3];
+                        const uint32_t lo01 = __byte_perm(x0, x1, 0x5140), hi01 = __byte_perm(x0, x1, 0x7362);
+                        const uint32_t lo23 = __byte_perm(x2, x3, 0x5140), hi23 = __byte_perm(x2, x3, 0x7362);
+                        T[0] = __byte_perm(lo01, lo23, 0x5410);
+                        T[1] = __byte_perm(lo01, lo23, 0x7632);
+                        T[2] = __byte_perm(hi01, hi23, 0x5410);
+                        T[3] = __byte_perm(hi01, hi23, 0x7632);
+                    }
 #pragma unroll
                     for (int b = 0; b < 4; ++b)
 #pragma unroll

@@ -71,6 +71,22 @@ int make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t row_bytes, uint64_t
     return TERNIX_B200_OK;
 }
 
+// 2-D tensor of 32-bit words [rows][row_words] with `pitch` bytes between rows; box = box_rows x box_words.
+int make_tmap_2d_u32(CUtensorMap* out, const void* ptr, uint64_t row_words, uint64_t rows, uint64_t pitch,
+                     uint32_t box_words, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return cuda_fail(cudaErrorNotSupported);
+    const cuuint64_t dims[2] = {row_words, rows};
+    const cuuint64_t strides[1] = {pitch};
+    const cuuint32_t box[2] = {box_words, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+    return TERNIX_B200_OK;
+}
+
 bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 int sm_count() {
@@ -400,7 +416,7 @@ bool group_gemv_ok(const ternix_b200_problem& q) {
            q.N >= 64 && aligned(q.dA, 16) && aligned(q.dW, 16) && q.ldc >= q.N;
 }
 
-template <int MR, int WORDS>
+template <int MR, int WORDS, bool PRE = false>
 int launch_gemv_group_t(const ternix_b200_group* g, int32_t* d_status, cudaStream_t st);
 
 }  // namespace
@@ -412,6 +428,7 @@ struct ternix_b200_group {
     const tb200::GroupItem* d_items = nullptr;
     const int* d_cta_first = nullptr;
     int grid = 0, mr = 0, words = 0, device = 0;
+    bool prepacked = false;                     // dW of every member is in the ternix_b200_prepack_k4 layout
     size_t grouped = 0;
     // prefill-regime members: one launch of the paired-CTA GEMM over all their tiles
     void* d_tc_blob = nullptr;                  // [Tc2Problem[] | Tc2Tile[] | int pair_first[]]
@@ -427,9 +444,9 @@ struct ternix_b200_group {
 
 namespace {
 
-template <int MR, int WORDS>
+template <int MR, int WORDS, bool PRE>
 int launch_gemv_group_t(const ternix_b200_group* g, int32_t* d_status, cudaStream_t st) {
-    auto kern = tb200::ternary_gemv_group_kernel<MR, WORDS>;
+    auto kern = tb200::ternary_gemv_group_kernel<MR, WORDS, PRE>;
     constexpr size_t smem = tb200::gemv_group_smem_bytes<MR, WORDS>();
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
@@ -672,8 +689,8 @@ int ternix_b200_unpack_gathered(const int32_t* d_gathered, int32_t* dC, int M, i
     return TERNIX_B200_OK;
 }
 
-int ternix_b200_group_create_ex(ternix_b200_group** out, const ternix_b200_problem* problems, int count,
-                                int32_t* const* peer_dC, int n_peers) {
+static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem* problems, int count,
+                             int32_t* const* peer_dC, int n_peers, bool prepacked) {
     if (!out || count < 0 || (count > 0 && !problems)) return TERNIX_B200_ERR_INVALID_ARG;
     if (n_peers < 0 || n_peers >= tb200::kTc2MaxDest || (n_peers > 0 && !peer_dC)) return TERNIX_B200_ERR_INVALID_ARG;
     *out = nullptr;
@@ -689,7 +706,8 @@ int ternix_b200_group_create_ex(ternix_b200_group** out, const ternix_b200_probl
 
     // Item width: 512 columns (128-byte rows) unless TERNIX_B200_GROUP_WORDS=16 asks for 256 (tuning aid).
     g->words = 32;
-    if (const char* env = std::getenv("TERNIX_B200_GROUP_WORDS")) g->words = std::atoi(env) == 16 ? 16 : 32;
+    g->prepacked = prepacked;
+    if (const char* env = std::getenv("TERNIX_B200_GROUP_WORDS")) g->words = (!prepacked && std::atoi(env) == 16) ? 16 : 32;
     const int item_cols = g->words * 16;
     std::vector<tb200::Tc2Problem> tc_probs;
     std::vector<tb200::GroupProblem> probs;
@@ -699,7 +717,8 @@ int ternix_b200_group_create_ex(ternix_b200_group** out, const ternix_b200_probl
     for (int i = 0; i < count; ++i) {
         const ternix_b200_problem& q = problems[i];
         if (q.M == 0 || q.N == 0) continue;
-        if (q.K > 0 && gemm_tc2_ok(q.dA, q.dW, q.M, q.K, q.N)) {
+        if (prepacked && !group_gemv_ok(q)) { delete g; return TERNIX_B200_ERR_UNSUPPORTED; }   // decode members only
+        if (!prepacked && q.K > 0 && gemm_tc2_ok(q.dA, q.dW, q.M, q.K, q.N)) {
             tb200::Tc2Problem tp{};
             int rc = make_tmap_2d(&tp.tmap_a, q.dA, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.M),
                                   static_cast<uint64_t>(q.K), tb200::kTcBK, tb200::kTcBM, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -729,9 +748,12 @@ int ternix_b200_group_create_ex(ternix_b200_group** out, const ternix_b200_probl
         }
         if (!group_gemv_ok(q)) { g->singles.push_back(q); continue; }
         tb200::GroupProblem gp{};
-        const int rc = make_tmap_2d(&gp.tmap_w, q.dW, static_cast<uint64_t>(q.N / 4), static_cast<uint64_t>(q.K),
-                                    static_cast<uint64_t>(q.N / 4), g->words * 4, tb200::group_stage_rows(g->words),
-                                    CU_TENSOR_MAP_SWIZZLE_NONE);
+        const int rc = prepacked
+            ? make_tmap_2d_u32(&gp.tmap_w, q.dW, static_cast<uint64_t>(q.N / 4), static_cast<uint64_t>((q.K + 3) / 4),
+                               static_cast<uint64_t>(q.N), 128, tb200::group_stage_rows(32) / 4)
+            : make_tmap_2d(&gp.tmap_w, q.dW, static_cast<uint64_t>(q.N / 4), static_cast<uint64_t>(q.K),
+                           static_cast<uint64_t>(q.N / 4), g->words * 4, tb200::group_stage_rows(g->words),
+                           CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc) { delete g; return rc; }
         gp.A = q.dA; gp.C = q.dC; gp.ldc = q.ldc; gp.M = q.M; gp.K = q.K; gp.N = q.N;
         const int pi = static_cast<int>(probs.size());
@@ -839,8 +861,36 @@ int ternix_b200_group_create_ex(ternix_b200_group** out, const ternix_b200_probl
     return TERNIX_B200_OK;
 }
 
+int ternix_b200_group_create_ex(ternix_b200_group** out, const ternix_b200_problem* problems, int count,
+                                int32_t* const* peer_dC, int n_peers) {
+    return group_create_impl(out, problems, count, peer_dC, n_peers, false);
+}
+
 int ternix_b200_group_create(ternix_b200_group** out, const ternix_b200_problem* problems, int count) {
-    return ternix_b200_group_create_ex(out, problems, count, nullptr, 0);
+    return group_create_impl(out, problems, count, nullptr, 0, false);
+}
+
+int ternix_b200_group_create_prepacked(ternix_b200_group** out, const ternix_b200_problem* problems, int count) {
+    return group_create_impl(out, problems, count, nullptr, 0, true);
+}
+
+size_t ternix_b200_prepack_k4_bytes(int K, int N) {
+    if (K < 0 || N < 0 || (N % 4) != 0) return 0;
+    return static_cast<size_t>((K + 3) / 4) * static_cast<size_t>(N);
+}
+
+int ternix_b200_prepack_k4(const uint8_t* dW, uint8_t* dW_prepacked, int K, int N, void* stream) {
+    if (K < 0 || N < 0 || (N % 4) != 0) return TERNIX_B200_ERR_INVALID_SHAPE;
+    if (K == 0 || N == 0) return TERNIX_B200_OK;
+    if (!dW || !dW_prepacked || !aligned(dW_prepacked, 16)) return TERNIX_B200_ERR_INVALID_ARG;
+    const long long total = static_cast<long long>((K + 3) / 4) * (N / 4);
+    long long blocks = (total + 255) / 256;
+    const long long cap = static_cast<long long>(sm_count()) * 16;
+    if (blocks > cap) blocks = cap;
+    tb200::prepack_k4_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        dW, reinterpret_cast<uint32_t*>(dW_prepacked), K, N / 4);
+    TB_CUDA(cudaGetLastError());
+    return TERNIX_B200_OK;
 }
 
 
@@ -850,7 +900,11 @@ int ternix_b200_group_run(const ternix_b200_group* g, int32_t* d_status, void* s
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (g->grid > 0) {
         int rc;
-        if (g->words == 32) {
+        if (g->prepacked) {
+            if (g->mr == 1) rc = launch_gemv_group_t<1, 32, true>(g, d_status, st);
+            else if (g->mr == 2) rc = launch_gemv_group_t<2, 32, true>(g, d_status, st);
+            else rc = launch_gemv_group_t<4, 32, true>(g, d_status, st);
+        } else if (g->words == 32) {
             if (g->mr == 1) rc = launch_gemv_group_t<1, 32>(g, d_status, st);
             else if (g->mr == 2) rc = launch_gemv_group_t<2, 32>(g, d_status, st);
             else rc = launch_gemv_group_t<4, 32>(g, d_status, st);

@@ -426,3 +426,36 @@ def test_group_run_inside_a_cuda_graph():
     torch.cuda.synchronize()
     for (a, w, out), e in zip(probs, expect):
         assert_same(out.cpu().numpy(), e, "graph replay")
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 7])
+def test_prepacked_weights_group(M):
+    """Decode batch on weights in the K-interleaved prepack layout: identical results, ragged K and N tails."""
+    import torch
+    shapes = [(M, 2560, 6912), (M, 2560, 640), (1, 1040, 320), (M, 6912, 2560), (M, 144, 64), (M, 8192, 128)]
+    probs, expect = [], []
+    for i, (m, k, n) in enumerate(shapes):
+        a, wp = synth(m, k, n, 55 * M + i)
+        expect.append(oracle_lib.matmul(a, wp))
+        dw = torch.from_numpy(wp).cuda()
+        pre = tb.prepack_k4(dw)
+        assert tuple(pre.shape) == ((k + 3) // 4, n)
+        # the layout itself: word [r][b] holds bytes W[4r..4r+3][b]
+        ref = np.zeros(((k + 3) // 4 * 4, n // 4), dtype=np.uint8)
+        ref[:k] = wp
+        ref = ref.reshape(-1, 4, n // 4).transpose(0, 2, 1).reshape(-1, n)
+        assert np.array_equal(pre.cpu().numpy(), ref)
+        probs.append((torch.from_numpy(a).cuda(), pre, torch.full((m, n), -999, dtype=torch.int32, device="cuda")))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    group = tb.ProjectionGroup(probs, prepacked=True)
+    assert group.launches == 1
+    for _ in range(2):
+        group.run(status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for (a, w, out), e in zip(probs, expect):
+        assert_same(out.cpu().numpy(), e, f"prepacked member {tuple(a.shape)}")
+    with pytest.raises(ValueError):                                  # prefill-sized members are not taken
+        big = torch.zeros((256, 64), dtype=torch.int8, device="cuda")
+        tb.ProjectionGroup([(big, tb.prepack_k4(torch.zeros((64, 64), dtype=torch.uint8, device="cuda")),
+                             torch.zeros((256, 256), dtype=torch.int32, device="cuda"))], prepacked=True)
