@@ -435,6 +435,13 @@ def bench_gemv(tb, dev, peaks):
     bytes_per = GEMV_K * GEMV_N // 4 + GEMV_K + 4 * GEMV_N
     passes = 20
     us_group = timed(group.run, passes, 5, lambda: None) * 1e3 / (passes * copies)
+    # the same 64 GEMVs on prepacked (K-interleaved) copies of the weights: no byte transpose in the kernel
+    pre_w = [tb.prepack_k4(w) for w in dws]
+    group_pre = tb.ProjectionGroup([(da, pre_w[i], outs[i]) for i in range(copies)], prepacked=True)
+    group_pre.run(status=status)
+    check("grouped, prepacked")
+    us_group_pre = timed(group_pre.run, passes, 5, lambda: None) * 1e3 / (passes * copies)
+    del group_pre, pre_w
     us_stream = timed(sweep, 5, 3, lambda: None) * 1e3 / (5 * copies)
     g = torch.cuda.CUDAGraph()
     s = torch.cuda.Stream()
@@ -462,6 +469,14 @@ def bench_gemv(tb, dev, peaks):
         if not np.array_equal(C.cpu().numpy(), oracle_lib.matmul(A.cpu().numpy(), W.cpu().numpy(), "scalar")):
             raise SystemExit("config 5 projection differs from the CPU oracle; refusing to report a number")
     ms5 = timed(g5.run, passes, 5, lambda: None) / passes
+    pre5 = [(A, tb.prepack_k4(W), torch.empty_like(C)) for (A, W, C) in probs]
+    g5p = tb.ProjectionGroup(pre5, prepacked=True)
+    g5p.run(status=status)
+    torch.cuda.synchronize()
+    for (A, W, C), (Ap, Wp_, Cp) in zip(probs, pre5):
+        if not torch.equal(C, Cp):
+            raise SystemExit("config 5: prepacked result differs from the packed-format result")
+    ms5p = timed(g5p.run, passes, 5, lambda: None) / passes
 
     t_cpu0 = time.perf_counter()
     reps = 5
@@ -483,6 +498,13 @@ def bench_gemv(tb, dev, peaks):
             "config5_m1": {"projections": 210, "launches": g5.launches, "ms": ms5, "projections_per_s": 210 / (ms5 * 1e-3),
                            "gbs": total_bytes / (ms5 * 1e-3) / 1e9, "frac_of_measured_hbm": total_bytes / (ms5 * 1e-3) / 1e9 / peaks["hbm_gbs"],
                            "algorithmic_bytes": total_bytes},
+            "prepacked_weights": {
+                "what": "same kernels on ternix_b200_prepack_k4 copies of the weights (same size, four k-rows interleaved per "
+                        "packed byte column); the packed format above stays the headline",
+                "config1_x64_us_per_gemv": us_group_pre, "config1_x64_gbs": gbs(us_group_pre),
+                "config5_m1_ms": ms5p, "config5_m1_gbs": total_bytes / (ms5p * 1e-3) / 1e9,
+                "config5_m1_frac_of_measured_hbm": total_bytes / (ms5p * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                "config5_m1_frac_of_nominal_8000": total_bytes / (ms5p * 1e-3) / 1e9 / 8000.0},
             "cpu_baseline": {"value": bytes_per / cpu_s / 1e9, "unit": "GB/s", "cores": 1,
                              "kind": "reference" if oracle_lib.have_ref() else "port",
                              "sample": f"one whole GEMV, mean of {reps}, one thread (the kernel cannot slice M=1)"}}
