@@ -131,7 +131,7 @@ void ternix_b200_group_destroy(ternix_b200_group *group);
 /* ---- a decode batch for callers that must not allocate ---------------------------------------------
  * No counterpart in the reference.  Some callers cannot have the library call cudaMalloc on their behalf:
  * an inference server whose device memory is owned entirely by its own pool allocator, a caller inside a
- * memory-budgeted or real-time section, a plugin host that forbids allocation after start-up.  For them
+ * memory-capped or real-time section, a plugin host that forbids allocation after start-up.  For them
  * this entry point runs the same persistent decode kernel as ternix_b200_group_run, but the tables that
  * kernel reads (TMA descriptors, work list) sit in a fixed array inside the library image instead of a
  * cudaMalloc'ed block, and the host side uses fixed buffers too: no cudaMalloc, cudaFree or other

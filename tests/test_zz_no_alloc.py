@@ -1,7 +1,7 @@
 """The allocation-free decode batch (ternix_b200_gemv_batch_noalloc).
 
 Who needs it: callers that cannot let a library call cudaMalloc for them -- a serving process whose device
-memory belongs to its own pool allocator, code running inside a fixed memory budget or a latency-critical
+memory belongs to its own pool allocator, code running under a fixed memory cap or in a latency-critical
 section, hosts that forbid allocation after start-up.  The entry point keeps the kernel's tables in a fixed
 array inside the library image, so the only device memory it touches besides that array is what the caller
 passes in.
