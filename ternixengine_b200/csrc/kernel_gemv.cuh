@@ -139,19 +139,22 @@ ternary_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const int8_t* __
 
         const int word = lane % WORDS;
         const int kg = warp * G::kGroupsPerWarp + lane / WORDS;   // 4-row group inside a stage
+        // explicit shared-window addresses: pointers derived from the dynamic-shared base are generic to the compiler
+        const uint32_t stages_sa = smem_u32(stages), a_sa = smem_u32(a_s), part_sa = smem_u32(part);
+        const uint32_t w_off = ((kg * 4) * WORDS + word) * 4;
 
         for (int t = 0; t < ntiles; ++t) {
             const int s = t % kGemvStages;
             if (!mbar_wait(&full[s], (t / kGemvStages) & 1, abort_flag)) break;
-            const uint32_t* st = reinterpret_cast<const uint32_t*>(stages + s * kGemvStageBytes);
-            const uint32_t w0 = st[(kg * 4 + 0) * WORDS + word];
-            const uint32_t w1 = st[(kg * 4 + 1) * WORDS + word];
-            const uint32_t w2 = st[(kg * 4 + 2) * WORDS + word];
-            const uint32_t w3 = st[(kg * 4 + 3) * WORDS + word];
+            const uint32_t st = stages_sa + s * kGemvStageBytes + w_off;
+            const uint32_t w0 = lds_u32(st);
+            const uint32_t w1 = lds_u32(st + WORDS * 4);
+            const uint32_t w2 = lds_u32(st + 2 * WORDS * 4);
+            const uint32_t w3 = lds_u32(st + 3 * WORDS * 4);
             int a4[MR];
 #pragma unroll
             for (int r = 0; r < MR; ++r)
-                a4[r] = *reinterpret_cast<const int*>(a_s + r * krange + t * G::kStageRows + kg * 4);
+                a4[r] = static_cast<int>(lds_u32(a_sa + r * krange + t * G::kStageRows + kg * 4));
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);   // the words are in registers: release the stage early
 
@@ -177,7 +180,7 @@ ternary_gemv_kernel(const __grid_constant__ CUtensorMap tmap_w, const int8_t* __
 #pragma unroll
         for (int r = 0; r < MR; ++r)
 #pragma unroll
-            for (int c = 0; c < 16; ++c) atomicAdd(&part[(r * 16 + c) * (WORDS + 1) + word], acc[r][c]);
+            for (int c = 0; c < 16; ++c) red_shared_add(part_sa + ((r * 16 + c) * (WORDS + 1) + word) * 4, acc[r][c]);
     }
 
     __syncwarp();

@@ -25,18 +25,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred = 0;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "elect.sync _|p, 0xffffffff;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}\n"
-        : "=r"(pred));
-    return pred != 0;
-}
-
 // ---------------------------------------------------------------- shared-memory data access by 32-bit address
 // Data in dynamic shared memory is addressed through these helpers with explicit shared-window
 // addresses: a pointer derived from the dynamic-shared base is a generic pointer to the compiler,
@@ -217,13 +205,4 @@ __device__ __forceinline__ uint32_t dsmem_map(uint32_t smem_addr, uint32_t rank)
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
     return r;
 }
-__device__ __forceinline__ int4 dsmem_ld_v4(uint32_t cluster_addr) {
-    int4 v;
-    asm volatile("ld.shared::cluster.v4.s32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "r"(cluster_addr)
-                 : "memory");
-    return v;
-}
-
 }  // namespace tb200
