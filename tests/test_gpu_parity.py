@@ -459,3 +459,23 @@ def test_prepacked_weights_group(M):
         big = torch.zeros((256, 64), dtype=torch.int8, device="cuda")
         tb.ProjectionGroup([(big, tb.prepack_k4(torch.zeros((64, 64), dtype=torch.uint8, device="cuda")),
                              torch.zeros((256, 256), dtype=torch.int32, device="cuda"))], prepacked=True)
+
+
+def test_python_module_device_arrays():
+    """ternix_engine.ternary_matmul on device arrays (__cuda_array_interface__): no host round trip, strided out."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "ternixengine_b200"))
+    import ternix_engine as te
+    for (m, k, n) in [(1, 2560, 6912), (300, 1040, 832), (7, 129, 4)]:
+        a, wp = synth(m, k, n, 5 * m + n)
+        expect = oracle_lib.matmul(a, wp)
+        da, dw = torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda()
+        wide = torch.full((m, n + 4), -9, dtype=torch.int32, device="cuda")
+        out = wide[:, :n]
+        got = te.ternary_matmul(da, dw, "cuda_tiled", out=out, stream=torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert got is out
+        assert_same(out.cpu().numpy(), expect, f"device arrays {m}x{k}x{n}")
+        assert bool((wide[:, n:] == -9).all())
+    with pytest.raises(ValueError):
+        te.ternary_matmul(da, dw)                                  # device input without `out`
