@@ -167,6 +167,22 @@ int ternix_b200_peer_export(void *dptr, unsigned char handle[64]);
 int ternix_b200_peer_import(const unsigned char handle[64], void **dptr);
 int ternix_b200_peer_close(void *dptr);
 
+/* ---- the steps either side of the product in a BitNet-style layer -----------------------------------
+ * No counterpart in the reference (its README lists activation/absmean scaling as missing, README.md:203); the
+ * arithmetic is the published BitNet b1.58 recipe, stated exactly so that it can be checked bit for bit:
+ *   quantize_rows:  absmax = max_k |x[m,k]|;  q = rint(x * (127 / absmax)) clamped to [-127,127] (fp32, nearest
+ *                   even);  row_scale[m] = absmax / 127  (all-zero row: q = 0, row_scale = 1).
+ *   matmul_dequant: y[m,n] = bf16_rn((float(c[m,n]) * row_scale[m]) * w_scale) with c the exact int32 product;
+ *                   bfloat16 out (ldy in elements), up to 8 destinations as for ternix_b200_matmul_bcast.  Large
+ *                   problems do this in the GEMM epilogue; others compute int32 into a pool buffer and convert. */
+#define TERNIX_B200_DTYPE_F32   0
+#define TERNIX_B200_DTYPE_BF16  1
+int ternix_b200_quantize_rows(const void *dX, int x_dtype, long long ldx, int8_t *dA, float *d_row_scale, int M, int K,
+                              void *stream);
+int ternix_b200_matmul_dequant(const int8_t *dA, const uint8_t *dW, void *const *dY_list, int n_dest,
+                               const float *d_row_scale, float w_scale, int M, int K, int N, long long ldy,
+                               int32_t *d_status, void *stream);
+
 /* ---- N-column sharding plan (host arithmetic only) ---------------------------------------------
  * Splits N columns over `world` ranks in granules of `granule` columns (a multiple of 4; 64 keeps each
  * shard's packed rows 16-byte aligned).  Writes the first column and the column count of `rank`.

@@ -48,6 +48,7 @@ EXPORTS = (
     "ternix_b200_group_create", "ternix_b200_group_create_ex", "ternix_b200_group_create_prepacked",
     "ternix_b200_prepack_k4", "ternix_b200_prepack_k4_bytes", "ternix_b200_group_run", "ternix_b200_group_launches", "ternix_b200_group_destroy",
     "ternix_b200_gemv_batch_noalloc", "ternix_b200_gemv_batch_noalloc_limits",
+    "ternix_b200_quantize_rows", "ternix_b200_matmul_dequant",
     "ternix_b200_matmul_bcast", "ternix_b200_peer_alloc", "ternix_b200_peer_free", "ternix_b200_peer_export",
     "ternix_b200_peer_import", "ternix_b200_peer_close",
     "ternix_b200_shard_columns", "ternix_b200_unpack_gathered",
@@ -99,6 +100,8 @@ def _load() -> ctypes.CDLL:
         "ternix_b200_group_destroy": (None, [vp]),
         "ternix_b200_gemv_batch_noalloc": (i32, [c.POINTER(_Problem), i32, vp, vp]),
         "ternix_b200_gemv_batch_noalloc_limits": (i32, [c.POINTER(i32), c.POINTER(i32), c.POINTER(i64)]),
+        "ternix_b200_quantize_rows": (i32, [vp, i32, i64, vp, vp, i32, i32, vp]),
+        "ternix_b200_matmul_dequant": (i32, [vp, vp, c.POINTER(vp), i32, vp, c.c_float, i32, i32, i32, i64, vp, vp]),
         "ternix_b200_matmul_bcast": (i32, [vp, vp, c.POINTER(vp), i32, i32, i32, i32, i64, vp, vp]),
         "ternix_b200_peer_alloc": (i32, [c.POINTER(vp), sz]),
         "ternix_b200_peer_free": (i32, [vp]),
@@ -250,6 +253,41 @@ def matmul(a, w_packed, out=None, kernel: str = "auto", status=None, stream=None
                                        KERNELS[kernel], status.data_ptr() if status is not None else None,
                                        s.cuda_stream)
     _check(rc, "matmul")
+    return out
+
+
+def quantize_rows(x):
+    """Per-row absmax int8 quantisation of a CUDA float32 / bfloat16 (M, K) tensor -> (int8 (M, K), float32 (M,))."""
+    import torch
+
+    if not x.is_cuda or x.dim() != 2 or x.stride(1) != 1 or x.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError("quantize_rows takes a CUDA float32 or bfloat16 (M, K) tensor with unit column stride")
+    M, K = x.shape
+    a = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    scale = torch.empty((M,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(lib.ternix_b200_quantize_rows(x.data_ptr(), 0 if x.dtype == torch.float32 else 1, x.stride(0) if M > 1 else K,
+                                             a.data_ptr(), scale.data_ptr(), M, K,
+                                             torch.cuda.current_stream(x.device).cuda_stream), "quantize_rows")
+    return a, scale
+
+
+def matmul_dequant(a, w_packed, row_scale, w_scale: float, out=None, status=None, extra_dest_ptrs=()):
+    """bfloat16 (M, N) = (A x W) * row_scale[:, None] * w_scale with the integer product exact."""
+    import torch
+
+    M, K = a.shape
+    N = w_packed.shape[1] * 4
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != (M, N) or out.stride(1) != 1:
+        raise ValueError("out must be (M, N) bfloat16 with unit column stride")
+    ptrs = (ctypes.c_void_p * (1 + len(extra_dest_ptrs)))(out.data_ptr(), *extra_dest_ptrs)
+    with torch.cuda.device(a.device):
+        _check(lib.ternix_b200_matmul_dequant(a.data_ptr(), w_packed.data_ptr(), ptrs, len(ptrs), row_scale.data_ptr(),
+                                              ctypes.c_float(w_scale), M, K, N, out.stride(0) if M > 1 else N,
+                                              status.data_ptr() if status is not None else None,
+                                              torch.cuda.current_stream(a.device).cuda_stream), "matmul_dequant")
     return out
 
 

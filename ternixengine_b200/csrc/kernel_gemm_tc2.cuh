@@ -26,9 +26,15 @@
 // same columns of C in every peer GPU's memory (plain stores through peer-mapped pointers), which
 // replaces a separate all-gather and overlaps the transfer with the next tile's main loop.
 //
+// Dequantising epilogue (kBf16).  The step after this product in a BitNet-style layer multiplies the integer
+// result by the activation row's scale and the weight tensor's scale.  With kBf16 the epilogue does that in
+// fp32 -- y = bf16_rn((float(c) * row_scale[m]) * w_scale) -- and stores bfloat16, half the bytes of int32, which
+// also halves what a fused gather ships over NVLink.  The integer accumulation before it is unchanged and exact.
+//
 // Decode, layouts, exactness and bounded waits are those of ternary_gemm_tc_kernel.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cstdint>
 #include "kernel_gemm_tc.cuh"
 #include "ptx_sm100.cuh"
@@ -169,12 +175,14 @@ __device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank)
                  : "memory");
 }
 
-template <bool kGrouped>
+template <bool kGrouped, bool kBf16 = false>
 __global__ void __launch_bounds__(kTc2Threads, 1)
 ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                         const __grid_constant__ Tc2Dest dest, int M, int K, int N, long long ldc, int c_vec_ok,
                         const Tc2Problem* __restrict__ probs, const Tc2Tile* __restrict__ tiles,
-                        const int* __restrict__ pair_first, int32_t* __restrict__ status) {
+                        const int* __restrict__ pair_first, int32_t* __restrict__ status,
+                        const float* __restrict__ row_scale = nullptr, float w_scale = 1.0f) {
+    static_assert(!(kGrouped && kBf16), "the dequantising epilogue is built for single products");
     using G = Tc2Geom;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -373,6 +381,8 @@ ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             tc_fence_after_sync();
             const int row_base = m_t * 2 * kTcBM + rank * kTcBM + quad * 32;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kTc2TileN;
+            float rs = 0.0f;                                           // scale of this lane's accumulator row
+            if constexpr (kBf16) rs = (row_base + lane < M) ? row_scale[row_base + lane] : 0.0f;
 #pragma unroll 1
             for (int c0 = 0; c0 < kTc2TileN; c0 += 64) {
 #pragma unroll
@@ -386,14 +396,60 @@ ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
                             o[g * 16 + 4 * (i & 3) + (i >> 2)] = static_cast<int32_t>(r[g * 16 + i]) >> 6;
+                    if constexpr (kBf16) {
+                        // 32 columns -> 32 bfloat16 = four 16-byte chunks of this lane's 128-byte staging row
+                        uint32_t pk[16];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int chunk = h * 8 + j;                   // 16-byte chunk of the 64-column row
-                        sts_v4(my_row_sa + ((chunk ^ (lane & 7)) << 4),
-                               make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
+                        for (int i = 0; i < 16; ++i) {
+                            const float lo = (static_cast<float>(o[2 * i]) * rs) * w_scale;
+                            const float hi = (static_cast<float>(o[2 * i + 1]) * rs) * w_scale;
+                            const __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+                            pk[i] = *reinterpret_cast<const uint32_t*>(&b2);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int chunk = h * 4 + j;
+                            sts_v4(stage_sa + lane * 128 + ((chunk ^ (lane & 7)) << 4),
+                                   make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const int chunk = h * 8 + j;               // 16-byte chunk of the 64-column row
+                            sts_v4(my_row_sa + ((chunk ^ (lane & 7)) << 4),
+                                   make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
+                        }
                     }
                 }
                 __syncwarp();
+                if constexpr (kBf16) {
+                    // read back row-contiguous: 8 lanes cover the 128 bytes (64 bfloat16) of one row, a warp four rows
+                    const int col = n_t * kTc2TileN + c0 + (lane & 7) * 8;
+#pragma unroll 4
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = 4 * i + (lane >> 3);
+                        const uint4 v = lds_v4(stage_sa + rr * 128 + (((lane & 7) ^ (rr & 7)) << 4));
+                        const int row = row_base + rr;
+                        if (row < M && col < N) {
+                            const size_t off = static_cast<size_t>(row) * ldc + col;
+#pragma unroll
+                            for (int d = 0; d < kTc2MaxDest; ++d) {
+                                if (d >= n_dest) break;
+                                uint16_t* out = reinterpret_cast<uint16_t*>(dst->c[d]) + off;
+                                if (c_vec_ok) {
+                                    *reinterpret_cast<uint4*>(out) = v;
+                                } else {
+                                    const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                                    for (int e2 = 0; e2 < 4; ++e2) {
+                                        out[2 * e2] = static_cast<uint16_t>(wds[e2] & 0xFFFFu);
+                                        out[2 * e2 + 1] = static_cast<uint16_t>(wds[e2] >> 16);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                } else {
                 // read back row-contiguous: 16 lanes cover the 256 bytes of one row, a warp covers two rows
                 const int col = n_t * kTc2TileN + c0 + (lane & 15) * 4;
 #pragma unroll 4
@@ -417,6 +473,7 @@ ternary_gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                             }
                         }
                     }
+                }
                 }
                 __syncwarp();                                          // before the staging tile is rewritten
             }

@@ -3,6 +3,7 @@
 #include "ternix_b200.h"
 
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -353,7 +354,8 @@ int launch_gemm_tc2_t(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_li
     } else {
         TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc2_kernel<false>, tmap_a, tmap_w, dest, M, K, N, ldc,
                                    c_vec_ok, static_cast<const tb200::Tc2Problem*>(nullptr),
-                                   static_cast<const tb200::Tc2Tile*>(nullptr), static_cast<const int*>(nullptr), d_status));
+                                   static_cast<const tb200::Tc2Tile*>(nullptr), static_cast<const int*>(nullptr), d_status,
+                                   static_cast<const float*>(nullptr), 1.0f));
     }
     return TERNIX_B200_OK;
 }
@@ -484,7 +486,105 @@ int launch_gemm_tc2_group(const ternix_b200_group* g, int32_t* d_status, cudaStr
     CUtensorMap unused{};
     tb200::Tc2Dest no_dest{};
     TB_CUDA(cudaLaunchKernelEx(&cfg, kern, unused, unused, no_dest, 0, 0, 0, 0LL, 0, g->d_tc_probs, g->d_tc_tiles,
-                               g->d_tc_first, d_status));
+                               g->d_tc_first, d_status, static_cast<const float*>(nullptr), 1.0f));
+    return TERNIX_B200_OK;
+}
+
+// ---------------------------------------------------------------- the steps either side of the product
+// Per-row absmax quantisation of activations (BitNet b1.58's activation quantiser): one CTA per row.
+//   absmax = max_k |x|;  s = 127 / absmax;  q = rint(x * s) in [-127, 127];  row_scale = absmax / 127.
+// An all-zero row gets q = 0 and row_scale = 1.  fp32 arithmetic, round-to-nearest-even.
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+quantize_rows_kernel(const T* __restrict__ X, long long ldx, int8_t* __restrict__ A, float* __restrict__ row_scale,
+                     int M, int K) {
+    __shared__ float s_max[8];
+    const int row = blockIdx.x;
+    const T* x = X + static_cast<size_t>(row) * ldx;
+    float m = 0.0f;
+    for (int k = threadIdx.x; k < K; k += 256) m = fmaxf(m, fabsf(to_f32<T>(x[k])));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = s_max[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, s_max[w]);
+    const float s = m > 0.0f ? 127.0f / m : 0.0f;
+    if (threadIdx.x == 0) row_scale[row] = m > 0.0f ? m / 127.0f : 1.0f;
+    int8_t* a = A + static_cast<size_t>(row) * K;
+    for (int k = threadIdx.x; k < K; k += 256) {
+        int q = __float2int_rn(to_f32<T>(x[k]) * s);
+        q = q > 127 ? 127 : q < -127 ? -127 : q;
+        a[k] = static_cast<int8_t>(q);
+    }
+}
+
+// y = bf16_rn((float(c) * row_scale[m]) * w_scale), from an int32 C to up to 8 bfloat16 destinations: the
+// unfused form of the dequantising epilogue, for problems the paired-CTA kernel does not take.
+__global__ void dequant_rows_kernel(const int32_t* __restrict__ C, long long ldc, tb200::Tc2Dest dest, long long ldy,
+                                    const float* __restrict__ row_scale, float w_scale, int M, int N) {
+    const long long total = static_cast<long long>(M) * N;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int row = static_cast<int>(i / N), col = static_cast<int>(i % N);
+        const float v = (static_cast<float>(C[static_cast<size_t>(row) * ldc + col]) * row_scale[row]) * w_scale;
+        const __nv_bfloat16 b = __float2bfloat16_rn(v);
+        for (int d = 0; d < dest.count; ++d)
+            reinterpret_cast<__nv_bfloat16*>(dest.c[d])[static_cast<size_t>(row) * ldy + col] = b;
+    }
+}
+
+int launch_gemm_tc2_bf16(const int8_t* dA, const uint8_t* dW, void* const* dY_list, int n_dest, const float* row_scale,
+                         float w_scale, int M, int K, int N, long long ldy, int32_t* d_status, cudaStream_t st) {
+    using G = tb200::Tc2Geom;
+    auto kern = tb200::ternary_gemm_tc2_kernel<false, true>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(G::kSmemBytes));
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    CUtensorMap tmap_a, tmap_w;
+    int rc = make_tmap_2d(&tmap_a, dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K),
+                          tb200::kTcBK, tb200::kTcBM, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tmap_w, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K),
+                      static_cast<uint64_t>(N / 4), G::kWpRowBytes, tb200::kTcBK, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    const long tiles = static_cast<long>((M + 255) / 256) * ((N + 255) / 256);
+    const long max_pairs = sm_count() / 2;
+    const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
+    tb200::Tc2Dest dest{};
+    dest.count = n_dest;
+    int vec_ok = (ldy % 8 == 0);
+    for (int d = 0; d < n_dest; ++d) {
+        dest.c[d] = static_cast<int32_t*>(dY_list[d]);
+        vec_ok = vec_ok && aligned(dY_list[d], 16);
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(tb200::kTc2Threads, 1, 1);
+    cfg.dynamicSmemBytes = G::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    TB_CUDA(cudaLaunchKernelEx(&cfg, kern, tmap_a, tmap_w, dest, M, K, N, ldy, vec_ok,
+                               static_cast<const tb200::Tc2Problem*>(nullptr), static_cast<const tb200::Tc2Tile*>(nullptr),
+                               static_cast<const int*>(nullptr), d_status, row_scale, w_scale));
     return TERNIX_B200_OK;
 }
 
@@ -1081,6 +1181,56 @@ int ternix_b200_gemv_batch_noalloc_limits(int* max_problems, int* max_items, lon
     if (max_items) *max_items = kNoAllocMaxItems;
     if (scratch_bytes) *scratch_bytes = static_cast<long long>(kNoAllocBytes);
     return TERNIX_B200_OK;
+}
+
+int ternix_b200_quantize_rows(const void* dX, int x_dtype, long long ldx, int8_t* dA, float* d_row_scale, int M, int K,
+                              void* stream) {
+    if (M < 0 || K < 0) return TERNIX_B200_ERR_INVALID_SHAPE;
+    if (x_dtype != TERNIX_B200_DTYPE_F32 && x_dtype != TERNIX_B200_DTYPE_BF16) return TERNIX_B200_ERR_INVALID_ARG;
+    if (M == 0) return TERNIX_B200_OK;
+    if (!dX || !dA || !d_row_scale || ldx < K) return TERNIX_B200_ERR_INVALID_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (x_dtype == TERNIX_B200_DTYPE_F32)
+        quantize_rows_kernel<float><<<M, 256, 0, st>>>(static_cast<const float*>(dX), ldx, dA, d_row_scale, M, K);
+    else
+        quantize_rows_kernel<__nv_bfloat16><<<M, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dX), ldx, dA, d_row_scale, M, K);
+    TB_CUDA(cudaGetLastError());
+    return TERNIX_B200_OK;
+}
+
+int ternix_b200_matmul_dequant(const int8_t* dA, const uint8_t* dW, void* const* dY_list, int n_dest,
+                               const float* d_row_scale, float w_scale, int M, int K, int N, long long ldy,
+                               int32_t* d_status, void* stream) {
+    if (M < 0 || K < 0 || N < 0 || (N % 4) != 0) return TERNIX_B200_ERR_INVALID_SHAPE;
+    if (ldy < N || n_dest < 1 || n_dest > tb200::kTc2MaxDest || !dY_list || !d_row_scale) return TERNIX_B200_ERR_INVALID_ARG;
+    if (M == 0 || N == 0) return TERNIX_B200_OK;
+    for (int d = 0; d < n_dest; ++d)
+        if (!dY_list[d]) return TERNIX_B200_ERR_INVALID_ARG;
+    if (K > 0 && (!dA || !dW)) return TERNIX_B200_ERR_INVALID_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (K > 0 && gemm_tc2_ok(dA, dW, M, K, N))
+        return launch_gemm_tc2_bf16(dA, dW, dY_list, n_dest, d_row_scale, w_scale, M, K, N, ldy, d_status, st);
+    // Anything else: exact int32 product into a pool buffer, then one conversion pass.
+    cudaMemPool_t pool = nullptr;
+    int rc = host_call_pool(&pool);
+    if (rc) return rc;
+    int32_t* tmp = nullptr;
+    TB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&tmp), static_cast<size_t>(M) * N * 4, pool, st));
+    rc = ternix_b200_matmul_ex(dA, dW, tmp, M, K, N, N, TERNIX_B200_KERNEL_AUTO, d_status, stream);
+    if (rc == TERNIX_B200_OK) {
+        tb200::Tc2Dest dest{};
+        dest.count = n_dest;
+        for (int d = 0; d < n_dest; ++d) dest.c[d] = static_cast<int32_t*>(dY_list[d]);
+        const long long total = static_cast<long long>(M) * N;
+        long long blocks = (total + 255) / 256;
+        const long long cap = static_cast<long long>(sm_count()) * 16;
+        if (blocks > cap) blocks = cap;
+        dequant_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(tmp, N, dest, ldy, d_row_scale, w_scale, M, N);
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) rc = cuda_fail(e);
+    }
+    cudaFreeAsync(tmp, st);
+    return rc;
 }
 
 }  // extern "C"
