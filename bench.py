@@ -279,6 +279,19 @@ def run_b200(args):
                      "note": "ternix_b200_matmul_host (what the reference's mul_mat_ternary_cuda_host binds): pinned host A, "
                              "packed W and C; pool allocation, H2D of A and W, kernel, D2H of C, free, sync inside every call"}
 
+    # the same job with the dequantising epilogue: bfloat16 C = C_int * row_scale * w_scale on every GPU
+    row_scale = torch.full((M,), 0.01, dtype=torch.float32, device=dev)
+    y = layer.forward_dequant(da, row_scale, 0.05, status=status)
+    torch.cuda.synchronize()
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import bitnet_scaling_oracle as scaling
+    y_bits = y[torch.from_numpy(rows).to(dev)].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    if not np.array_equal(y_bits, scaling.dequant_bf16_bits(expect, np.full(len(rows), 0.01, np.float32), 0.05)):
+        raise SystemExit(f"rank {rank}: dequantised output differs from its CPU restatement")
+    ms_deq = max_over_ranks(timed(lambda: layer.forward_dequant(da, row_scale, 0.05), args.steps, args.warmup, barrier))
+    dequant = {"what": "same product, GEMM epilogue emits bfloat16 = C * row_scale * w_scale (and ships it to the peers)",
+               "ms_per_step": ms_deq / args.steps, "tops": ops * args.steps / (ms_deq * 1e-3) / 1e12}
+
     # config 5 at M=256: the 210 projections of a 30-layer BitNet-2B-shaped model, sharded where it pays off
     cfg5 = bench_config5_m256(tb, dev, world, rank, barrier, max_over_ranks)
 
@@ -339,6 +352,7 @@ def run_b200(args):
         "nccl_gather_baseline": None if nccl_ms is None else {
             "ms_per_step": nccl_ms, "tops": ops / (nccl_ms * 1e-3) / 1e12,
             "what": "same shards, local GEMM then ncclAllGather of C blocks then unpack to row-major"},
+        "dequant_bf16_output": dequant,
         "config5_m256": cfg5,
         "gemv": gemv,
         "cpu_baseline": {"value": cpu_tops, "unit": "TOPS", "cores": cpu_threads, "kind": cpu_kind,

@@ -426,7 +426,9 @@ class _DeviceBuffer:
         import torch
 
         itemsize = torch.empty((), dtype=dtype).element_size()
-        typestr = {torch.int32: "<i4", torch.int8: "|i1", torch.uint8: "|u1"}[dtype]
+        if dtype == torch.bfloat16:          # no array-interface code for bfloat16: view 16-bit words, reinterpret
+            return self.as_tensor(shape, torch.int16, device).view(torch.bfloat16)
+        typestr = {torch.int32: "<i4", torch.int8: "|i1", torch.uint8: "|u1", torch.int16: "<i2"}[dtype]
         strides = []
         acc = itemsize
         for d in reversed(shape):
@@ -533,6 +535,49 @@ class ShardedTernaryLinear:
                 out.copy_(self._c)
                 return out
             return self._c
+        return self._forward_nccl(a, out, status)
+
+    def forward_dequant(self, a, row_scale, w_scale: float, status=None):
+        """bfloat16 C = (A x W) * row_scale[:, None] * w_scale on every rank.  With more than one rank the GEMM
+        epilogue of each rank scales, rounds and stores its columns into all ranks' bfloat16 C: half the NVLink
+        bytes of the int32 gather."""
+        import torch
+        import torch.distributed as dist
+
+        M = a.shape[0]
+        if self.world == 1:
+            return matmul_dequant(a, self.w_local, row_scale, w_scale, status=status)
+        if getattr(self, "_y_M", None) != M:
+            if getattr(self, "_y_M", None) is not None:
+                raise ValueError("one bfloat16 C buffer is kept: M must not change between calls")
+            with torch.cuda.device(self.device):
+                self._y_buf = _DeviceBuffer(M * self.N * 2)
+                handles = [None] * self.world
+                dist.all_gather_object(handles, self._y_buf.export(), group=self.group)
+                ptrs = []
+                for r, h in enumerate(handles):
+                    if r == self.rank:
+                        ptrs.append(self._y_buf.ptr)
+                    else:
+                        p = ctypes.c_void_p()
+                        _check(lib.ternix_b200_peer_import(h, ctypes.byref(p)), "peer_import")
+                        ptrs.append(p.value)
+            self._y = self._y_buf.as_tensor((M, self.N), torch.bfloat16, self.device)
+            self._y_peers = tuple(ptrs[r] + 2 * self.shard.n0 for r in range(self.world) if r != self.rank)
+            if self._token is None:
+                self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self._y_M = M
+        if self.shard.n_cols:
+            matmul_dequant(a, self.w_local, row_scale, w_scale, out=self._y[:, self.shard.n0:self.shard.n0 + self.shard.n_cols],
+                           status=status, extra_dest_ptrs=self._y_peers)
+        dist.all_reduce(self._token, group=self.group)
+        return self._y
+
+    def _forward_nccl(self, a, out, status):
+        import torch
+        import torch.distributed as dist
+
+        M = a.shape[0]
         # ---- NCCL baseline
         if out is None:
             out = torch.empty((M, self.N), dtype=torch.int32, device=a.device)
