@@ -710,11 +710,176 @@ int ternix_b200_matmul(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, 
     return ternix_b200_matmul_ex(dA, dW, dC, M, K, N, N, TERNIX_B200_KERNEL_AUTO, nullptr, stream);
 }
 
+}  // extern "C"
+
+namespace {
+// Streams and events of the pipelined host-pointer call, one set per device, created on first use.  The call holds
+// `mu` from start to end: two host threads on one device run one after the other.
+struct HostPipe {
+    std::mutex mu;
+    bool ready = false;
+    cudaStream_t s_in = nullptr, s_run = nullptr, s_out = nullptr;
+    static constexpr int kMaxSlabs = 16;
+    cudaEvent_t ev_alloc = nullptr, ev_a = nullptr, ev_done = nullptr, ev_w[kMaxSlabs] = {}, ev_c[kMaxSlabs] = {};
+};
+int host_pipe(HostPipe** out) {
+    static std::mutex mu;
+    static HostPipe* pipes[64] = {};
+    int dev = 0;
+    TB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return TERNIX_B200_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!pipes[dev]) pipes[dev] = new HostPipe();
+    HostPipe* p = pipes[dev];
+    if (!p->ready) {
+        TB_CUDA(cudaStreamCreateWithFlags(&p->s_in, cudaStreamNonBlocking));
+        TB_CUDA(cudaStreamCreateWithFlags(&p->s_run, cudaStreamNonBlocking));
+        TB_CUDA(cudaStreamCreateWithFlags(&p->s_out, cudaStreamNonBlocking));
+        cudaEvent_t* singles[] = {&p->ev_alloc, &p->ev_a, &p->ev_done};
+        for (cudaEvent_t* e : singles) TB_CUDA(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+        for (int i = 0; i < HostPipe::kMaxSlabs; ++i) {
+            TB_CUDA(cudaEventCreateWithFlags(&p->ev_w[i], cudaEventDisableTiming));
+            TB_CUDA(cudaEventCreateWithFlags(&p->ev_c[i], cudaEventDisableTiming));
+        }
+        p->ready = true;
+    }
+    *out = p;
+    return TERNIX_B200_OK;
+}
+
+// Large products through host pointers are bound by the device-to-host copy of C (4 bytes per output against one
+// byte per 4 weights in).  This path cuts C into slabs and runs three streams: the inputs of slab j+1 go up while
+// slab j is computed and slab j-1 comes down, so that the link carries C from shortly after the shared operand has
+// arrived.  Column slabs (by_rows == false) share A and take W slab by slab; W and C of a slab are compact on the
+// device and the copies are pitched on the host side.  Row slabs share W and take A slab by slab; every copy is
+// contiguous.
+int matmul_host_pipelined(const int8_t* A, const uint8_t* Wp, int32_t* C, int M, int K, int N, int kernel, int slab,
+                          bool by_rows) {
+    HostPipe* hp = nullptr;
+    int rc = host_pipe(&hp);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(hp->mu);
+    const int extent = by_rows ? M : N;
+    const int n_slabs = (extent + slab - 1) / slab;
+    if (n_slabs > HostPipe::kMaxSlabs) return TERNIX_B200_ERR_INVALID_ARG;
+    auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+    // [status | shared operand | per slab: its input, its C]
+    const size_t shared_bytes = by_rows ? static_cast<size_t>(K) * (N / 4) : static_cast<size_t>(M) * K;
+    size_t off_in[HostPipe::kMaxSlabs], off_c[HostPipe::kMaxSlabs];
+    size_t total = 256 + up(shared_bytes);
+    for (int j = 0; j < n_slabs; ++j) {
+        const size_t ext = std::min(slab, extent - j * slab);
+        off_in[j] = total;
+        total += up(by_rows ? ext * K : static_cast<size_t>(K) * (ext / 4));
+        off_c[j] = total;
+        total += up((by_rows ? ext * N : static_cast<size_t>(M) * ext) * sizeof(int32_t));
+    }
+    cudaMemPool_t pool = nullptr;
+    rc = host_call_pool(&pool);
+    if (rc) return rc;
+    uint8_t* blob = nullptr;
+    cudaError_t e = cudaMallocFromPoolAsync(reinterpret_cast<void**>(&blob), total, pool, hp->s_run);
+    if (e != cudaSuccess) return cuda_fail(e);
+    int32_t* dS = reinterpret_cast<int32_t*>(blob);
+    uint8_t* d_shared = blob + 256;
+    int32_t h_status = 0;
+    do {
+        if ((e = cudaMemsetAsync(dS, 0, 4, hp->s_run)) != cudaSuccess) break;
+        if ((e = cudaEventRecord(hp->ev_alloc, hp->s_run)) != cudaSuccess) break;
+        if ((e = cudaStreamWaitEvent(hp->s_in, hp->ev_alloc, 0)) != cudaSuccess) break;
+        if ((e = cudaStreamWaitEvent(hp->s_out, hp->ev_alloc, 0)) != cudaSuccess) break;
+        // up: the first slab's own input, then the shared operand, then the other slabs
+        for (int j = 0; j < n_slabs && e == cudaSuccess; ++j) {
+            const int x0 = j * slab, ext = std::min(slab, extent - x0);
+            if (by_rows)
+                e = cudaMemcpyAsync(blob + off_in[j], A + static_cast<size_t>(x0) * K, static_cast<size_t>(ext) * K,
+                                    cudaMemcpyHostToDevice, hp->s_in);
+            else
+                e = cudaMemcpy2DAsync(blob + off_in[j], ext / 4, Wp + x0 / 4, N / 4, ext / 4, K, cudaMemcpyHostToDevice,
+                                      hp->s_in);
+            if (e == cudaSuccess) e = cudaEventRecord(hp->ev_w[j], hp->s_in);
+            if (j == 0 && e == cudaSuccess) {
+                e = cudaMemcpyAsync(d_shared, by_rows ? static_cast<const void*>(Wp) : static_cast<const void*>(A),
+                                    shared_bytes, cudaMemcpyHostToDevice, hp->s_in);
+                if (e == cudaSuccess) e = cudaEventRecord(hp->ev_a, hp->s_in);
+            }
+        }
+        if (e != cudaSuccess) break;
+        if ((e = cudaStreamWaitEvent(hp->s_run, hp->ev_a, 0)) != cudaSuccess) break;
+        for (int j = 0; j < n_slabs; ++j) {
+            const int x0 = j * slab, ext = std::min(slab, extent - x0);
+            int32_t* dCj = reinterpret_cast<int32_t*>(blob + off_c[j]);
+            if ((e = cudaStreamWaitEvent(hp->s_run, hp->ev_w[j], 0)) != cudaSuccess) break;
+            if (by_rows)
+                rc = ternix_b200_matmul_ex(reinterpret_cast<const int8_t*>(blob + off_in[j]), d_shared, dCj, ext, K, N, N,
+                                           kernel, dS, hp->s_run);
+            else
+                rc = ternix_b200_matmul_ex(reinterpret_cast<const int8_t*>(d_shared), blob + off_in[j], dCj, M, K, ext,
+                                           ext, kernel, dS, hp->s_run);
+            if (rc) break;
+            if ((e = cudaEventRecord(hp->ev_c[j], hp->s_run)) != cudaSuccess) break;
+            if ((e = cudaStreamWaitEvent(hp->s_out, hp->ev_c[j], 0)) != cudaSuccess) break;
+            if (by_rows)
+                e = cudaMemcpyAsync(C + static_cast<size_t>(x0) * N, dCj, static_cast<size_t>(ext) * N * 4,
+                                    cudaMemcpyDeviceToHost, hp->s_out);
+            else
+                e = cudaMemcpy2DAsync(C + x0, static_cast<size_t>(N) * 4, dCj, static_cast<size_t>(ext) * 4,
+                                      static_cast<size_t>(ext) * 4, M, cudaMemcpyDeviceToHost, hp->s_out);
+            if (e != cudaSuccess) break;
+        }
+        if (e != cudaSuccess || rc) break;
+        e = cudaMemcpyAsync(&h_status, dS, 4, cudaMemcpyDeviceToHost, hp->s_out);
+    } while (false);
+    // Whatever happened above, everything queued so far ends before the block goes back to the pool.
+    const cudaError_t e_in = cudaStreamSynchronize(hp->s_in);
+    const cudaError_t e_out = cudaStreamSynchronize(hp->s_out);
+    cudaFreeAsync(blob, hp->s_run);
+    const cudaError_t e_run = cudaStreamSynchronize(hp->s_run);
+    if (e == cudaSuccess) e = e_in;
+    if (e == cudaSuccess) e = e_out;
+    if (e == cudaSuccess) e = e_run;
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (rc) return rc;
+    return h_status ? h_status : TERNIX_B200_OK;
+}
+
+// Slab plan of a host-pointer product: the slab extent (0 = single-shot path) and whether slabs are rows.  About
+// 64 MB of C per slab, at most 16 slabs.  Column slabs (multiples of 512 columns, at least 4096 wide so that the
+// pitched copy of C keeps long rows) are taken when A is the smaller operand to wait for; row slabs (multiples of
+// 256 rows) otherwise.  TERNIX_B200_HOST_SLAB=<columns>, or r<rows>, overrides; 0 switches the pipeline off.
+int host_slab_plan(int M, int K, int N, bool* by_rows) {
+    *by_rows = false;
+    if (K <= 0 || (N % 64) != 0) return 0;
+    auto fit = [](long long extent, long long want, long long unit) {
+        long long v = std::max(unit, (want + unit - 1) / unit * unit);
+        while ((extent + v - 1) / v > HostPipe::kMaxSlabs) v += unit;
+        return v >= extent ? 0ll : v;
+    };
+    if (const char* env = std::getenv("TERNIX_B200_HOST_SLAB")) {
+        *by_rows = env[0] == 'r';
+        const long long want = std::atoll(env + (*by_rows ? 1 : 0));
+        if (want <= 0) return 0;
+        return static_cast<int>(*by_rows ? fit(M, want, 256) : fit(N, want, 512));
+    }
+    const size_t c_bytes = static_cast<size_t>(M) * N * sizeof(int32_t);
+    if (c_bytes < (size_t(64) << 20)) return 0;
+    const long long slabs = std::min<long long>(HostPipe::kMaxSlabs, std::max<long long>(2, c_bytes / (size_t(64) << 20)));
+    const bool a_smaller = static_cast<size_t>(M) * K <= static_cast<size_t>(K) * (N / 4);
+    if (a_smaller && N >= 8192) return static_cast<int>(fit(N, std::max<long long>(4096, (N + slabs - 1) / slabs), 512));
+    *by_rows = true;
+    return static_cast<int>(fit(M, (M + slabs - 1) / slabs, 256));
+}
+}  // namespace
+
+extern "C" {
+
 int ternix_b200_matmul_host(const int8_t* A, const uint8_t* Wp, int32_t* C, int M, int K, int N, int kernel) {
     if (M < 0 || K < 0 || N < 0 || (N % 4) != 0) return TERNIX_B200_ERR_INVALID_SHAPE;
     if (kernel < TERNIX_B200_KERNEL_AUTO || kernel > TERNIX_B200_KERNEL_GEMM_TC) return TERNIX_B200_ERR_INVALID_ARG;
     if (M == 0 || N == 0) return TERNIX_B200_OK;
     if (!C || (K > 0 && (!A || !Wp))) return TERNIX_B200_ERR_INVALID_ARG;
+    bool by_rows = false;
+    if (const int slab = host_slab_plan(M, K, N, &by_rows)) return matmul_host_pipelined(A, Wp, C, M, K, N, kernel, slab, by_rows);
     const size_t a_bytes = static_cast<size_t>(M) * K, w_bytes = static_cast<size_t>(K) * (N / 4),
                  c_bytes = static_cast<size_t>(M) * N * sizeof(int32_t);
     int8_t* dA = nullptr;

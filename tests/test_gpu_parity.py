@@ -479,3 +479,28 @@ def test_python_module_device_arrays():
         assert bool((wide[:, n:] == -9).all())
     with pytest.raises(ValueError):
         te.ternary_matmul(da, dw)                                  # device input without `out`
+
+
+# ---------------------------------------------------------------- host-pointer call, column-slab pipeline
+@pytest.mark.parametrize("slab", ["512", "1024", "r256", "0"])
+def test_host_call_pipelined_slabs(monkeypatch, slab):
+    """The host-pointer entry point cuts large products into column slabs on three streams; forced here on a small
+    product (ragged last slab included) and switched off, all against the oracle."""
+    monkeypatch.setenv("TERNIX_B200_HOST_SLAB", slab)
+    for (m, k, n) in [(300, 512, 2304), (129, 256, 1088), (5, 64, 1024)]:
+        a, wp = synth(m, k, n, 300 + m)
+        expect = oracle_lib.matmul(a, wp)
+        for _ in range(2):
+            assert_same(tb.ternary_matmul_host(a, wp), expect, f"host call, slab {slab}, {m}x{k}x{n}")
+
+
+def test_host_call_pipelined_default_threshold():
+    """Above 64 MB of output the pipeline is on by default: same result as the device-pointer call."""
+    import torch
+    for (m, k, n) in [(4096, 256, 4608), (1024, 128, 16384 + 64)]:      # row slabs; column slabs
+        a, wp = synth(m, k, n, 77)
+        dc = tb.matmul(torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda())
+        got = tb.ternary_matmul_host(a, wp)
+        assert_same(got, dc.cpu().numpy(), "pipelined host call vs device call")
+        rows = np.arange(0, m, 97)
+        assert_same(got[rows], oracle_lib.matmul(a[rows], wp), "pipelined host call vs oracle (row sample)")
