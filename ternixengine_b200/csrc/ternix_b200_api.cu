@@ -1018,7 +1018,7 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
                                static_cast<uint64_t>(q.N), 128, tb200::group_stage_rows(32) / 4)
             : make_tmap_2d(&gp.tmap_w, q.dW, static_cast<uint64_t>(q.N / 4), static_cast<uint64_t>(q.K),
                            static_cast<uint64_t>(q.N / 4), g->words * 4, tb200::group_stage_rows(g->words),
-                           CU_TENSOR_MAP_SWIZZLE_NONE);
+                           g->words == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc) { delete g; return rc; }
         gp.A = q.dA; gp.C = q.dC; gp.ldc = q.ldc; gp.M = q.M; gp.K = q.K; gp.N = q.N;
         const int pi = static_cast<int>(probs.size());
@@ -1281,7 +1281,7 @@ int ternix_b200_gemv_batch_noalloc(const ternix_b200_problem* problems, int coun
         gp = tb200::GroupProblem{};
         rc = make_tmap_2d(&gp.tmap_w, q.dW, static_cast<uint64_t>(q.N / 4), static_cast<uint64_t>(q.K),
                           static_cast<uint64_t>(q.N / 4), words * 4, tb200::group_stage_rows(words),
-                          CU_TENSOR_MAP_SWIZZLE_NONE);
+                          CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
         gp.A = q.dA; gp.C = q.dC; gp.ldc = q.ldc; gp.M = q.M; gp.K = q.K; gp.N = q.N;
         max_m = std::max(max_m, q.M);
