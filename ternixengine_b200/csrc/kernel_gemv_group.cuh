@@ -7,34 +7,34 @@
 // same TMA ring (8 stages of 8 KB) without draining it between items: per SM tens of KB are always in flight, which is what a 4 MB GEMV launched on
 // its own cannot do.  The per-problem TMA descriptors live in a table in global memory.
 //
-// This kernel is bound by integer instruction issue, not by HBM, so the decode is the leanest
-// exact form found:
-//   * 4x4 byte transpose of four k-rows' words (8 PRMT), as in ternary_gemv_kernel;
+// The decode is the leanest exact form found; with it the kernel runs at the memory system's pace while every SM
+// holds its four CTAs, and what is lost is lost to the coarse items (see "Balance" below).
+//   * The packed bytes of four k-rows of one byte column are brought together by the load itself:
+//     ldmatrix.m16n16.x2.trans.b8 reads a block of 16 k-rows x 32 packed bytes and hands lane l four registers, each
+//     holding the bytes of k-rows 4(l%4)..4(l%4)+3 of one byte column (columns l/4, l/4+8, 16+l/4, 24+l/4 of the
+//     block).  The stage is loaded with the TMA swizzle that matches its row length (128 or 64 bytes) so that the
+//     16-byte rows of a block fall in different banks.  A warp keeps one 128-column block of the item and walks two
+//     16-row blocks of every stage; four lanes and two or four warps share each column and meet in the
+//     shared-memory reduction.
 //   * T ^= 0xAAAAAAAA turns every 2-bit code c in {0,1,3} into c^2 in {2,3,1} = w + 2, so a field
 //     can be used IN PLACE, unsigned, with one AND and no shift or sign extension:
 //     dp4a.u32.s32(T & (0x03030303 << 2j), a) adds 4^j * sum_k a_k (w_k + 2);
 //   * the epilogue takes (acc >> 2j) - 2 * sum_k a_k.  The row sum of the activations is the same
 //     for every column and is computed once per item by one warp (dp4a against 0x01010101 and a
 //     warp-shuffle reduction).  Bound: 4^3 * 3 * 128 * K < 2^31, K <= 8192 here.
-//   45 integer instructions per 64 weights at M = 1 instead of 52.
-// With 64-byte rows (WORDS = 16) the two half-warps read k-rows in the orders 0,1,2,3 and 1,0,3,2 so that
-// their rows fall in different halves of the 32 banks; the activation bytes of the second half are
-// permuted to match.
+//   34 instructions per 64 weights at M = 1 (1 ldmatrix, 1 activation load, 16 LOP3, 16 dp4a).
 //
-// With 128-byte rows (WORDS = 32, the default) the byte transpose is done by the load itself:
-// ldmatrix.m16n16.x2.trans.b8 reads a block of 16 k-rows x 32 packed bytes and hands lane l four registers, each
-// holding the bytes of k-rows 4(l%4)..4(l%4)+3 of one byte column (columns l/4, l/4+8, 16+l/4, 24+l/4 of the
-// block).  That is exactly the transposed word the AND + dp4a part wants, so the 8 PRMT and 3 of the 4 loads go
-// away: 34 instructions per 64 weights, the same as with prepacked weights but on the reference's own format.
-// The stage is loaded with the 128-byte TMA swizzle so that the 16-byte rows of a block fall in different banks.
-// A warp keeps one 128-column block of the item (warp % 4) and walks the 16-row blocks warp/4 and warp/4 + 2 of
-// every 64-row stage; four lanes and two warps share each column and meet in the shared-memory reduction.
+// Balance.  Items are whole: a 512-column chunk over all of K.  64 projections of 2560 x 6912 are 6.05 items per SM,
+// so the last third of the launch runs with two CTAs per SM instead of four.  Cutting items along K to even this out
+// was tried and is slower: neighbouring CTAs then stop reading the same weight rows at the same time, and the
+// 128-byte row segments of a lone CTA no longer share DRAM pages with anybody's (4.3 TB/s instead of 6.8 TB/s in the
+// fully occupied phase).
 //
-// Prepacked weights (PRE = true, optional).  The byte transpose costs 8 of the 40 decode instructions and is
-// the same for every call, so it can be done once: ternix_b200_prepack_k4 stores, for every group of four
-// k-rows and every packed byte column, the four bytes of that column together in one 32-bit word (same size as
-// the packed matrix, K rounded up to a multiple of 4).  A lane then loads its four transposed words with one
-// 16-byte shared-memory load and goes straight to the AND + dp4a part: 32 instructions per 64 weights.
+// Prepacked weights (PRE = true, optional).  ternix_b200_prepack_k4 stores, for every group of four k-rows and
+// every packed byte column, the four bytes of that column together in one 32-bit word (same size as the packed
+// matrix, K rounded up to a multiple of 4), so that a lane loads its four transposed words with one 16-byte
+// shared-memory load.  It predates the transposing loads above and is no faster than them; it stays for callers
+// that already hold weights in that layout.
 //
 // Activations of the next item are prefetched with a 1-D bulk copy into the second of two
 // buffers while the current item is consumed; the per-item epilogue is one named barrier.
@@ -119,9 +119,8 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
     static_assert(!PRE || WORDS == 32, "prepacked weights use 512-column items");
     constexpr int kGroupStageRows = kGroupStageBytes / (WORDS * 4);
     constexpr int kGroupStages = MR <= 2 ? 4 : 8;               // = group_stages(MR)
-    constexpr int kHalves = 32 / WORDS;                 // k-groups a warp covers per load
     constexpr int kPartInts = MR * 16 * (WORDS + 1);
-    constexpr bool LDM = !PRE && WORDS == 32;           // transposing loads from a swizzled stage
+    constexpr bool LDM = !PRE;                          // transposing loads from a swizzled stage
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* stages = base;
@@ -191,20 +190,15 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
         }
     } else {
         // ------------------------------------------------------------ consumers
-        const int word = lane & (WORDS - 1);
-        const int half = lane / WORDS;                         // 64-byte rows: second half-warp reads rows 1,0,3,2
-        const int kg = warp * kHalves + half;                  // 4-row groups kg and kg + 8*kHalves of each stage
-        const uint32_t a_sel = half ? 0x2301u : 0x3210u;       // activation bytes in the same order
-        // byte offsets inside a stage of the four rows of this thread's first k-group, in load order
-        const uint32_t row_bytes = WORDS * 4;
-        const uint32_t o_base = (kg * 4) * row_bytes + word * 4;
-        const uint32_t o0 = o_base + half * row_bytes, o1 = o_base + (half ^ 1) * row_bytes;
-        const uint32_t o2 = o_base + (2 + half) * row_bytes, o3 = o_base + (3 - half) * row_bytes;
-        constexpr uint32_t kSecondGroup = 8 * kHalves * 4 * WORDS * 4;   // second k-group of the stage: 4 KB further
-        // transposing loads: 128-column block `cb`, 16-row blocks `kb0` and `kb0 + 2`; this lane's row address
-        // inside the swizzled stage (16-byte chunk index XOR row % 8) and its four k-rows inside a block
-        const int cb = warp & 3, kb0 = warp >> 2;
-        const uint32_t ldm_off = (kb0 * 16 + (lane & 15)) * 128 + ((((cb * 2 + (lane >> 4)) ^ (lane & 7)) & 7) << 4);
+        const int kg = warp;                                   // prepacked: 4-row groups kg and kg + 8 of each stage
+        // transposing loads: 128-column block `cb`, 16-row blocks `kb0` and `kb0 + (blocks per stage) / 2`; this lane's
+        // row address inside the swizzled stage and its four k-rows inside a block.  128-byte rows: 4 column blocks x
+        // 4 row blocks per stage, 16-byte chunk index ^= row % 8; 64-byte rows: 2 x 8, chunk index ^= (row / 2) % 4.
+        constexpr int kColBlocks = WORDS / 8;
+        const int cb = warp & (kColBlocks - 1), kb0 = warp / kColBlocks;
+        const int ldm_row = kb0 * 16 + (lane & 15);
+        const uint32_t ldm_swz = WORDS == 32 ? (ldm_row & 7) : ((ldm_row >> 1) & 3);
+        const uint32_t ldm_off = ldm_row * (WORDS * 4) + (((cb * 2 + (lane >> 4)) ^ ldm_swz) << 4);
         const int ldm_k = kb0 * 16 + 4 * (lane & 3);
         const uint32_t stages_sa = smem_u32(stages), a_sa = smem_u32(a_buf), part_sa = smem_u32(part);
         uint32_t t = 0;
@@ -249,21 +243,15 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
                         // row (4-k group) kg + 8g of the stage, this lane's four transposed words
                         const uint4 v = lds_v4(st + (kg + 8 * g) * (WORDS * 16) + lane * 16);
                         w[g][0] = v.x; w[g][1] = v.y; w[g][2] = v.z; w[g][3] = v.w;
-                    } else if constexpr (LDM) {
-                        ldmatrix_x2_trans_b8(w[g], st + ldm_off + g * 4096);
                     } else {
-                        w[g][0] = lds_u32(st + o0 + g * kSecondGroup);
-                        w[g][1] = lds_u32(st + o1 + g * kSecondGroup);
-                        w[g][2] = lds_u32(st + o2 + g * kSecondGroup);
-                        w[g][3] = lds_u32(st + o3 + g * kSecondGroup);
+                        ldmatrix_x2_trans_b8(w[g], st + ldm_off + g * 4096);       // second half of the stage: 4 KB on
                     }
-                    const int k = LDM ? tt * kGroupStageRows + ldm_k + 32 * g
-                                      : tt * kGroupStageRows + (kg + 8 * kHalves * g) * 4;
+                    const int k = LDM ? tt * kGroupStageRows + ldm_k + (kGroupStageRows / 2) * g
+                                      : tt * kGroupStageRows + (kg + 8 * g) * 4;
 #pragma unroll
                     for (int r = 0; r < MR; ++r) {
                         const uint32_t raw = lds_u32(a_sa + (buf * MR + r) * kGroupMaxK + k);
-                        const int ordered = static_cast<int>(kHalves > 1 ? __byte_perm(raw, 0, a_sel) : raw);
-                        a4[g][r] = k < K ? ordered : 0;                    // nothing beyond K
+                        a4[g][r] = k < K ? static_cast<int>(raw) : 0;      // nothing beyond K
                     }
                 }
                 __syncwarp();
@@ -271,18 +259,7 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
 
 #pragma unroll
                 for (int g = 0; g < 2; ++g) {
-                    uint32_t T[4];
-                    if constexpr (PRE || LDM) {
-                        T[0] = w[g][0]; T[1] = w[g][1]; T[2] = w[g][2]; T[3] = w[g][3];
-                    } else {
-                        const uint32_t x0 = w[g][0], x1 = w[g][1], x2 = w[g][2], x3 = w[g][3];
-                        const uint32_t lo01 = __byte_perm(x0, x1, 0x5140), hi01 = __byte_perm(x0, x1, 0x7362);
-                        const uint32_t lo23 = __byte_perm(x2, x3, 0x5140), hi23 = __byte_perm(x2, x3, 0x7362);
-                        T[0] = __byte_perm(lo01, lo23, 0x5410);
-                        T[1] = __byte_perm(lo01, lo23, 0x7632);
-                        T[2] = __byte_perm(hi01, hi23, 0x5410);
-                        T[3] = __byte_perm(hi01, hi23, 0x7632);
-                    }
+                    const uint32_t (&T)[4] = w[g];     // four transposed words: the bytes of 4 k-rows of one byte column each
 #pragma unroll
                     for (int b = 0; b < 4; ++b)
 #pragma unroll
@@ -307,7 +284,7 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
                         const int col = cb * 128 + (((c >> 2) & 1) * 8 + (c >> 3) * 16 + (lane >> 2)) * 4 + (c & 3);
                         red_shared_add(pt + ((r * 16 + (col & 15)) * (WORDS + 1) + (col >> 4)) * 4, acc[r][c]);
                     } else {
-                        red_shared_add(pt + ((r * 16 + c) * (WORDS + 1) + word) * 4, acc[r][c]);
+                        red_shared_add(pt + ((r * 16 + c) * (WORDS + 1) + lane) * 4, acc[r][c]);
                     }
                 }
             asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumerWarps * 32) : "memory");

@@ -969,9 +969,16 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
     if (!g) return TERNIX_B200_ERR_INVALID_ARG;
     if (cudaGetDevice(&g->device) != cudaSuccess) g->device = 0;
 
-    // Item width: 512 columns (128-byte rows) unless TERNIX_B200_GROUP_WORDS=16 asks for 256 (tuning aid).
-    g->words = 32;
+    // Item width: 256 columns (64-byte rows) when every decode member has one row: the finer items balance better
+    // over the SMs (measured +1..4 %); 512 columns (128-byte rows) for row groups, where the wider item wins.
+    // TERNIX_B200_GROUP_WORDS=16|32 overrides (tuning aid).
     g->prepacked = prepacked;
+    int decode_max_m = 0;
+    for (int i = 0; i < count; ++i)
+        if (problems[i].M > 0 && problems[i].N > 0 && group_gemv_ok(problems[i]) &&
+            !(problems[i].K > 0 && gemm_tc2_ok(problems[i].dA, problems[i].dW, problems[i].M, problems[i].K, problems[i].N)))
+            decode_max_m = std::max(decode_max_m, problems[i].M);
+    g->words = (!prepacked && decode_max_m == 1) ? 16 : 32;
     if (const char* env = std::getenv("TERNIX_B200_GROUP_WORDS")) g->words = (!prepacked && std::atoi(env) == 16) ? 16 : 32;
     const int item_cols = g->words * 16;
     std::vector<tb200::Tc2Problem> tc_probs;
@@ -1018,7 +1025,7 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
                                static_cast<uint64_t>(q.N), 128, tb200::group_stage_rows(32) / 4)
             : make_tmap_2d(&gp.tmap_w, q.dW, static_cast<uint64_t>(q.N / 4), static_cast<uint64_t>(q.K),
                            static_cast<uint64_t>(q.N / 4), g->words * 4, tb200::group_stage_rows(g->words),
-                           g->words == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
+                           g->words == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
         if (rc) { delete g; return rc; }
         gp.A = q.dA; gp.C = q.dC; gp.ldc = q.ldc; gp.M = q.M; gp.K = q.K; gp.N = q.N;
         const int pi = static_cast<int>(probs.size());

@@ -504,3 +504,35 @@ def test_host_call_pipelined_default_threshold():
         assert_same(got, dc.cpu().numpy(), "pipelined host call vs device call")
         rows = np.arange(0, m, 97)
         assert_same(got[rows], oracle_lib.matmul(a[rows], wp), "pipelined host call vs oracle (row sample)")
+
+
+# ---------------------------------------------------------------- decode batch: both item widths
+@pytest.mark.parametrize("words", ["32", "16"])
+@pytest.mark.parametrize("shapes", [
+    [(1, 2560, 6912)],
+    [(1, 8192, 512), (1, 8192, 64)],                          # deepest K
+    [(2, 2560, 640), (1, 4112, 1088), (2, 6912, 2560)],       # two-row groups, K not a multiple of the stage
+    [(5, 2560, 1152), (16, 1040, 576), (4, 6912, 512)],       # four-row groups, several row groups per chunk
+])
+def test_decode_batch_item_widths(monkeypatch, words, shapes):
+    """The persistent decode kernel with 512-column items (128-byte rows, the default) and 256-column items
+    (64-byte rows): transposing loads from a stage swizzled to match.  The oracle's bytes, run after run."""
+    import torch
+    monkeypatch.setenv("TERNIX_B200_GROUP_WORDS", words)
+    probs, expect = [], []
+    for i, (m, k, n) in enumerate(shapes):
+        a, wp = synth(m, k, n, 900 + 7 * i + m)
+        expect.append(torch.from_numpy(oracle_lib.matmul(a, wp)).cuda())
+        probs.append((torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda(),
+                      torch.empty((m, n), dtype=torch.int32, device="cuda")))
+    group = tb.ProjectionGroup(probs)
+    assert group.launches == 1
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    bad = 0
+    for _ in range(10):
+        for p in probs:
+            p[2].fill_(-7)
+        group.run(status=status)
+        bad += sum(int(bool((p[2] != e).any())) for p, e in zip(probs, expect))
+    assert int(status.item()) == 0 and bad == 0
+    group.close()
