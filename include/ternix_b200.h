@@ -39,6 +39,8 @@ extern "C" {
 #define TERNIX_B200_KERNEL_GENERIC  1  /* any M, K; N % 4 == 0; any pitch or alignment                */
 #define TERNIX_B200_KERNEL_GEMV     2  /* decode regime, M <= 16: TMA-streamed packed W, dp4a         */
 #define TERNIX_B200_KERNEL_GEMM_TC  3  /* prefill regime: TMA + tcgen05 kind::i8, int32 in TMEM       */
+#define TERNIX_B200_KERNEL_DECODE_MMA 4 /* batched decode (a few to a few dozen rows): TMA-streamed   */
+                                       /* packed W decoded in registers into mma.sync.m16n8k32       */
 
 const char *ternix_b200_status_string(int status);
 /* cudaError_t (as int) of the last failing CUDA call made by the calling thread, 0 if none. */

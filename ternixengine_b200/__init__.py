@@ -36,7 +36,9 @@ KERNEL_AUTO = 0
 KERNEL_GENERIC = 1
 KERNEL_GEMV = 2
 KERNEL_GEMM_TC = 3
-KERNELS = {"auto": KERNEL_AUTO, "generic": KERNEL_GENERIC, "gemv": KERNEL_GEMV, "gemm_tc": KERNEL_GEMM_TC}
+KERNEL_DECODE_MMA = 4
+KERNELS = {"auto": KERNEL_AUTO, "generic": KERNEL_GENERIC, "gemv": KERNEL_GEMV, "gemm_tc": KERNEL_GEMM_TC,
+           "decode_mma": KERNEL_DECODE_MMA}
 
 # every symbol include/ternix_b200.h declares
 EXPORTS = (

@@ -52,6 +52,7 @@ int kernel_of(const std::string& impl, size_t N) {
     if (impl == "b200_generic") return TERNIX_B200_KERNEL_GENERIC;
     if (impl == "b200_gemv") return TERNIX_B200_KERNEL_GEMV;
     if (impl == "b200_gemm_tc") return TERNIX_B200_KERNEL_GEMM_TC;
+    if (impl == "b200_decode_mma") return TERNIX_B200_KERNEL_DECODE_MMA;
     throw std::invalid_argument("unknown impl '" + impl + "'");
 }
 

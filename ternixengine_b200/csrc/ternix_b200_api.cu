@@ -19,6 +19,7 @@
 #include "kernel_gemm_tc2.cuh"
 #include "kernel_gemm_tc2w.cuh"
 #include "kernel_gemv.cuh"
+#include "kernel_decode_mma.cuh"
 #include "kernel_gemv_group.cuh"
 #include "kernel_generic.cuh"
 
@@ -132,11 +133,37 @@ bool gemm_tc_ok(const void* dA, const void* dW, int K, int N) {
     return (N % 64) == 0 && (K % 16) == 0 && aligned(dA, 16) && aligned(dW, 16) && K <= kMaxScaledK;
 }
 
+// Members of a problem group with this many rows go to the mma.sync decode kernel (one row: the dp4a kernel;
+// more: tcgen05 tiles).  Measured on 210 BitNet-2B projections per launch: 2 rows 116 us with dp4a row groups
+// against 97 us here, 16 rows 732 us against 148 us.
+constexpr int kGroupMmaMinRows = 2, kGroupMmaMaxRows = 64;
+
+// Batched decode on the warp-level tensor instruction: row groups of 8 or 16, any M >= 1.
+bool decode_mma_ok(const void* dA, const void* dW, int M, int K, int N) {
+    return M >= 1 && (N % 64) == 0 && (K % 16) == 0 && K >= 16 && K <= 65536 && aligned(dA, 16) && aligned(dW, 16);
+}
+// Rows from which the automatic choice prefers it to the one-row kernel's row groups, and up to which it prefers it
+// to the tcgen05 tiles (TERNIX_B200_MMA_ROWS="lo,hi" overrides; tuning aid).
+void decode_mma_rows(int* lo, int* hi) {
+    static int s_lo = 0, s_hi = 0;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        s_lo = 2;
+        s_hi = 64;
+        if (const char* env = std::getenv("TERNIX_B200_MMA_ROWS")) std::sscanf(env, "%d,%d", &s_lo, &s_hi);
+    });
+    *lo = s_lo;
+    *hi = s_hi;
+}
+
 bool gemm_tc2_ok(const void* dA, const void* dW, int M, int K, int N) {
     return gemm_tc_ok(dA, dW, K, N) && M > 128 && N >= 256;
 }
 
 int select_kernel(const void* dA, const void* dW, int M, int K, int N) {
+    int mma_lo = 0, mma_hi = 0;
+    decode_mma_rows(&mma_lo, &mma_hi);
+    if (M >= mma_lo && M <= mma_hi && decode_mma_ok(dA, dW, M, K, N)) return TERNIX_B200_KERNEL_DECODE_MMA;
     if (gemv_ok(dW, M, K, N)) return TERNIX_B200_KERNEL_GEMV;
     if (gemm_tc_ok(dA, dW, K, N)) return TERNIX_B200_KERNEL_GEMM_TC;
     return TERNIX_B200_KERNEL_GENERIC;
@@ -243,6 +270,122 @@ int launch_gemv(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, 
     if (M == 2) return TB_GEMV(2, 16);
     return TB_GEMV(4, 16);
 #undef TB_GEMV
+}
+
+
+// ---------------------------------------------------------------- batched decode on mma.sync (kernel_decode_mma.cuh)
+int make_mma_problem(tb200::MmaProblem* out, const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N,
+                     long long ldc) {
+    *out = tb200::MmaProblem{};
+    int rc = make_tmap_2d(&out->tmap_w, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K),
+                          static_cast<uint64_t>(N / 4), tb200::kMmaItemCols / 4, tb200::kMmaStageRows,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = make_tmap_2d(&out->tmap_a, dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), 64,
+                      tb200::kMmaBoxRows, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+    out->C = dC;
+    out->ldc = ldc;
+    out->M = M;
+    out->K = K;
+    out->N = N;
+    out->c_vec_ok = (ldc % 4 == 0) && aligned(dC, 16);
+    return TERNIX_B200_OK;
+}
+
+template <bool kSingle, int NG>
+int decode_mma_attr() {
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(tb200::ternary_decode_mma_kernel<kSingle, NG>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tb200::kMmaSmemBytes));
+    });
+    return attr_err == cudaSuccess ? TERNIX_B200_OK : cuda_fail(attr_err);
+}
+
+// One problem: items enumerated in the kernel.  When whole-K items would leave most of the GPU idle the K range is
+// cut into slices that add into a zeroed C (TERNIX_B200_MMA_SLICES=<n> forces the slice count; tuning aid).
+template <int NG>
+int launch_decode_mma_t(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,
+                        int32_t* d_status, cudaStream_t st) {
+    tb200::MmaProblem prob;
+    int rc = make_mma_problem(&prob, dA, dW, dC, M, K, N, ldc);
+    if (rc) return rc;
+    if ((rc = decode_mma_attr<true, NG>())) return rc;
+    auto kern = tb200::ternary_decode_mma_kernel<true, NG>;
+    tb200::MmaSingle sg{};
+    sg.group_rows = 8 * NG;
+    sg.chunks = (N + tb200::kMmaItemCols - 1) / tb200::kMmaItemCols;
+    sg.row_groups = (M + sg.group_rows - 1) / sg.group_rows;
+    sg.total_tiles = (K + tb200::kMmaStageRows - 1) / tb200::kMmaStageRows;
+    const int resident = sm_count() * tb200::kMmaCtasPerSm;
+    const int base_items = sg.chunks * sg.row_groups;
+    // Slices of K buy parallelism (a lone CTA streams about 23 GB/s) and cost one red.global.add per output and
+    // slice (the L2 retires about 160 of them per ns), plus the zeroing of C.  Take the count with the smallest sum.
+    int slices = 1;
+    {
+        const double w_bytes = static_cast<double>(K) * (N / 4) * sg.row_groups;
+        double best = 0;
+        const int max_slices = std::max(1, std::min(sg.total_tiles / 2, resident / std::max(1, base_items)));
+        for (int sl = 1; sl <= max_slices; ++sl) {
+            const int ctas = std::min(resident, base_items * sl);
+            const double stream_ns = std::max(w_bytes / (ctas * 23.0), w_bytes / 6000.0);
+            const double add_ns = sl > 1 ? 2000.0 + static_cast<double>(M) * N * sl / 160.0 : 0.0;
+            const double total = stream_ns + add_ns;
+            if (sl == 1 || total < best) { best = total; slices = sl; }
+        }
+    }
+    if (const char* env = std::getenv("TERNIX_B200_MMA_SLICES")) slices = std::max(1, std::min(std::atoi(env), sg.total_tiles));
+    // Cluster form: the largest cluster that still leaves one item per resident CTA (TERNIX_B200_MMA_CLUSTER=0|2|4|8
+    // overrides; tuning aid).
+    int cluster = 0;
+    for (int c : {8, 4, 2})
+        if (base_items * c <= resident && sg.total_tiles >= 2 * c) { cluster = c; break; }
+    if (const char* env = std::getenv("TERNIX_B200_MMA_CLUSTER")) {
+        const int c = std::atoi(env);
+        cluster = ((c == 2 || c == 4 || c == 8) && base_items * c <= resident) ? c : 0;
+    } else if (std::getenv("TERNIX_B200_MMA_SLICES")) {
+        cluster = 0;
+    }
+    if (cluster) {
+        sg.cluster = cluster;
+        sg.slices = cluster;
+        sg.tiles_per_slice = (sg.total_tiles + cluster - 1) / cluster;
+        sg.add = 0;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(static_cast<unsigned>(base_items * cluster));
+        cfg.blockDim = dim3(tb200::kMmaThreads);
+        cfg.dynamicSmemBytes = tb200::kMmaSmemBytes;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = static_cast<unsigned>(cluster);
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const tb200::MmaProblem* no_probs = nullptr;
+        const tb200::MmaItem* no_items = nullptr;
+        const int* no_first = nullptr;
+        TB_CUDA(cudaLaunchKernelEx(&cfg, kern, prob, sg, no_probs, no_items, no_first, d_status));
+        return TERNIX_B200_OK;
+    }
+    sg.tiles_per_slice = (sg.total_tiles + slices - 1) / slices;
+    sg.slices = (sg.total_tiles + sg.tiles_per_slice - 1) / sg.tiles_per_slice;
+    sg.add = sg.slices > 1;
+    if (sg.add) TB_CUDA(cudaMemset2DAsync(dC, static_cast<size_t>(ldc) * 4, 0, static_cast<size_t>(N) * 4, M, st));
+    const int grid = std::min(resident, base_items * sg.slices);
+    kern<<<grid, tb200::kMmaThreads, tb200::kMmaSmemBytes, st>>>(prob, sg, nullptr, nullptr, nullptr, d_status);
+    TB_CUDA(cudaGetLastError());
+    return TERNIX_B200_OK;
+}
+
+// Row groups of 8 up to 8 rows (half the tensor instructions), of 16 beyond.
+int launch_decode_mma(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,
+                      int32_t* d_status, cudaStream_t st) {
+    if (M <= 8) return launch_decode_mma_t<1>(dA, dW, dC, M, K, N, ldc, d_status, st);
+    return launch_decode_mma_t<2>(dA, dW, dC, M, K, N, ldc, d_status, st);
 }
 
 template <int BN>
@@ -439,6 +582,15 @@ struct ternix_b200_group {
     const int* d_tc_first = nullptr;
     int tc_pairs = 0;
     size_t tc_grouped = 0;
+    // batched-decode members (3 to 64 rows): one launch of the mma.sync kernel per row-group size (8, 16)
+    struct MmaTables {
+        void* d_blob = nullptr;                 // [MmaProblem[] | MmaItem[] | int cta_first[]]
+        const tb200::MmaProblem* d_probs = nullptr;
+        const tb200::MmaItem* d_items = nullptr;
+        const int* d_first = nullptr;
+        int grid = 0;
+    } mma[2];
+    size_t mma_grouped = 0;
     // members the grouped kernels could not take but that have peer destinations: copied after their launch
     struct PeerCopy { ternix_b200_problem q; std::vector<int32_t*> peers; };
     std::vector<PeerCopy> single_peers;
@@ -685,7 +837,7 @@ int ternix_b200_matmul_ex(const int8_t* dA, const uint8_t* dW, int32_t* dC, int 
     // tests/test_cuda_matmul.cu:41-43).
     if (M < 0 || K < 0 || N < 0 || (N % 4) != 0) return TERNIX_B200_ERR_INVALID_SHAPE;
     if (ldc < N) return TERNIX_B200_ERR_INVALID_ARG;
-    if (kernel < TERNIX_B200_KERNEL_AUTO || kernel > TERNIX_B200_KERNEL_GEMM_TC) return TERNIX_B200_ERR_INVALID_ARG;
+    if (kernel < TERNIX_B200_KERNEL_AUTO || kernel > TERNIX_B200_KERNEL_DECODE_MMA) return TERNIX_B200_ERR_INVALID_ARG;
     if (M == 0 || N == 0) return TERNIX_B200_OK;
     if (!dC || (K > 0 && (!dA || !dW))) return TERNIX_B200_ERR_INVALID_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -701,6 +853,9 @@ int ternix_b200_matmul_ex(const int8_t* dA, const uint8_t* dW, int32_t* dC, int 
         case TERNIX_B200_KERNEL_GEMM_TC:
             if (!gemm_tc_ok(dA, dW, K, N)) return TERNIX_B200_ERR_UNSUPPORTED;
             return launch_gemm_tc(dA, dW, dC, M, K, N, ldc, d_status, st);
+        case TERNIX_B200_KERNEL_DECODE_MMA:
+            if (!decode_mma_ok(dA, dW, M, K, N)) return TERNIX_B200_ERR_UNSUPPORTED;
+            return launch_decode_mma(dA, dW, dC, M, K, N, ldc, d_status, st);
         default:
             return launch_generic(dA, dW, dC, M, K, N, ldc, st);
     }
@@ -875,7 +1030,7 @@ extern "C" {
 
 int ternix_b200_matmul_host(const int8_t* A, const uint8_t* Wp, int32_t* C, int M, int K, int N, int kernel) {
     if (M < 0 || K < 0 || N < 0 || (N % 4) != 0) return TERNIX_B200_ERR_INVALID_SHAPE;
-    if (kernel < TERNIX_B200_KERNEL_AUTO || kernel > TERNIX_B200_KERNEL_GEMM_TC) return TERNIX_B200_ERR_INVALID_ARG;
+    if (kernel < TERNIX_B200_KERNEL_AUTO || kernel > TERNIX_B200_KERNEL_DECODE_MMA) return TERNIX_B200_ERR_INVALID_ARG;
     if (M == 0 || N == 0) return TERNIX_B200_OK;
     if (!C || (K > 0 && (!A || !Wp))) return TERNIX_B200_ERR_INVALID_ARG;
     bool by_rows = false;
@@ -977,11 +1132,12 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
     for (int i = 0; i < count; ++i)
         if (problems[i].M > 0 && problems[i].N > 0 && group_gemv_ok(problems[i]) &&
             !(problems[i].K > 0 && gemm_tc2_ok(problems[i].dA, problems[i].dW, problems[i].M, problems[i].K, problems[i].N)))
-            decode_max_m = std::max(decode_max_m, problems[i].M);
+            if (prepacked || problems[i].M < kGroupMmaMinRows) decode_max_m = std::max(decode_max_m, problems[i].M);
     g->words = (!prepacked && decode_max_m == 1) ? 16 : 32;
     if (const char* env = std::getenv("TERNIX_B200_GROUP_WORDS")) g->words = (!prepacked && std::atoi(env) == 16) ? 16 : 32;
     const int item_cols = g->words * 16;
     std::vector<tb200::Tc2Problem> tc_probs;
+    std::vector<tb200::MmaProblem> mma_probs[2];          // row groups of 8, of 16
     std::vector<tb200::GroupProblem> probs;
     struct HostItem { tb200::GroupItem item; long cost; };
     std::vector<HostItem> items;
@@ -1017,6 +1173,15 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
             ternix_b200_group::PeerCopy pc{q, {}};
             for (int j = 0; j < n_peers; ++j) pc.peers.push_back(peer_dC[static_cast<size_t>(i) * n_peers + j]);
             g->single_peers.push_back(pc);
+        }
+        if (!prepacked && q.M >= kGroupMmaMinRows && q.M <= kGroupMmaMaxRows && q.K > 0 && q.ldc >= q.N &&
+            decode_mma_ok(q.dA, q.dW, q.M, q.K, q.N)) {
+            tb200::MmaProblem mp;
+            const int rc = make_mma_problem(&mp, q.dA, q.dW, q.dC, q.M, q.K, q.N, q.ldc);
+            if (rc) { delete g; return rc; }
+            mma_probs[q.M <= 8 ? 0 : 1].push_back(mp);
+            ++g->mma_grouped;
+            continue;
         }
         if (!group_gemv_ok(q)) { g->singles.push_back(q); continue; }
         tb200::GroupProblem gp{};
@@ -1129,6 +1294,57 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
         g->d_tc_first = reinterpret_cast<const int*>(d + b_probs + b_tiles);
         g->tc_pairs = pairs;
     }
+    for (int v = 0; v < 2; ++v) {
+        if (mma_probs[v].empty()) continue;
+        // whole-K items, deepest K first, each to the least-loaded CTA: with equal costs this deals the items out in
+        // order, so that neighbouring CTAs read the same weight rows of neighbouring chunks at the same time
+        const int group_rows = v == 0 ? 8 : 16;
+        struct HostMmaItem { tb200::MmaItem item; long cost; };
+        std::vector<HostMmaItem> hi;
+        for (int pi = 0; pi < static_cast<int>(mma_probs[v].size()); ++pi) {
+            const tb200::MmaProblem& mp = mma_probs[v][pi];
+            const int chunks = (mp.N + tb200::kMmaItemCols - 1) / tb200::kMmaItemCols;
+            for (int row0 = 0; row0 < mp.M; row0 += group_rows)
+                for (int c = 0; c < chunks; ++c) hi.push_back({{pi, c, row0, 0}, static_cast<long>(mp.K) + 256});
+        }
+        const int ctas = static_cast<int>(std::min<size_t>(hi.size(), static_cast<size_t>(sm_count()) * tb200::kMmaCtasPerSm));
+        std::stable_sort(hi.begin(), hi.end(), [](const HostMmaItem& a, const HostMmaItem& b) { return a.cost > b.cost; });
+        using Load = std::pair<long, int>;
+        std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
+        for (int c = 0; c < ctas; ++c) heap.push({0, c});
+        std::vector<std::vector<tb200::MmaItem>> per_cta(ctas);
+        for (const HostMmaItem& h : hi) {
+            Load l = heap.top();
+            heap.pop();
+            per_cta[l.second].push_back(h.item);
+            heap.push({l.first + h.cost, l.second});
+        }
+        std::vector<tb200::MmaItem> flat;
+        std::vector<int> first(ctas + 1, 0);
+        for (int c = 0; c < ctas; ++c) {
+            first[c] = static_cast<int>(flat.size());
+            flat.insert(flat.end(), per_cta[c].begin(), per_cta[c].end());
+        }
+        first[ctas] = static_cast<int>(flat.size());
+        const size_t b_probs = mma_probs[v].size() * sizeof(tb200::MmaProblem);
+        const size_t b_items = (flat.size() * sizeof(tb200::MmaItem) + 63) & ~size_t(63);
+        const size_t b_first = first.size() * sizeof(int);
+        auto& mt = g->mma[v];
+        cudaError_t e = cudaMalloc(&mt.d_blob, b_probs + b_items + b_first);
+        if (e != cudaSuccess) { ternix_b200_group_destroy(g); return cuda_fail(e); }
+        uint8_t* d = static_cast<uint8_t*>(mt.d_blob);
+        if ((e = cudaMemcpy(d, mma_probs[v].data(), b_probs, cudaMemcpyHostToDevice)) != cudaSuccess ||
+            (e = cudaMemcpy(d + b_probs, flat.data(), flat.size() * sizeof(tb200::MmaItem), cudaMemcpyHostToDevice)) !=
+                cudaSuccess ||
+            (e = cudaMemcpy(d + b_probs + b_items, first.data(), b_first, cudaMemcpyHostToDevice)) != cudaSuccess) {
+            ternix_b200_group_destroy(g);
+            return cuda_fail(e);
+        }
+        mt.d_probs = reinterpret_cast<const tb200::MmaProblem*>(d);
+        mt.d_items = reinterpret_cast<const tb200::MmaItem*>(d + b_probs);
+        mt.d_first = reinterpret_cast<const int*>(d + b_probs + b_items);
+        mt.grid = ctas;
+    }
     *out = g;
     return TERNIX_B200_OK;
 }
@@ -1191,6 +1407,21 @@ int ternix_b200_group_run(const ternix_b200_group* g, int32_t* d_status, void* s
         const int rc = launch_gemm_tc2_group(g, d_status, st);
         if (rc) return rc;
     }
+    for (int v = 0; v < 2; ++v) {
+        const auto& mt = g->mma[v];
+        if (mt.grid == 0) continue;
+        int rc = v == 0 ? decode_mma_attr<false, 1>() : decode_mma_attr<false, 2>();
+        if (rc) return rc;
+        const tb200::MmaProblem none{};
+        const tb200::MmaSingle sg{};
+        if (v == 0)
+            tb200::ternary_decode_mma_kernel<false, 1><<<mt.grid, tb200::kMmaThreads, tb200::kMmaSmemBytes, st>>>(
+                none, sg, mt.d_probs, mt.d_items, mt.d_first, d_status);
+        else
+            tb200::ternary_decode_mma_kernel<false, 2><<<mt.grid, tb200::kMmaThreads, tb200::kMmaSmemBytes, st>>>(
+                none, sg, mt.d_probs, mt.d_items, mt.d_first, d_status);
+        TB_CUDA(cudaGetLastError());
+    }
     for (const ternix_b200_problem& q : g->singles) {
         const int rc = ternix_b200_matmul_ex(q.dA, q.dW, q.dC, q.M, q.K, q.N, q.ldc, TERNIX_B200_KERNEL_AUTO, d_status,
                                              stream);
@@ -1205,13 +1436,16 @@ int ternix_b200_group_run(const ternix_b200_group* g, int32_t* d_status, void* s
 
 int ternix_b200_group_launches(const ternix_b200_group* g) {
     if (!g) return 0;
-    return (g->grid > 0 ? 1 : 0) + (g->tc_pairs > 0 ? 1 : 0) + static_cast<int>(g->singles.size());
+    return (g->grid > 0 ? 1 : 0) + (g->tc_pairs > 0 ? 1 : 0) + (g->mma[0].grid > 0 ? 1 : 0) + (g->mma[1].grid > 0 ? 1 : 0) +
+           static_cast<int>(g->singles.size());
 }
 
 void ternix_b200_group_destroy(ternix_b200_group* g) {
     if (!g) return;
     if (g->d_blob) cudaFree(g->d_blob);
     if (g->d_tc_blob) cudaFree(g->d_tc_blob);
+    for (auto& mt : g->mma)
+        if (mt.d_blob) cudaFree(mt.d_blob);
     delete g;
 }
 

@@ -38,6 +38,8 @@ def kernels_for(M, K, N):
         ks.append("gemv")
     if N % 64 == 0 and K % 16 == 0:
         ks.append("gemm_tc")
+        if K >= 16:
+            ks.append("decode_mma")
     return ks + ["auto"]
 
 
@@ -100,8 +102,31 @@ def test_gemv_every_split_plan(plan, monkeypatch):
 def test_config2_skinny_gemm():
     a, wp = synth(32, 4096, 11008, 21, lo=-127)
     expect = oracle_lib.matmul(a, wp)
-    for kern in ("gemm_tc", "generic", "auto"):
+    for kern in ("gemm_tc", "decode_mma", "generic", "auto"):
         assert_same(device_matmul(a, wp, kern), expect, f"config2 [{kern}]")
+    assert tb.select_kernel(32, 4096, 11008) == tb.KERNELS["decode_mma"]
+
+
+@pytest.mark.parametrize("slices", ["", "SLICES=1", "SLICES=3", "SLICES=1000", "CLUSTER=0", "CLUSTER=2", "CLUSTER=4",
+                                    "CLUSTER=8"])
+def test_decode_mma_rows_slices_and_edges(monkeypatch, slices):
+    """Batched decode on mma.sync: every row count of a row group and across row groups, K not a multiple of the
+    64-row stage, column tails, unaligned and padded C, the largest magnitudes; with the automatic plan, with forced
+    K-slice counts (whole-K stores and sliced adds into a zeroed C) and with forced cluster sizes (slices reduced
+    through distributed shared memory, some of them empty)."""
+    if slices:
+        key, value = slices.split("=")
+        monkeypatch.setenv("TERNIX_B200_MMA_" + key, value)
+    for (m, k, n, pad) in [(1, 64, 64, 0), (2, 2560, 6912, 0), (3, 1040, 320, 1), (7, 4112, 1088, 0), (15, 16, 64, 3),
+                           (16, 6912, 2560, 0), (17, 272, 576, 0), (33, 8192, 128, 4), (64, 1024, 2112, 0),
+                           (100, 144, 704, 0)]:
+        a, wp = synth(m, k, n, 40 + m + k)
+        assert_same(device_matmul(a, wp, "decode_mma", pad_cols=pad), oracle_lib.matmul(a, wp),
+                    f"decode_mma slices={slices!r} {m}x{k}x{n} pad {pad}")
+    m, k, n = 16, 8192, 512
+    a = np.full((m, k), -128, dtype=np.int8)
+    wp = tb.pack_ternary(np.full((k, n), -1, dtype=np.int8))
+    assert_same(device_matmul(a, wp, "decode_mma"), np.full((m, n), 128 * k, dtype=np.int32), "decode_mma worst case")
 
 
 @pytest.mark.parametrize("bn", ["128", "256", "2", "2w"])
@@ -267,7 +292,9 @@ def test_projection_group_mixed_rows_and_fallbacks(M):
         probs.append((torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda(), wide[:, :n]))
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     group = tb.ProjectionGroup(probs)
-    assert group.launches == 1 + 3           # the ragged, the M=64 and the K>8192 members run on their own
+    # one-row member: dp4a kernel; 2..64 rows: one mma.sync launch per row-group size (8: M <= 8, 16: the M = 64
+    # member and M = 16); the member with ragged K and N runs on its own
+    assert group.launches == (4 if M <= 8 else 3)
     group.run(status=status)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
@@ -526,7 +553,8 @@ def test_decode_batch_item_widths(monkeypatch, words, shapes):
         probs.append((torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda(),
                       torch.empty((m, n), dtype=torch.int32, device="cuda")))
     group = tb.ProjectionGroup(probs)
-    assert group.launches == 1
+    rows = [m for (m, _, _) in shapes]          # one launch per kernel in use: dp4a (1 row), mma.sync (2..8, 9..64 rows)
+    assert group.launches == any(m == 1 for m in rows) + any(2 <= m <= 8 for m in rows) + any(m > 8 for m in rows)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     bad = 0
     for _ in range(10):
