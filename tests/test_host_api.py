@@ -107,8 +107,11 @@ def test_shard_plan_partitions_columns(N, world, granule):
 def test_kernel_selection_by_shape_and_alignment():
     sel = tb.select_kernel
     assert sel(1, 2560, 6912) == tb.KERNEL_GEMV
-    assert sel(16, 4096, 11008) == tb.KERNEL_GEMV
-    assert sel(32, 4096, 11008) == tb.KERNEL_GEMM_TC
+    assert sel(16, 4096, 11008) == tb.KERNEL_DECODE_MMA
+    assert sel(32, 4096, 11008) == tb.KERNEL_DECODE_MMA                 # config 2
+    assert sel(64, 4096, 11008) == tb.KERNEL_DECODE_MMA
+    assert sel(65, 4096, 11008) == tb.KERNEL_GEMM_TC
+    assert sel(4, 2560, 6912, a_ptr=8) == tb.KERNEL_GEMV                # small M, A not 16-byte aligned: no TMA view of A
     assert sel(4096, 8192, 28672) == tb.KERNEL_GEMM_TC
     for (m, k, n) in [(1, 3001, 1028), (7, 129, 4), (37, 4099, 2052), (255, 2561, 6916)]:
         assert sel(m, k, n) == tb.KERNEL_GENERIC                        # packed rows are not 16-byte multiples
