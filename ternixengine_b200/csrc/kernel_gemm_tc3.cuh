@@ -1,0 +1,329 @@
+// Prefill-regime kernel, paired CTAs, weights as the tensor-core A operand in tensor memory.
+//
+// The other tcgen05 kernels of this library expand every packed weight byte into four int8 bytes of shared
+// memory, in the canonical operand layout, before the tensor core can read them; that expansion (shared-memory
+// stores, proxy fences, a second ring) is what bounds them.  tcgen05.mma can also take its A operand from tensor
+// memory, where row i of A sits in lane i and four K-bytes fill one 32-bit column.  So this kernel computes the
+// product transposed,
+//     C^T[n][m] = sum_k W[k][n] * A[m][k],
+// with the weights as the A operand and the activations, untouched, as the B operand:
+//   * activations: 128 rows x 128 K-bytes per CTA and stage, straight from TMA into the K-major 128-byte-swizzle
+//     layout the B descriptor reads (the pair's two halves make the N = 256 columns of the instruction);
+//   * weights: 128 k-rows x 32 packed bytes per CTA and stage (its 128 weight columns), TMA with the 32-byte
+//     swizzle.  An expander warp reads them with ldmatrix.m16n16.x2.trans.b8, which leaves four consecutive K-bytes
+//     of one byte column in one register.  Lane L of the operand is weight column L of the CTA's 128, i.e. byte
+//     column L / 4, field L % 4, so the warp of lane quarter q needs byte columns 8q .. 8q+7 in all four fields:
+//     eight shuffles per 32-deep group bring each lane the registers of its rows, one variable shift and three ALU
+//     operations decode its field (2-bit code -> int8 -1/0/+1), and tcgen05.st.16x128b writes them to tensor
+//     memory.  Nothing expanded ever touches shared memory: per CTA and 128-deep k-block the expanders execute a
+//     few hundred instructions in all, and the ring holds 20 KB per stage instead of 56 KB.
+//   * epilogue: lane = weight column, tensor-memory column = activation row.  A step moves 32 activation rows x
+//     128 columns into a staging buffer in shared memory, row-major as in C (a warp writes 128 contiguous bytes per
+//     row), and one thread hands the buffer to the TMA unit as a tensor store.  The accumulator is released as soon
+//     as it has been read; the stores to global memory, whose rate per SM (about 30 GB/s) is what an epilogue out
+//     of registers has to wait for, run in the background under the next tile's MMAs.
+//
+// Tensor memory (512 columns per CTA): columns 0-255 the accumulator (128 weight columns x 256 activation rows,
+// int32, single-buffered), columns 256-511 the A ring: up to 8 stages x 32 columns (128 K-bytes per lane).
+//
+// Roles per CTA (warps): 0 TMA producer; 1 MMA issuer (leader CTA only: four M=256 N=256 K=32 pair MMAs per
+// stage, commit -> `empty` of both CTAs); 2-9 expanders (lane quarter = warp % 4, two warps per quarter share the
+// stage's four 32-deep groups; after tcgen05.wait::st they arrive on the leader's `ready`, which therefore also
+// says that this CTA's activation tile has landed); 10-17 epilogue, two groups of four that take alternate steps.
+//
+// Exactness: int8 x int8 -> int32 on decoded -1/0/+1 weights, no scaling; any K the tensor maps can describe.
+#pragma once
+#include <cuda.h>
+#include <cstdint>
+#include "kernel_gemm_tc2.cuh"
+
+namespace tb200 {
+
+#ifndef TB200_TC3_STAGES
+#define TB200_TC3_STAGES 6
+#endif
+constexpr int kTc3Stages = TB200_TC3_STAGES;
+constexpr int kTc3TileW = 256;                    // weight columns per pair (128 per CTA)
+constexpr int kTc3TileA = 256;                    // activation rows per pair (128 loaded per CTA)
+constexpr int kTc3ActBytes = 128 * kTcBK;         // 16384
+constexpr int kTc3WpRowBytes = 32;
+constexpr int kTc3WpBytes = kTcBK * kTc3WpRowBytes;          // 4096
+constexpr int kTc3StageBytes = kTc3ActBytes + kTc3WpBytes;   // 20480
+constexpr uint32_t kTc3AccCols = 256, kTc3ARingCol = 256, kTc3AStageCols = 32;
+#ifndef TB200_TC3_EXPAND_WARPS
+#define TB200_TC3_EXPAND_WARPS 8
+#endif
+#ifndef TB200_TC3_SLEEP_NS
+#define TB200_TC3_SLEEP_NS 64
+#endif
+constexpr int kTc3ExpandWarps = TB200_TC3_EXPAND_WARPS;      // 4, 8 or 16: per lane quarter 1, 2 or 4 warps share the stage's four 32-deep groups
+constexpr int kTc3GroupsPerWarp = 16 / kTc3ExpandWarps;
+constexpr int kTc3FirstExpandWarp = 2;
+constexpr int kTc3FirstEpilogueWarp = kTc3FirstExpandWarp + kTc3ExpandWarps;    // 18
+#ifndef TB200_TC3_EPI_GROUPS
+#define TB200_TC3_EPI_GROUPS 2
+#endif
+constexpr int kTc3EpiGroups = TB200_TC3_EPI_GROUPS;                              // groups of 4 epilogue warps (one per lane quarter)
+constexpr int kTc3Threads = (kTc3FirstEpilogueWarp + 4 * kTc3EpiGroups) * 32;
+#ifndef TB200_TC3_EPI_BUFS
+#define TB200_TC3_EPI_BUFS 3
+#endif
+constexpr int kTc3EpiBufs = TB200_TC3_EPI_BUFS;   // staging buffers per epilogue group
+constexpr int kTc3EpiBytes = 32 * 128 * 4;        // one step of the epilogue: 32 activation rows x 128 weight columns
+constexpr size_t kTc3SmemBytes = 1024 + size_t(kTc3Stages) * kTc3StageBytes +
+                                 size_t(kTc3EpiGroups) * kTc3EpiBufs * kTc3EpiBytes + 512;
+// M = 256 (pair), N = 256, int8 x int8 -> int32, both operands K-major
+constexpr uint32_t kTc3Idesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(256 >> 3) << 17) |
+                               (static_cast<uint32_t>(256 >> 4) << 24);
+
+__device__ __forceinline__ void tc_mma_i8_pair_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                                      uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], [%1], %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 16 lanes x 8 columns: r0/r1 = rows lane/4 and lane/4 + 8 at column lane%4, r2/r3 = the same rows at column 4 + lane%4.
+__device__ __forceinline__ void tmem_st_16x128_x2(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+    asm volatile("tcgen05.st.sync.aligned.16x128b.x2.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(r0), "r"(r1), "r"(r2),
+                 "r"(r3)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void ldmatrix_x2_trans_b8_tc3(uint32_t (&r)[4], uint32_t smem_addr) {
+    asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_addr)
+                 : "memory");
+}
+// Field `shift / 2` of every byte of T as int8: codes 0, 1, 3 -> 0, +1, -1.
+__device__ __forceinline__ uint32_t decode_field_s8(uint32_t T, uint32_t shift) {
+    const uint32_t x = (T >> shift) & 0x03030303u;
+    return (x & 0x02020202u) * 126u + x;          // 3 -> 3 + 252 = 0xFF; no carry between bytes
+}
+
+__global__ void __launch_bounds__(kTc3Threads, 1)
+ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                        const __grid_constant__ CUtensorMap tmap_c, int use_tma_store, int32_t* __restrict__ C, int M,
+                        int K, int N, long long ldc, int store_c, int32_t* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sAct = base;                                            // [stages][128 rows][128 k]  128-byte swizzle
+    uint8_t* sWp = sAct + kTc3Stages * kTc3ActBytes;                 // [stages][128 k][32]        32-byte swizzle
+    uint8_t* sEpi = sWp + kTc3Stages * kTc3WpBytes;                  // [groups][bufs][32 rows][128] int32
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + kTc3EpiGroups * kTc3EpiBufs * kTc3EpiBytes);
+    uint64_t* full = bars;                         // this CTA's TMA bytes of a stage have landed
+    uint64_t* empty = full + kTc3Stages;           // the pair's MMAs on a stage have retired
+    uint64_t* ready = empty + kTc3Stages;          // (leader) both CTAs' operands of a stage are in place
+    uint64_t* acc_full = ready + kTc3Stages;       // [1]
+    uint64_t* acc_empty = acc_full + 1;            // [1] (leader)
+    uint64_t* drain = acc_empty + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int a_tiles = (M + kTc3TileA - 1) / kTc3TileA;
+    const int w_tiles = (N + kTc3TileW - 1) / kTc3TileW;
+    const int num_tiles = a_tiles * w_tiles;
+    const int k_blocks = (K + kTcBK - 1) / kTcBK;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTc3Stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+            mbar_init(&ready[s], 2 * kTc3ExpandWarps);
+        }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty, 8 * kTc3EpiGroups);
+        mbar_init(drain, 1);
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair<512>(tmem_slot);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ================================================================ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_a);
+            tma_prefetch_desc(&tmap_w);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                const int w_t = tile % w_tiles, a_t = tile / w_tiles;
+                const int row0 = a_t * kTc3TileA + rank * 128;
+                const int wp_x = (w_t * kTc3TileW + rank * 128) / 4;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % kTc3Stages;
+                    if (!mbar_wait_backoff(&empty[s], ((it / kTc3Stages) & 1) ^ 1, abort_flag, 32)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&full[s], kTc3StageBytes);
+                    tma_load_2d(sAct + s * kTc3ActBytes, &tmap_a, kb * kTcBK, row0, &full[s]);
+                    tma_load_2d(sWp + s * kTc3WpBytes, &tmap_w, wp_x, kb * kTcBK, &full[s]);
+                }
+            }
+            if (!ok) {
+                const uint32_t first = it > kTc3Stages ? it - kTc3Stages : 0;
+                for (uint32_t j = first; j < it; ++j) mbar_drain(&full[j % kTc3Stages], (j / kTc3Stages) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        // ================================================================ MMA issuer (leader CTA only)
+        if (leader && lane == 0) {
+            uint32_t it = 0, lt = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++lt) {
+                if (!mbar_wait(acc_empty, (lt & 1) ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % kTc3Stages;
+                    if (!mbar_wait(&ready[s], (it / kTc3Stages) & 1, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t act_addr = smem_u32(sAct + s * kTc3ActBytes);
+                    const uint32_t a_col = tmem_base + kTc3ARingCol + s * kTc3AStageCols;
+#pragma unroll
+                    for (int g = 0; g < kTcBK / 32; ++g) {
+                        const uint64_t db = umma_desc_sw128(act_addr + g * 32, 16, 1024);
+                        tc_mma_i8_pair_tmem_a(tmem_base, a_col + 8 * g, db, kTc3Idesc, (kb != 0 || g != 0) ? 1u : 0u);
+                    }
+                    tc_commit_pair_both(&empty[s]);
+                }
+                if (ok) tc_commit_pair_both(acc_full);
+            }
+            tc_commit_pair(drain);
+            mbar_wait(drain, 0, abort_flag);
+        }
+    } else if (warp < kTc3FirstEpilogueWarp) {
+        // ================================================================ expanders: packed bytes -> int8 rows of the A operand
+        // Lane L of the A operand is weight column L of the CTA's 128: byte column L / 4, field L % 4.  The warp of
+        // lane quarter q therefore needs byte columns 8q .. 8q+7 (half of the 16-byte chunk q / 2 of a row) in all
+        // four fields.
+        const uint32_t q = warp & 3;
+        const int g0 = ((warp - kTc3FirstExpandWarp) >> 2) * kTc3GroupsPerWarp;     // this warp's 32-deep groups of every stage
+        // ldmatrix.x2: matrix 0 = k 0-15, matrix 1 = k 16-31 of a 32-deep group, both of chunk q / 2; row (lane & 15),
+        // 32-byte swizzle (address bit 4 ^= address bit 7, i.e. chunk ^= bit 2 of the row)
+        const uint32_t r_in = lane & 15;
+        const uint32_t ld_off = (lane >> 4) * 512 + r_in * 32 + (((q >> 1) ^ ((r_in >> 2) & 1)) << 4);
+        // After the load lane (c, t) = (lane / 4, lane % 4) holds k-bytes 4t..4t+3 of byte column 8q + c (register q & 1
+        // of each matrix).  The store wants, in lane (g, t), rows g and g + 8 of a 16-lane group, i.e. byte columns
+        // g / 4 (+2, +4, +6) in field g % 4: four shuffles per matrix bring them over.
+        const int t4 = lane & 3, g4 = lane >> 4;
+        const int src0 = (g4 + 0) * 4 + t4, src1 = (g4 + 2) * 4 + t4, src2 = (g4 + 4) * 4 + t4, src3 = (g4 + 6) * 4 + t4;
+        const uint32_t shift = 2 * ((lane >> 2) & 3);
+        const uint32_t wp_sa = smem_u32(sWp);
+        const uint32_t t_lane = (q * 32) << 16;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const uint32_t s = it % kTc3Stages;
+                if (!mbar_wait_backoff(&full[s], (it / kTc3Stages) & 1, abort_flag, TB200_TC3_SLEEP_NS)) { ok = false; break; }
+                const uint32_t wp = wp_sa + s * kTc3WpBytes;
+                const uint32_t a_col = tmem_base + kTc3ARingCol + s * kTc3AStageCols;
+#pragma unroll
+                for (int gg = 0; gg < kTc3GroupsPerWarp; ++gg) {
+                    const int g = g0 + gg;
+                    uint32_t m[4];
+                    ldmatrix_x2_trans_b8_tc3(m, wp + g * 1024 + ld_off);
+                    const uint32_t X = (q & 1) ? m[1] : m[0], Y = (q & 1) ? m[3] : m[2];
+                    const uint32_t x0 = __shfl_sync(0xffffffffu, X, src0), x1 = __shfl_sync(0xffffffffu, X, src1);
+                    const uint32_t x2 = __shfl_sync(0xffffffffu, X, src2), x3 = __shfl_sync(0xffffffffu, X, src3);
+                    const uint32_t y0 = __shfl_sync(0xffffffffu, Y, src0), y1 = __shfl_sync(0xffffffffu, Y, src1);
+                    const uint32_t y2 = __shfl_sync(0xffffffffu, Y, src2), y3 = __shfl_sync(0xffffffffu, Y, src3);
+                    tmem_st_16x128_x2(a_col + t_lane + 8 * g, decode_field_s8(x0, shift), decode_field_s8(x1, shift),
+                                      decode_field_s8(y0, shift), decode_field_s8(y1, shift));
+                    tmem_st_16x128_x2(a_col + t_lane + (16u << 16) + 8 * g, decode_field_s8(x2, shift),
+                                      decode_field_s8(x3, shift), decode_field_s8(y2, shift), decode_field_s8(y3, shift));
+                }
+                tmem_st_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if (leader) mbar_arrive(&ready[s]);
+                    else mbar_arrive_remote(&ready[s], 0);
+                }
+            }
+        }
+    } else {
+        // ================================================================ epilogue: 128 weight columns x 256 activation rows
+        // Lane = weight column, registers = activation rows.  A step moves 32 activation rows x 128 columns from
+        // tensor memory into a staging buffer in shared memory, row-major as in C (a warp writes 128 contiguous bytes
+        // per row: no bank conflicts), and one thread hands the buffer to the TMA unit (cp.async.bulk.tensor store).
+        // The accumulator is released as soon as it has been read: the stores to global memory, whose rate per SM is
+        // what an epilogue out of registers waits for, run in the background under the next tile's MMAs.
+        const uint32_t q = warp & 3;
+        const int eg = (warp - kTc3FirstEpilogueWarp) >> 2;             // group: takes steps eg, eg + groups, ...
+        const bool elected = ((warp - kTc3FirstEpilogueWarp) & 3) == 0 && lane == 0;
+        const uint32_t epi_sa = smem_u32(sEpi);
+        uint32_t lt = 0, step = 0;                                      // step: steps taken by this group so far
+        bool ok = true;
+        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++lt) {
+            const int w_t = tile % w_tiles, a_t = tile / w_tiles;
+            if (!mbar_wait_backoff(acc_full, lt & 1, abort_flag, 256)) { ok = false; break; }
+            tc_fence_after_sync();
+            const int col0 = w_t * kTc3TileW + rank * 128;
+#pragma unroll 1
+            for (int c = eg; c < kTc3TileA / 32; c += kTc3EpiGroups, ++step) {
+                const uint32_t buf = epi_sa + (eg * kTc3EpiBufs + step % kTc3EpiBufs) * kTc3EpiBytes;
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((q * 32) << 16) + 32 * c, r);
+                // the store that last read this buffer has finished reading
+                if (elected) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kTc3EpiBufs - 1) : "memory");
+                tmem_ld_wait();
+                asm volatile("bar.sync %0, 128;" ::"r"(2 + eg) : "memory");
+                const int row0 = a_t * kTc3TileA + 32 * c;
+                if (use_tma_store) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) sts_u32(buf + ((j * 128 + q * 32 + lane) << 2), r[j]);
+                    fence_proxy_async_smem();
+                    asm volatile("bar.sync %0, 128;" ::"r"(2 + eg) : "memory");
+                    if (elected && store_c) {
+                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                                         reinterpret_cast<uint64_t>(&tmap_c)),
+                                     "r"(col0), "r"(row0), "r"(buf)
+                                     : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                } else {
+                    // C cannot be described to the TMA unit (pitch or base not 16-byte aligned): 128-byte row pieces
+                    const int col = col0 + q * 32 + lane;
+                    if (col < N && store_c) {
+                        int32_t* out = C + static_cast<size_t>(row0) * ldc + col;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (row0 + j < M) out[static_cast<size_t>(j) * ldc] = static_cast<int32_t>(r[j]);
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if (leader) mbar_arrive(acc_empty);
+                else mbar_arrive_remote(acc_empty, 0);
+            }
+        }
+        if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // nothing in flight when the CTA leaves
+    }
+
+    __syncwarp();
+    if (*abort_flag && lane == 0 && status) atomicMax(status, kStatusTimeout);
+    tc_fence_before_sync();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair<512>(tmem_base);
+    }
+}
+
+}  // namespace tb200

@@ -93,6 +93,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     *abort_flag = 1;
     return false;
 }
+// The same for waiters with slack (a whole ring stage or tile of it): sleeps between probes so that dozens of
+// polling warps do not compete with the tensor core for shared-memory bandwidth.
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t sleep_ns) {
+    uint64_t t0 = 0;
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(sleep_ns);
+        if ((spin & 63u) == 63u) {
+            if (*abort_flag) return false;
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) break;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
 // Teardown helper: bounded wait with no abort check (used only after a timeout, to let copies land).
 __device__ __forceinline__ void mbar_drain(uint64_t* bar, uint32_t parity) {
     const uint64_t t0 = global_timer_ns();

@@ -18,6 +18,7 @@
 #include "kernel_gemm_tc.cuh"
 #include "kernel_gemm_tc2.cuh"
 #include "kernel_gemm_tc2w.cuh"
+#include "kernel_gemm_tc3.cuh"
 #include "kernel_gemv.cuh"
 #include "kernel_decode_mma.cuh"
 #include "kernel_gemv_group.cuh"
@@ -506,8 +507,60 @@ int launch_gemm_tc2_t(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_li
 // Wide tiles for large single-destination products.  With peer destinations the 256-wide kernel is used: its
 // accumulator is double-buffered, so the slower NVLink stores of the epilogue hide under the next tile's main
 // loop, which the single-buffered wide kernel cannot do.  TERNIX_B200_TC_WIDE=0|1 forces the choice.
+// Paired CTAs with the weights as the A operand in tensor memory (kernel_gemm_tc3.cuh): one destination.
+int launch_gemm_tc3(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,
+                    int32_t* d_status, cudaStream_t st) {
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(tb200::ternary_gemm_tc3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(tb200::kTc3SmemBytes));
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    CUtensorMap tmap_a, tmap_w;
+    int rc = make_tmap_2d(&tmap_a, dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K),
+                          tb200::kTcBK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tmap_w, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K), static_cast<uint64_t>(N / 4),
+                      tb200::kTc3WpRowBytes, tb200::kTcBK, CU_TENSOR_MAP_SWIZZLE_32B);
+    if (rc) return rc;
+    const long tiles = static_cast<long>((M + tb200::kTc3TileA - 1) / tb200::kTc3TileA) *
+                       ((N + tb200::kTc3TileW - 1) / tb200::kTc3TileW);
+    const long max_pairs = sm_count() / 2;
+    const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(tb200::kTc3Threads, 1, 1);
+    cfg.dynamicSmemBytes = tb200::kTc3SmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const int store_c = 1;
+    // C as a tensor of 32-bit words for the epilogue's TMA stores (needs a 16-byte aligned base and pitch)
+    CUtensorMap tmap_c{};
+    int use_tma_store = (ldc % 4 == 0) && aligned(dC, 16);
+    if (use_tma_store) {
+        rc = make_tmap_2d_u32(&tmap_c, dC, static_cast<uint64_t>(N), static_cast<uint64_t>(M), static_cast<uint64_t>(ldc) * 4,
+                              128, 32);
+        if (rc) return rc;
+    }
+    TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc3_kernel, tmap_a, tmap_w, tmap_c, use_tma_store, dC, M, K, N, ldc,
+                               store_c, d_status));
+    return TERNIX_B200_OK;
+}
+
 int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
                     long long ldc, int32_t* d_status, cudaStream_t st) {
+    // One destination: the kernel that keeps the decoded weights in tensor memory (TERNIX_B200_TC3=0 falls back to
+    // the kernels that expand them into shared memory; tuning aid).  Several destinations: those kernels.
+    bool tc3 = n_dest == 1;
+    if (const char* env = std::getenv("TERNIX_B200_TC3")) tc3 = tc3 && std::atoi(env) != 0;
+    if (tc3) return launch_gemm_tc3(dA, dW, dC_list[0], M, K, N, ldc, d_status, st);
     bool wide = n_dest == 1 && N >= 1024 && K >= 1024;
     if (const char* env = std::getenv("TERNIX_B200_TC_WIDE")) wide = std::atoi(env) != 0;
     if (wide) return launch_gemm_tc2_t<true>(dA, dW, dC_list, n_dest, M, K, N, ldc, d_status, st);

@@ -129,15 +129,20 @@ def test_decode_mma_rows_slices_and_edges(monkeypatch, slices):
     assert_same(device_matmul(a, wp, "decode_mma"), np.full((m, n), 128 * k, dtype=np.int32), "decode_mma worst case")
 
 
-@pytest.mark.parametrize("bn", ["128", "256", "2", "2w"])
+@pytest.mark.parametrize("bn", ["128", "256", "2", "2w", "3"])
 def test_gemm_tc_tile_widths_and_ragged_edges(bn, monkeypatch):
-    # 128 / 256: single-CTA tiles; 2: paired CTAs, 256 x 256; 2w: paired CTAs, 256 x 512
-    monkeypatch.setenv("TERNIX_B200_TC_BN", bn[0] if bn.startswith("2") else bn)
+    # 128 / 256: single-CTA tiles; 2: paired CTAs, 256 x 256; 2w: paired CTAs, 256 x 512 (weights expanded into shared
+    # memory); 3: paired CTAs, weights decoded into tensor memory (the default for one destination)
+    monkeypatch.setenv("TERNIX_B200_TC_BN", "2" if bn in ("2", "2w", "3") else bn)
     monkeypatch.setenv("TERNIX_B200_TC_WIDE", "1" if bn == "2w" else "0")
+    monkeypatch.setenv("TERNIX_B200_TC3", "1" if bn == "3" else "0")
     for (m, k, n) in [(128, 128, 256), (128, 512, 128), (256, 1024, 512), (300, 2064, 832), (1, 16, 64),
                       (129, 144, 320), (640, 4096, 1024), (1000, 272, 1984)]:
         a, wp = synth(m, k, n, m + k + n)
         assert_same(device_matmul(a, wp, "gemm_tc", pad_cols=4), oracle_lib.matmul(a, wp), f"gemm_tc bn={bn} {m}x{k}x{n}")
+    # a pitch that is not a multiple of 16 bytes: no TMA view of C, no vector stores
+    a, wp = synth(300, 272, 576, 99)
+    assert_same(device_matmul(a, wp, "gemm_tc", pad_cols=3), oracle_lib.matmul(a, wp), f"gemm_tc bn={bn} odd pitch")
 
 
 @pytest.mark.parametrize("shape", [(1, 3001, 1028), (7, 129, 4), (37, 4099, 2052), (255, 2561, 6916)])
@@ -409,11 +414,14 @@ def test_projection_group_mixed_regimes():
         assert_same(out.cpu().numpy(), e, f"group member {tuple(a.shape)}")
 
 
+@pytest.mark.parametrize("tc3", ["0", "1"])
 @pytest.mark.parametrize("shape", [(4096, 2048, 5120), (2304, 2048, 9216), (4000, 4096, 5056)])
-def test_wide_kernel_k_sliced_tail(shape):
-    """Shapes whose last round of 256x512 tiles is split along K and added into a zeroed C: still bit-exact,
-    launch after launch, including ragged M and N edges inside the tail."""
+def test_wide_kernel_k_sliced_tail(shape, tc3, monkeypatch):
+    """Shapes whose last round of 256x512 tiles is split along K and added into a zeroed C (the kernel that expands
+    weights into shared memory), and the same shapes through the default kernel: bit-exact, launch after launch,
+    including ragged M and N edges and a C wider than N."""
     import torch
+    monkeypatch.setenv("TERNIX_B200_TC3", tc3)
     m, k, n = shape
     a, wp = synth(m, k, n, m + n)
     expect = torch.from_numpy(oracle_lib.matmul(a, wp)).cuda()
