@@ -331,7 +331,8 @@ def run_b200(args):
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath):
-        traffic = json.load(open(tpath)).get("gemm_tc_config3_dram_bytes_per_launch")
+        # measured for the single-GPU kernel on the whole of config 3; a column shard runs another kernel
+        traffic = json.load(open(tpath)).get("gemm_tc3_config3_dram_bytes_per_launch") if world == 1 else None
     kernel_ms = ms_local / args.steps
     local_ops = 2.0 * M * K * shard.n_cols
     line = {
@@ -347,7 +348,7 @@ def run_b200(args):
                           "columns_rank0": shard.n_cols},
         "roofline": {"bound": "tensor", "achieved": local_ops / (kernel_ms * 1e-3) / 1e12, "peak": int8_peak,
                      "unit": "TOPS", "frac": local_ops / (kernel_ms * 1e-3) / 1e12 / int8_peak, "traffic": traffic,
-                     "kernel": "ternary_gemm_tc2w_kernel", "peak_source": f"2 x bf16 burst of {peaks['source']} peaks "
+                     "kernel": "ternary_gemm_tc3_kernel" if world == 1 else "ternary_gemm_tc2_kernel", "peak_source": f"2 x bf16 burst of {peaks['source']} peaks "
                      "(dense int8 proxy)", "frac_of_nominal_4500": local_ops / (kernel_ms * 1e-3) / 1e12 / 4500.0},
         "nccl_gather_baseline": None if nccl_ms is None else {
             "ms_per_step": nccl_ms, "tops": ops / (nccl_ms * 1e-3) / 1e12,
@@ -527,8 +528,8 @@ def bench_gemv(tb, dev, peaks):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     args = ap.parse_args()
     if args.warmup < 3:

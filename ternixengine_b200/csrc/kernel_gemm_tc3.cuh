@@ -162,7 +162,7 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             uint32_t it = 0;
             bool ok = true;
             for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-                const int w_t = tile % w_tiles, a_t = tile / w_tiles;
+                const int a_t = tile % a_tiles, w_t = tile / a_tiles;   // pairs that run together share few weight blocks and all of A
                 const int row0 = a_t * kTc3TileA + rank * 128;
                 const int wp_x = (w_t * kTc3TileW + rank * 128) / 4;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
@@ -269,7 +269,7 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         uint32_t lt = 0, step = 0;                                      // step: steps taken by this group so far
         bool ok = true;
         for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++lt) {
-            const int w_t = tile % w_tiles, a_t = tile / w_tiles;
+            const int a_t = tile % a_tiles, w_t = tile / a_tiles;   // pairs that run together share few weight blocks and all of A
             if (!mbar_wait_backoff(acc_full, lt & 1, abort_flag, 256)) { ok = false; break; }
             tc_fence_after_sync();
             const int col0 = w_t * kTc3TileW + rank * 128;
