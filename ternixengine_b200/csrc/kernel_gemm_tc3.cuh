@@ -106,10 +106,18 @@ __device__ __forceinline__ uint32_t decode_field_s8(uint32_t T, uint32_t shift) 
     return (x & 0x02020202u) * 126u + x;          // 3 -> 3 + 252 = 0xFF; no carry between bytes
 }
 
+// Where the finished tiles go: the local C first, then the same place in each peer's C (fused gather over NVLink:
+// one TMA tensor store per destination from the same staging buffer).
+constexpr int kTc3MaxDest = 8;
+struct Tc3Stores {
+    CUtensorMap tmap_c[kTc3MaxDest];     // C [M][N] int32 with its row pitch, box 128 columns x 32 rows
+    int count;                           // 0: C cannot be described to the TMA unit; stores from registers into `C`
+};
+
 __global__ void __launch_bounds__(kTc3Threads, 1)
 ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                        const __grid_constant__ CUtensorMap tmap_c, int use_tma_store, int32_t* __restrict__ C, int M,
-                        int K, int N, long long ldc, int store_c, int32_t* __restrict__ status) {
+                        const __grid_constant__ Tc3Stores stores, int32_t* __restrict__ C, int M, int K, int N,
+                        long long ldc, int32_t* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sAct = base;                                            // [stages][128 rows][128 k]  128-byte swizzle
@@ -283,22 +291,23 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 tmem_ld_wait();
                 asm volatile("bar.sync %0, 128;" ::"r"(2 + eg) : "memory");
                 const int row0 = a_t * kTc3TileA + 32 * c;
-                if (use_tma_store) {
+                if (stores.count > 0) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) sts_u32(buf + ((j * 128 + q * 32 + lane) << 2), r[j]);
                     fence_proxy_async_smem();
                     asm volatile("bar.sync %0, 128;" ::"r"(2 + eg) : "memory");
-                    if (elected && store_c) {
-                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
-                                         reinterpret_cast<uint64_t>(&tmap_c)),
-                                     "r"(col0), "r"(row0), "r"(buf)
-                                     : "memory");
+                    if (elected) {
+                        for (int d = 0; d < stores.count; ++d)
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                                             reinterpret_cast<uint64_t>(&stores.tmap_c[d])),
+                                         "r"(col0), "r"(row0), "r"(buf)
+                                         : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                 } else {
                     // C cannot be described to the TMA unit (pitch or base not 16-byte aligned): 128-byte row pieces
                     const int col = col0 + q * 32 + lane;
-                    if (col < N && store_c) {
+                    if (col < N) {
                         int32_t* out = C + static_cast<size_t>(row0) * ldc + col;
 #pragma unroll
                         for (int j = 0; j < 32; ++j)

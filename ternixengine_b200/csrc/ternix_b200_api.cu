@@ -507,9 +507,10 @@ int launch_gemm_tc2_t(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_li
 // Wide tiles for large single-destination products.  With peer destinations the 256-wide kernel is used: its
 // accumulator is double-buffered, so the slower NVLink stores of the epilogue hide under the next tile's main
 // loop, which the single-buffered wide kernel cannot do.  TERNIX_B200_TC_WIDE=0|1 forces the choice.
-// Paired CTAs with the weights as the A operand in tensor memory (kernel_gemm_tc3.cuh): one destination.
-int launch_gemm_tc3(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,
-                    int32_t* d_status, cudaStream_t st) {
+// Paired CTAs with the weights as the A operand in tensor memory (kernel_gemm_tc3.cuh).  Several destinations need
+// every C to be describable to the TMA unit (16-byte aligned base and pitch); ERR_UNSUPPORTED otherwise.
+int launch_gemm_tc3(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
+                    long long ldc, int32_t* d_status, cudaStream_t st) {
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [&] {
@@ -517,6 +518,10 @@ int launch_gemm_tc3(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int
                                         static_cast<int>(tb200::kTc3SmemBytes));
     });
     if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    if (n_dest < 1 || n_dest > tb200::kTc3MaxDest) return TERNIX_B200_ERR_UNSUPPORTED;
+    bool tma_ok = (ldc % 4 == 0);
+    for (int d = 0; d < n_dest; ++d) tma_ok = tma_ok && aligned(dC_list[d], 16);
+    if (!tma_ok && n_dest > 1) return TERNIX_B200_ERR_UNSUPPORTED;
     CUtensorMap tmap_a, tmap_w;
     int rc = make_tmap_2d(&tmap_a, dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K),
                           tb200::kTcBK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -524,6 +529,13 @@ int launch_gemm_tc3(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int
     rc = make_tmap_2d(&tmap_w, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K), static_cast<uint64_t>(N / 4),
                       tb200::kTc3WpRowBytes, tb200::kTcBK, CU_TENSOR_MAP_SWIZZLE_32B);
     if (rc) return rc;
+    tb200::Tc3Stores stores{};
+    stores.count = tma_ok ? n_dest : 0;
+    for (int d = 0; d < stores.count; ++d) {
+        rc = make_tmap_2d_u32(&stores.tmap_c[d], dC_list[d], static_cast<uint64_t>(N), static_cast<uint64_t>(M),
+                              static_cast<uint64_t>(ldc) * 4, 128, 32);
+        if (rc) return rc;
+    }
     const long tiles = static_cast<long>((M + tb200::kTc3TileA - 1) / tb200::kTc3TileA) *
                        ((N + tb200::kTc3TileW - 1) / tb200::kTc3TileW);
     const long max_pairs = sm_count() / 2;
@@ -540,27 +552,20 @@ int launch_gemm_tc3(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const int store_c = 1;
-    // C as a tensor of 32-bit words for the epilogue's TMA stores (needs a 16-byte aligned base and pitch)
-    CUtensorMap tmap_c{};
-    int use_tma_store = (ldc % 4 == 0) && aligned(dC, 16);
-    if (use_tma_store) {
-        rc = make_tmap_2d_u32(&tmap_c, dC, static_cast<uint64_t>(N), static_cast<uint64_t>(M), static_cast<uint64_t>(ldc) * 4,
-                              128, 32);
-        if (rc) return rc;
-    }
-    TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc3_kernel, tmap_a, tmap_w, tmap_c, use_tma_store, dC, M, K, N, ldc,
-                               store_c, d_status));
+    TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc3_kernel, tmap_a, tmap_w, stores, dC_list[0], M, K, N, ldc, d_status));
     return TERNIX_B200_OK;
 }
 
 int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
                     long long ldc, int32_t* d_status, cudaStream_t st) {
-    // One destination: the kernel that keeps the decoded weights in tensor memory (TERNIX_B200_TC3=0 falls back to
-    // the kernels that expand them into shared memory; tuning aid).  Several destinations: those kernels.
-    bool tc3 = n_dest == 1;
-    if (const char* env = std::getenv("TERNIX_B200_TC3")) tc3 = tc3 && std::atoi(env) != 0;
-    if (tc3) return launch_gemm_tc3(dA, dW, dC_list[0], M, K, N, ldc, d_status, st);
+    // The kernel that keeps the decoded weights in tensor memory, unless TERNIX_B200_TC3=0 asks for the kernels that
+    // expand them into shared memory (tuning aid) or a C among several destinations has no TMA view.
+    bool tc3 = true;
+    if (const char* env = std::getenv("TERNIX_B200_TC3")) tc3 = std::atoi(env) != 0;
+    if (tc3) {
+        const int rc = launch_gemm_tc3(dA, dW, dC_list, n_dest, M, K, N, ldc, d_status, st);
+        if (rc != TERNIX_B200_ERR_UNSUPPORTED) return rc;
+    }
     bool wide = n_dest == 1 && N >= 1024 && K >= 1024;
     if (const char* env = std::getenv("TERNIX_B200_TC_WIDE")) wide = std::atoi(env) != 0;
     if (wide) return launch_gemm_tc2_t<true>(dA, dW, dC_list, n_dest, M, K, N, ldc, d_status, st);
