@@ -114,10 +114,60 @@ struct Tc3Stores {
     int count;                           // 0: C cannot be described to the TMA unit; stores from registers into `C`
 };
 
+// Grouped mode: one launch walks the tiles of many products (a "problem group"); descriptors and destinations come
+// from tables in global memory, and every pair owns a fixed slice of the tile list (Tc2Tile: problem, activation
+// block, weight block).
+struct alignas(64) Tc3Problem {
+    CUtensorMap tmap_a;        // A: [M rows][K bytes], box 128 x 128, 128-byte swizzle
+    CUtensorMap tmap_w;        // packed W: [K rows][N/4 bytes], box 32 B x 128 rows, 32-byte swizzle
+    Tc3Stores stores;
+    int32_t* C;
+    long long ldc;
+    int M, K, N, pad;
+};
+
+// The tile sequence of one CTA pair.  Every warp role constructs its own walker and sees the same sequence.
+template <bool kGrouped>
+struct Tc3Walk {
+    const CUtensorMap* ta;
+    const CUtensorMap* tw;
+    const Tc3Stores* st;
+    int32_t* C;
+    long long ldc;
+    int M, N, a_t, w_t, k_blocks;
+    // single product
+    int tile, num_tiles, stride, a_tiles;
+    // group
+    const Tc3Problem* probs;
+    const Tc2Tile* tiles;
+    int idx, end;
+
+    __device__ __forceinline__ bool next() {
+        if constexpr (kGrouped) {
+            if (idx >= end) return false;
+            const Tc2Tile t = tiles[idx++];
+            const Tc3Problem* p = probs + t.problem;
+            ta = &p->tmap_a; tw = &p->tmap_w; st = &p->stores;
+            C = p->C; ldc = p->ldc; M = p->M; N = p->N;
+            a_t = t.m_t; w_t = t.n_t;
+            k_blocks = (p->K + kTcBK - 1) / kTcBK;
+            return true;
+        } else {
+            if (tile >= num_tiles) return false;
+            // activation block fastest: pairs that run together share few weight blocks and all of A
+            a_t = tile % a_tiles; w_t = tile / a_tiles;
+            tile += stride;
+            return true;
+        }
+    }
+};
+
+template <bool kGrouped>
 __global__ void __launch_bounds__(kTc3Threads, 1)
 ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                         const __grid_constant__ Tc3Stores stores, int32_t* __restrict__ C, int M, int K, int N,
-                        long long ldc, int32_t* __restrict__ status) {
+                        long long ldc, const Tc3Problem* __restrict__ probs, const Tc2Tile* __restrict__ tiles,
+                        const int* __restrict__ pair_first, int32_t* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sAct = base;                                            // [stages][128 rows][128 k]  128-byte swizzle
@@ -137,10 +187,21 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    const int a_tiles = (M + kTc3TileA - 1) / kTc3TileA;
-    const int w_tiles = (N + kTc3TileW - 1) / kTc3TileW;
-    const int num_tiles = a_tiles * w_tiles;
-    const int k_blocks = (K + kTcBK - 1) / kTcBK;
+    auto make_walk = [&]() {
+        Tc3Walk<kGrouped> w{};
+        if constexpr (kGrouped) {
+            w.probs = probs; w.tiles = tiles;
+            w.idx = pair_first[pair]; w.end = pair_first[pair + 1];
+        } else {
+            w.ta = &tmap_a; w.tw = &tmap_w; w.st = &stores;
+            w.C = C; w.ldc = ldc; w.M = M; w.N = N;
+            w.a_tiles = (M + kTc3TileA - 1) / kTc3TileA;
+            w.num_tiles = w.a_tiles * ((N + kTc3TileW - 1) / kTc3TileW);
+            w.k_blocks = (K + kTcBK - 1) / kTcBK;
+            w.tile = pair; w.stride = num_pairs;
+        }
+        return w;
+    };
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTc3Stages; ++s) {
             mbar_init(&full[s], 1);
@@ -165,20 +226,22 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     if (warp == 0) {
         // ================================================================ TMA producer
         if (lane == 0) {
-            tma_prefetch_desc(&tmap_a);
-            tma_prefetch_desc(&tmap_w);
+            if constexpr (!kGrouped) {
+                tma_prefetch_desc(&tmap_a);
+                tma_prefetch_desc(&tmap_w);
+            }
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-                const int a_t = tile % a_tiles, w_t = tile / a_tiles;   // pairs that run together share few weight blocks and all of A
-                const int row0 = a_t * kTc3TileA + rank * 128;
-                const int wp_x = (w_t * kTc3TileW + rank * 128) / 4;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            Tc3Walk<kGrouped> w = make_walk();
+            while (ok && w.next()) {
+                const int row0 = w.a_t * kTc3TileA + rank * 128;
+                const int wp_x = (w.w_t * kTc3TileW + rank * 128) / 4;
+                for (int kb = 0; kb < w.k_blocks; ++kb, ++it) {
                     const uint32_t s = it % kTc3Stages;
                     if (!mbar_wait_backoff(&empty[s], ((it / kTc3Stages) & 1) ^ 1, abort_flag, 32)) { ok = false; break; }
                     mbar_arrive_expect_tx(&full[s], kTc3StageBytes);
-                    tma_load_2d(sAct + s * kTc3ActBytes, &tmap_a, kb * kTcBK, row0, &full[s]);
-                    tma_load_2d(sWp + s * kTc3WpBytes, &tmap_w, wp_x, kb * kTcBK, &full[s]);
+                    tma_load_2d(sAct + s * kTc3ActBytes, w.ta, kb * kTcBK, row0, &full[s]);
+                    tma_load_2d(sWp + s * kTc3WpBytes, w.tw, wp_x, kb * kTcBK, &full[s]);
                 }
             }
             if (!ok) {
@@ -191,10 +254,11 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         if (leader && lane == 0) {
             uint32_t it = 0, lt = 0;
             bool ok = true;
-            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++lt) {
+            Tc3Walk<kGrouped> w = make_walk();
+            for (; ok && w.next(); ++lt) {
                 if (!mbar_wait(acc_empty, (lt & 1) ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = 0; kb < w.k_blocks; ++kb, ++it) {
                     const uint32_t s = it % kTc3Stages;
                     if (!mbar_wait(&ready[s], (it / kTc3Stages) & 1, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
@@ -233,8 +297,9 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         const uint32_t t_lane = (q * 32) << 16;
         uint32_t it = 0;
         bool ok = true;
-        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        Tc3Walk<kGrouped> w = make_walk();
+        while (ok && w.next()) {
+            for (int kb = 0; kb < w.k_blocks; ++kb, ++it) {
                 const uint32_t s = it % kTc3Stages;
                 if (!mbar_wait_backoff(&full[s], (it / kTc3Stages) & 1, abort_flag, TB200_TC3_SLEEP_NS)) { ok = false; break; }
                 const uint32_t wp = wp_sa + s * kTc3WpBytes;
@@ -276,11 +341,16 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         const uint32_t epi_sa = smem_u32(sEpi);
         uint32_t lt = 0, step = 0;                                      // step: steps taken by this group so far
         bool ok = true;
-        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++lt) {
-            const int a_t = tile % a_tiles, w_t = tile / a_tiles;   // pairs that run together share few weight blocks and all of A
+        Tc3Walk<kGrouped> w = make_walk();
+        for (; ok && w.next(); ++lt) {
+            const int a_t = w.a_t;
+            const Tc3Stores* dst = w.st;
+            const int M = w.M, N = w.N;
+            const long long ldc = w.ldc;
+            int32_t* C = w.C;
             if (!mbar_wait_backoff(acc_full, lt & 1, abort_flag, 256)) { ok = false; break; }
             tc_fence_after_sync();
-            const int col0 = w_t * kTc3TileW + rank * 128;
+            const int col0 = w.w_t * kTc3TileW + rank * 128;
 #pragma unroll 1
             for (int c = eg; c < kTc3TileA / 32; c += kTc3EpiGroups, ++step) {
                 const uint32_t buf = epi_sa + (eg * kTc3EpiBufs + step % kTc3EpiBufs) * kTc3EpiBytes;
@@ -291,15 +361,15 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 tmem_ld_wait();
                 asm volatile("bar.sync %0, 128;" ::"r"(2 + eg) : "memory");
                 const int row0 = a_t * kTc3TileA + 32 * c;
-                if (stores.count > 0) {
+                if (dst->count > 0) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) sts_u32(buf + ((j * 128 + q * 32 + lane) << 2), r[j]);
                     fence_proxy_async_smem();
                     asm volatile("bar.sync %0, 128;" ::"r"(2 + eg) : "memory");
                     if (elected) {
-                        for (int d = 0; d < stores.count; ++d)
+                        for (int d = 0; d < dst->count; ++d)
                             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
-                                             reinterpret_cast<uint64_t>(&stores.tmap_c[d])),
+                                             reinterpret_cast<uint64_t>(&dst->tmap_c[d])),
                                          "r"(col0), "r"(row0), "r"(buf)
                                          : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");

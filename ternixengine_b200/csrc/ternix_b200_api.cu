@@ -514,7 +514,7 @@ int launch_gemm_tc3(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(tb200::ternary_gemm_tc3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        attr_err = cudaFuncSetAttribute(tb200::ternary_gemm_tc3_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(tb200::kTc3SmemBytes));
     });
     if (attr_err != cudaSuccess) return cuda_fail(attr_err);
@@ -552,7 +552,11 @@ int launch_gemm_tc3(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc3_kernel, tmap_a, tmap_w, stores, dC_list[0], M, K, N, ldc, d_status));
+    const tb200::Tc3Problem* no_probs = nullptr;
+    const tb200::Tc2Tile* no_tiles = nullptr;
+    const int* no_first = nullptr;
+    TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc3_kernel<false>, tmap_a, tmap_w, stores, dC_list[0], M, K, N, ldc,
+                               no_probs, no_tiles, no_first, d_status));
     return TERNIX_B200_OK;
 }
 
@@ -636,6 +640,7 @@ struct ternix_b200_group {
     // prefill-regime members: one launch of the paired-CTA GEMM over all their tiles
     void* d_tc_blob = nullptr;                  // [Tc2Problem[] | Tc2Tile[] | int pair_first[]]
     const tb200::Tc2Problem* d_tc_probs = nullptr;
+    const tb200::Tc3Problem* d_tc3_probs = nullptr;   // set instead of d_tc_probs when the tensor-memory kernel takes them
     const tb200::Tc2Tile* d_tc_tiles = nullptr;
     const int* d_tc_first = nullptr;
     int tc_pairs = 0;
@@ -671,7 +676,37 @@ int launch_gemv_group_t(const ternix_b200_group* g, int32_t* d_status, cudaStrea
     return TERNIX_B200_OK;
 }
 
+int launch_gemm_tc3_group(const ternix_b200_group* g, int32_t* d_status, cudaStream_t st) {
+    auto kern = tb200::ternary_gemm_tc3_kernel<true>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(tb200::kTc3SmemBytes));
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * g->tc_pairs, 1, 1);
+    cfg.blockDim = dim3(tb200::kTc3Threads, 1, 1);
+    cfg.dynamicSmemBytes = tb200::kTc3SmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CUtensorMap unused{};
+    tb200::Tc3Stores none{};
+    int32_t* no_c = nullptr;
+    TB_CUDA(cudaLaunchKernelEx(&cfg, kern, unused, unused, none, no_c, 0, 0, 0, 0LL, g->d_tc3_probs, g->d_tc_tiles,
+                               g->d_tc_first, d_status));
+    return TERNIX_B200_OK;
+}
+
 int launch_gemm_tc2_group(const ternix_b200_group* g, int32_t* d_status, cudaStream_t st) {
+    if (g->d_tc3_probs) return launch_gemm_tc3_group(g, d_status, st);
     using G = tb200::Tc2Geom;
     auto kern = tb200::ternary_gemm_tc2_kernel<true>;
     static std::once_flag once;
@@ -1195,6 +1230,9 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
     if (const char* env = std::getenv("TERNIX_B200_GROUP_WORDS")) g->words = (!prepacked && std::atoi(env) == 16) ? 16 : 32;
     const int item_cols = g->words * 16;
     std::vector<tb200::Tc2Problem> tc_probs;
+    std::vector<tb200::Tc3Problem> tc3_probs;
+    bool tc3_group = true;                                // TERNIX_B200_TC3=0: the expanding kernel (tuning aid)
+    if (const char* env = std::getenv("TERNIX_B200_TC3")) tc3_group = std::atoi(env) != 0;
     std::vector<tb200::MmaProblem> mma_probs[2];          // row groups of 8, of 16
     std::vector<tb200::GroupProblem> probs;
     struct HostItem { tb200::GroupItem item; long cost; };
@@ -1224,6 +1262,25 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
             }
             tp.ldc = q.ldc; tp.M = q.M; tp.K = q.K; tp.N = q.N;
             tc_probs.push_back(tp);
+            // the same member for the kernel that keeps decoded weights in tensor memory (needs TMA views of every C)
+            if (tc3_group && tp.c_vec_ok) {
+                tb200::Tc3Problem t3{};
+                rc = make_tmap_2d(&t3.tmap_a, q.dA, static_cast<uint64_t>(q.K), static_cast<uint64_t>(q.M),
+                                  static_cast<uint64_t>(q.K), tb200::kTcBK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+                if (!rc)
+                    rc = make_tmap_2d(&t3.tmap_w, q.dW, static_cast<uint64_t>(q.N / 4), static_cast<uint64_t>(q.K),
+                                      static_cast<uint64_t>(q.N / 4), tb200::kTc3WpRowBytes, tb200::kTcBK,
+                                      CU_TENSOR_MAP_SWIZZLE_32B);
+                t3.stores.count = tp.dest.count;
+                for (int d = 0; !rc && d < tp.dest.count; ++d)
+                    rc = make_tmap_2d_u32(&t3.stores.tmap_c[d], tp.dest.c[d], static_cast<uint64_t>(q.N),
+                                          static_cast<uint64_t>(q.M), static_cast<uint64_t>(q.ldc) * 4, 128, 32);
+                if (rc) { delete g; return rc; }
+                t3.C = q.dC; t3.ldc = q.ldc; t3.M = q.M; t3.K = q.K; t3.N = q.N;
+                tc3_probs.push_back(t3);
+            } else {
+                tc3_group = false;
+            }
             ++g->tc_grouped;
             continue;
         }
@@ -1334,20 +1391,23 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
             flat.insert(flat.end(), per_pair[c].begin(), per_pair[c].end());
         }
         first[pairs] = static_cast<int>(flat.size());
-        const size_t b_probs = tc_probs.size() * sizeof(tb200::Tc2Problem);
+        const bool use_tc3 = tc3_group && tc3_probs.size() == tc_probs.size();
+        const size_t b_probs = use_tc3 ? tc3_probs.size() * sizeof(tb200::Tc3Problem) : tc_probs.size() * sizeof(tb200::Tc2Problem);
+        const void* h_probs = use_tc3 ? static_cast<const void*>(tc3_probs.data()) : static_cast<const void*>(tc_probs.data());
         const size_t b_tiles = (flat.size() * sizeof(tb200::Tc2Tile) + 63) & ~size_t(63);
         const size_t b_first = first.size() * sizeof(int);
         cudaError_t e = cudaMalloc(&g->d_tc_blob, b_probs + b_tiles + b_first);
         if (e != cudaSuccess) { ternix_b200_group_destroy(g); return cuda_fail(e); }
         uint8_t* d = static_cast<uint8_t*>(g->d_tc_blob);
-        if ((e = cudaMemcpy(d, tc_probs.data(), b_probs, cudaMemcpyHostToDevice)) != cudaSuccess ||
+        if ((e = cudaMemcpy(d, h_probs, b_probs, cudaMemcpyHostToDevice)) != cudaSuccess ||
             (e = cudaMemcpy(d + b_probs, flat.data(), flat.size() * sizeof(tb200::Tc2Tile), cudaMemcpyHostToDevice)) !=
                 cudaSuccess ||
             (e = cudaMemcpy(d + b_probs + b_tiles, first.data(), b_first, cudaMemcpyHostToDevice)) != cudaSuccess) {
             ternix_b200_group_destroy(g);
             return cuda_fail(e);
         }
-        g->d_tc_probs = reinterpret_cast<const tb200::Tc2Problem*>(d);
+        if (use_tc3) g->d_tc3_probs = reinterpret_cast<const tb200::Tc3Problem*>(d);
+        else g->d_tc_probs = reinterpret_cast<const tb200::Tc2Problem*>(d);
         g->d_tc_tiles = reinterpret_cast<const tb200::Tc2Tile*>(d + b_probs);
         g->d_tc_first = reinterpret_cast<const int*>(d + b_probs + b_tiles);
         g->tc_pairs = pairs;
