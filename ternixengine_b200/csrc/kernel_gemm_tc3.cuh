@@ -27,9 +27,10 @@
 // int32, single-buffered), columns 256-511 the A ring: up to 8 stages x 32 columns (128 K-bytes per lane).
 //
 // Roles per CTA (warps): 0 TMA producer; 1 MMA issuer (leader CTA only: four M=256 N=256 K=32 pair MMAs per
-// stage, commit -> `empty` of both CTAs); 2-9 expanders (lane quarter = warp % 4, two warps per quarter share the
-// stage's four 32-deep groups; after tcgen05.wait::st they arrive on the leader's `ready`, which therefore also
-// says that this CTA's activation tile has landed); 10-17 epilogue, two groups of four that take alternate steps.
+// stage, commit -> `empty` of both CTAs); 2-9 expanders (lane quarter = warp % 4; the two warps of a quarter take
+// the stages in turn, so that a warp's chain of load, shuffle, decode, tensor-memory store and its wait spans two
+// stage times; after tcgen05.wait::st they arrive on the leader's `ready`, which therefore also says that this
+// CTA's activation tile has landed); 10-17 epilogue, two groups of four that take alternate steps.
 //
 // Exactness: int8 x int8 -> int32 on decoded -1/0/+1 weights, no scaling; any K the tensor maps can describe.
 #pragma once
@@ -56,8 +57,10 @@ constexpr uint32_t kTc3AccCols = 256, kTc3ARingCol = 256, kTc3AStageCols = 32;
 #ifndef TB200_TC3_SLEEP_NS
 #define TB200_TC3_SLEEP_NS 64
 #endif
-constexpr int kTc3ExpandWarps = TB200_TC3_EXPAND_WARPS;      // 4, 8 or 16: per lane quarter 1, 2 or 4 warps share the stage's four 32-deep groups
-constexpr int kTc3GroupsPerWarp = 16 / kTc3ExpandWarps;
+constexpr int kTc3ExpandWarps = TB200_TC3_EXPAND_WARPS;      // 4, 8 or 12: one, two or three warps per lane quarter
+constexpr int kTc3WarpsPerQuarter = kTc3ExpandWarps / 4;     // they take the stages in turn (stage it -> warp it % n)
+static_assert(TB200_TC3_STAGES % (TB200_TC3_EXPAND_WARPS / 4) == 0,
+              "a warp must meet every phase of the barriers it waits on: stages a multiple of warps per quarter");
 constexpr int kTc3FirstExpandWarp = 2;
 constexpr int kTc3FirstEpilogueWarp = kTc3FirstExpandWarp + kTc3ExpandWarps;    // 18
 #ifndef TB200_TC3_EPI_GROUPS
@@ -206,7 +209,7 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         for (int s = 0; s < kTc3Stages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
-            mbar_init(&ready[s], 2 * kTc3ExpandWarps);
+            mbar_init(&ready[s], 2 * 4);
         }
         mbar_init(acc_full, 1);
         mbar_init(acc_empty, 8 * kTc3EpiGroups);
@@ -282,7 +285,7 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         // lane quarter q therefore needs byte columns 8q .. 8q+7 (half of the 16-byte chunk q / 2 of a row) in all
         // four fields.
         const uint32_t q = warp & 3;
-        const int g0 = ((warp - kTc3FirstExpandWarp) >> 2) * kTc3GroupsPerWarp;     // this warp's 32-deep groups of every stage
+        const uint32_t slot = (warp - kTc3FirstExpandWarp) >> 2;       // this warp's turn among the warps of its quarter
         // ldmatrix.x2: matrix 0 = k 0-15, matrix 1 = k 16-31 of a 32-deep group, both of chunk q / 2; row (lane & 15),
         // 32-byte swizzle (address bit 4 ^= address bit 7, i.e. chunk ^= bit 2 of the row)
         const uint32_t r_in = lane & 15;
@@ -300,13 +303,13 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         Tc3Walk<kGrouped> w = make_walk();
         while (ok && w.next()) {
             for (int kb = 0; kb < w.k_blocks; ++kb, ++it) {
+                if (it % kTc3WarpsPerQuarter != slot) continue;
                 const uint32_t s = it % kTc3Stages;
                 if (!mbar_wait_backoff(&full[s], (it / kTc3Stages) & 1, abort_flag, TB200_TC3_SLEEP_NS)) { ok = false; break; }
                 const uint32_t wp = wp_sa + s * kTc3WpBytes;
                 const uint32_t a_col = tmem_base + kTc3ARingCol + s * kTc3AStageCols;
 #pragma unroll
-                for (int gg = 0; gg < kTc3GroupsPerWarp; ++gg) {
-                    const int g = g0 + gg;
+                for (int g = 0; g < kTcBK / 32; ++g) {
                     uint32_t m[4];
                     ldmatrix_x2_trans_b8_tc3(m, wp + g * 1024 + ld_off);
                     const uint32_t X = (q & 1) ? m[1] : m[0], Y = (q & 1) ? m[3] : m[2];
