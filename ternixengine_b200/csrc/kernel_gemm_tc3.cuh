@@ -41,16 +41,20 @@
 namespace tb200 {
 
 #ifndef TB200_TC3_STAGES
-#define TB200_TC3_STAGES 6
+#define TB200_TC3_STAGES 4
 #endif
 constexpr int kTc3Stages = TB200_TC3_STAGES;
 constexpr int kTc3TileW = 256;                    // weight columns per pair (128 per CTA)
 constexpr int kTc3TileA = 256;                    // activation rows per pair (128 loaded per CTA)
-constexpr int kTc3ActBytes = 128 * kTcBK;         // 16384
+#ifndef TB200_TC3_BK
+#define TB200_TC3_BK 256
+#endif
+constexpr int kTc3BK = TB200_TC3_BK;              // K-bytes per stage: 128 or 256 (the latter as two 128-byte-swizzle boxes)
+constexpr int kTc3ActBytes = 128 * kTc3BK;
 constexpr int kTc3WpRowBytes = 32;
-constexpr int kTc3WpBytes = kTcBK * kTc3WpRowBytes;          // 4096
+constexpr int kTc3WpBytes = kTc3BK * kTc3WpRowBytes;
 constexpr int kTc3StageBytes = kTc3ActBytes + kTc3WpBytes;   // 20480
-constexpr uint32_t kTc3AccCols = 256, kTc3ARingCol = 256, kTc3AStageCols = 32;
+constexpr uint32_t kTc3AccCols = 256, kTc3ARingCol = 256, kTc3AStageCols = kTc3BK / 4;
 #ifndef TB200_TC3_EXPAND_WARPS
 #define TB200_TC3_EXPAND_WARPS 8
 #endif
@@ -69,7 +73,7 @@ constexpr int kTc3FirstEpilogueWarp = kTc3FirstExpandWarp + kTc3ExpandWarps;    
 constexpr int kTc3EpiGroups = TB200_TC3_EPI_GROUPS;                              // groups of 4 epilogue warps (one per lane quarter)
 constexpr int kTc3Threads = (kTc3FirstEpilogueWarp + 4 * kTc3EpiGroups) * 32;
 #ifndef TB200_TC3_EPI_BUFS
-#define TB200_TC3_EPI_BUFS 3
+#define TB200_TC3_EPI_BUFS 2
 #endif
 constexpr int kTc3EpiBufs = TB200_TC3_EPI_BUFS;   // staging buffers per epilogue group
 constexpr int kTc3EpiBytes = 32 * 128 * 4;        // one step of the epilogue: 32 activation rows x 128 weight columns
@@ -153,7 +157,7 @@ struct Tc3Walk {
             ta = &p->tmap_a; tw = &p->tmap_w; st = &p->stores;
             C = p->C; ldc = p->ldc; M = p->M; N = p->N;
             a_t = t.m_t; w_t = t.n_t;
-            k_blocks = (p->K + kTcBK - 1) / kTcBK;
+            k_blocks = (p->K + kTc3BK - 1) / kTc3BK;
             return true;
         } else {
             if (tile >= num_tiles) return false;
@@ -200,7 +204,7 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             w.C = C; w.ldc = ldc; w.M = M; w.N = N;
             w.a_tiles = (M + kTc3TileA - 1) / kTc3TileA;
             w.num_tiles = w.a_tiles * ((N + kTc3TileW - 1) / kTc3TileW);
-            w.k_blocks = (K + kTcBK - 1) / kTcBK;
+            w.k_blocks = (K + kTc3BK - 1) / kTc3BK;
             w.tile = pair; w.stride = num_pairs;
         }
         return w;
@@ -243,8 +247,10 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     const uint32_t s = it % kTc3Stages;
                     if (!mbar_wait_backoff(&empty[s], ((it / kTc3Stages) & 1) ^ 1, abort_flag, 32)) { ok = false; break; }
                     mbar_arrive_expect_tx(&full[s], kTc3StageBytes);
-                    tma_load_2d(sAct + s * kTc3ActBytes, w.ta, kb * kTcBK, row0, &full[s]);
-                    tma_load_2d(sWp + s * kTc3WpBytes, w.tw, wp_x, kb * kTcBK, &full[s]);
+#pragma unroll
+                    for (int j = 0; j < kTc3BK / 128; ++j)
+                        tma_load_2d(sAct + s * kTc3ActBytes + j * 16384, w.ta, kb * kTc3BK + j * 128, row0, &full[s]);
+                    tma_load_2d(sWp + s * kTc3WpBytes, w.tw, wp_x, kb * kTc3BK, &full[s]);
                 }
             }
             if (!ok) {
@@ -268,8 +274,8 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     const uint32_t act_addr = smem_u32(sAct + s * kTc3ActBytes);
                     const uint32_t a_col = tmem_base + kTc3ARingCol + s * kTc3AStageCols;
 #pragma unroll
-                    for (int g = 0; g < kTcBK / 32; ++g) {
-                        const uint64_t db = umma_desc_sw128(act_addr + g * 32, 16, 1024);
+                    for (int g = 0; g < kTc3BK / 32; ++g) {
+                        const uint64_t db = umma_desc_sw128(act_addr + (g >> 2) * 16384 + (g & 3) * 32, 16, 1024);
                         tc_mma_i8_pair_tmem_a(tmem_base, a_col + 8 * g, db, kTc3Idesc, (kb != 0 || g != 0) ? 1u : 0u);
                     }
                     tc_commit_pair_both(&empty[s]);
@@ -309,7 +315,7 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 const uint32_t wp = wp_sa + s * kTc3WpBytes;
                 const uint32_t a_col = tmem_base + kTc3ARingCol + s * kTc3AStageCols;
 #pragma unroll
-                for (int g = 0; g < kTcBK / 32; ++g) {
+                for (int g = 0; g < kTc3BK / 32; ++g) {
                     uint32_t m[4];
                     ldmatrix_x2_trans_b8_tc3(m, wp + g * 1024 + ld_off);
                     const uint32_t X = (q & 1) ? m[1] : m[0], Y = (q & 1) ? m[3] : m[2];

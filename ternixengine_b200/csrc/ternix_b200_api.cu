@@ -527,7 +527,7 @@ int launch_gemm_tc3(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list
                           tb200::kTcBK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     rc = make_tmap_2d(&tmap_w, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K), static_cast<uint64_t>(N / 4),
-                      tb200::kTc3WpRowBytes, tb200::kTcBK, CU_TENSOR_MAP_SWIZZLE_32B);
+                      tb200::kTc3WpRowBytes, tb200::kTc3BK, CU_TENSOR_MAP_SWIZZLE_32B);
     if (rc) return rc;
     tb200::Tc3Stores stores{};
     stores.count = tma_ok ? n_dest : 0;
@@ -1269,7 +1269,7 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
                                   static_cast<uint64_t>(q.K), tb200::kTcBK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
                 if (!rc)
                     rc = make_tmap_2d(&t3.tmap_w, q.dW, static_cast<uint64_t>(q.N / 4), static_cast<uint64_t>(q.K),
-                                      static_cast<uint64_t>(q.N / 4), tb200::kTc3WpRowBytes, tb200::kTcBK,
+                                      static_cast<uint64_t>(q.N / 4), tb200::kTc3WpRowBytes, tb200::kTc3BK,
                                       CU_TENSOR_MAP_SWIZZLE_32B);
                 t3.stores.count = tp.dest.count;
                 for (int d = 0; !rc && d < tp.dest.count; ++d)
