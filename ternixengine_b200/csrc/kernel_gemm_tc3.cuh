@@ -7,16 +7,16 @@
 // product transposed,
 //     C^T[n][m] = sum_k W[k][n] * A[m][k],
 // with the weights as the A operand and the activations, untouched, as the B operand:
-//   * activations: 128 rows x 128 K-bytes per CTA and stage, straight from TMA into the K-major 128-byte-swizzle
-//     layout the B descriptor reads (the pair's two halves make the N = 256 columns of the instruction);
-//   * weights: 128 k-rows x 32 packed bytes per CTA and stage (its 128 weight columns), TMA with the 32-byte
+//   * activations: 128 rows x 256 K-bytes per CTA and stage (two boxes of 128 K-bytes), straight from TMA into the
+//     K-major 128-byte-swizzle layout the B descriptor reads (the pair's two halves make the N = 256 columns of the instruction);
+//   * weights: 256 k-rows x 32 packed bytes per CTA and stage (its 128 weight columns), TMA with the 32-byte
 //     swizzle.  An expander warp reads them with ldmatrix.m16n16.x2.trans.b8, which leaves four consecutive K-bytes
 //     of one byte column in one register.  Lane L of the operand is weight column L of the CTA's 128, i.e. byte
 //     column L / 4, field L % 4, so the warp of lane quarter q needs byte columns 8q .. 8q+7 in all four fields:
 //     eight shuffles per 32-deep group bring each lane the registers of its rows, one variable shift and three ALU
 //     operations decode its field (2-bit code -> int8 -1/0/+1), and tcgen05.st.16x128b writes them to tensor
 //     memory.  Nothing expanded ever touches shared memory: per CTA and 128-deep k-block the expanders execute a
-//     few hundred instructions in all, and the ring holds 20 KB per stage instead of 56 KB.
+//     few hundred instructions in all, and the ring holds 40 KB per 256-deep stage instead of 112 KB.
 //   * epilogue: lane = weight column, tensor-memory column = activation row.  A step moves 32 activation rows x
 //     128 columns into a staging buffer in shared memory, row-major as in C (a warp writes 128 contiguous bytes per
 //     row), and one thread hands the buffer to the TMA unit as a tensor store.  The accumulator is released as soon
@@ -24,9 +24,11 @@
 //     of registers has to wait for, run in the background under the next tile's MMAs.
 //
 // Tensor memory (512 columns per CTA): columns 0-255 the accumulator (128 weight columns x 256 activation rows,
-// int32, single-buffered), columns 256-511 the A ring: up to 8 stages x 32 columns (128 K-bytes per lane).
+// int32, single-buffered), columns 256-511 the A ring: 4 stages x 64 columns (256 K-bytes per lane).
+// Stages are 256 deep because every hand-over of a stage (TMA -> expanders -> leader -> tensor core -> producer)
+// costs about the same whatever it carries: 128-deep stages ran 10 % slower with the tensor pipe 71 % busy, these 85 %.
 //
-// Roles per CTA (warps): 0 TMA producer; 1 MMA issuer (leader CTA only: four M=256 N=256 K=32 pair MMAs per
+// Roles per CTA (warps): 0 TMA producer; 1 MMA issuer (leader CTA only: eight M=256 N=256 K=32 pair MMAs per
 // stage, commit -> `empty` of both CTAs); 2-9 expanders (lane quarter = warp % 4; the two warps of a quarter take
 // the stages in turn, so that a warp's chain of load, shuffle, decode, tensor-memory store and its wait spans two
 // stage times; after tcgen05.wait::st they arrive on the leader's `ready`, which therefore also says that this
