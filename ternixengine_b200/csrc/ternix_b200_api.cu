@@ -582,7 +582,12 @@ int launch_gemm_tc(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int 
     // paired-CTA kernel (tuning aids).  Default: pairs whenever there are rows for both CTAs of a pair.
     int bn = 0;
     if (const char* env = std::getenv("TERNIX_B200_TC_BN")) bn = std::atoi(env);
-    if (bn == 2 || (bn == 0 && M > 128 && N >= 256)) return launch_gemm_tc2(dA, dW, &dC, 1, M, K, N, ldc, d_status, st);
+    // Pairs from 65 rows up: the tensor-memory kernel pads a half-empty activation tile for nothing (rows beyond M
+    // arrive as zeros from TMA) and still beats the single-CTA tiles; TERNIX_B200_TC3=0 keeps the old limit of 128.
+    bool tc3_on = true;
+    if (const char* env = std::getenv("TERNIX_B200_TC3")) tc3_on = std::atoi(env) != 0;
+    const int pair_min_rows = tc3_on ? 64 : 128;
+    if (bn == 2 || (bn == 0 && M > pair_min_rows && N >= 256)) return launch_gemm_tc2(dA, dW, &dC, 1, M, K, N, ldc, d_status, st);
     if (bn != 128 && bn != 256) {
         const long m_tiles = (M + tb200::kTcBM - 1) / tb200::kTcBM;
         const long tiles256 = m_tiles * ((N + 255) / 256);
