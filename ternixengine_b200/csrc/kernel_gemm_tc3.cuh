@@ -37,6 +37,7 @@
 // Exactness: int8 x int8 -> int32 on decoded -1/0/+1 weights, no scaling; any K the tensor maps can describe.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cstdint>
 #include "kernel_gemm_tc2.cuh"
 
@@ -171,12 +172,21 @@ struct Tc3Walk {
     }
 };
 
-template <bool kGrouped>
+__device__ __forceinline__ void sts_u16(uint32_t saddr, uint16_t v) {
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(saddr), "h"(v) : "memory");
+}
+
+// kBf16: the epilogue emits bfloat16 = bf16_rn((float(c) * row_scale[m]) * w_scale) instead of int32 (the scaling
+// step that follows the product in a BitNet-style layer); `stores` then describes bfloat16 tensors and `C`, `ldc`
+// are the bfloat16 output and its pitch in elements.
+template <bool kGrouped, bool kBf16 = false>
 __global__ void __launch_bounds__(kTc3Threads, 1)
 ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                         const __grid_constant__ Tc3Stores stores, int32_t* __restrict__ C, int M, int K, int N,
                         long long ldc, const Tc3Problem* __restrict__ probs, const Tc2Tile* __restrict__ tiles,
-                        const int* __restrict__ pair_first, int32_t* __restrict__ status) {
+                        const int* __restrict__ pair_first, int32_t* __restrict__ status,
+                        const float* __restrict__ row_scale = nullptr, float w_scale = 1.0f) {
+    static_assert(!(kGrouped && kBf16), "the dequantising epilogue is built for single products");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sAct = base;                                            // [stages][128 rows][128 k]  128-byte swizzle
@@ -372,9 +382,23 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 tmem_ld_wait();
                 asm volatile("bar.sync %0, 128;" ::"r"(2 + eg) : "memory");
                 const int row0 = a_t * kTc3TileA + 32 * c;
-                if (dst->count > 0) {
+                if constexpr (kBf16) {
+                    // in place: r[j] becomes the bfloat16 bit pattern of the scaled value
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) sts_u32(buf + ((j * 128 + q * 32 + lane) << 2), r[j]);
+                    for (int j = 0; j < 32; ++j) {
+                        const float rs = row0 + j < M ? __ldg(row_scale + row0 + j) : 0.0f;
+                        const __nv_bfloat16 y = __float2bfloat16_rn((static_cast<float>(static_cast<int32_t>(r[j])) * rs) * w_scale);
+                        r[j] = static_cast<uint32_t>(__bfloat16_as_ushort(y));
+                    }
+                }
+                if (dst->count > 0) {
+                    if constexpr (kBf16) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) sts_u16(buf + ((j * 128 + q * 32 + lane) << 1), static_cast<uint16_t>(r[j]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) sts_u32(buf + ((j * 128 + q * 32 + lane) << 2), r[j]);
+                    }
                     fence_proxy_async_smem();
                     asm volatile("bar.sync %0, 128;" ::"r"(2 + eg) : "memory");
                     if (elected) {
@@ -389,10 +413,17 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     // C cannot be described to the TMA unit (pitch or base not 16-byte aligned): 128-byte row pieces
                     const int col = col0 + q * 32 + lane;
                     if (col < N) {
-                        int32_t* out = C + static_cast<size_t>(row0) * ldc + col;
+                        if constexpr (kBf16) {
+                            uint16_t* out = reinterpret_cast<uint16_t*>(C) + static_cast<size_t>(row0) * ldc + col;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (row0 + j < M) out[static_cast<size_t>(j) * ldc] = static_cast<int32_t>(r[j]);
+                            for (int j = 0; j < 32; ++j)
+                                if (row0 + j < M) out[static_cast<size_t>(j) * ldc] = static_cast<uint16_t>(r[j]);
+                        } else {
+                            int32_t* out = C + static_cast<size_t>(row0) * ldc + col;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (row0 + j < M) out[static_cast<size_t>(j) * ldc] = static_cast<int32_t>(r[j]);
+                        }
                     }
                 }
             }

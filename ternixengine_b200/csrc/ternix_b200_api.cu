@@ -90,6 +90,22 @@ int make_tmap_2d_u32(CUtensorMap* out, const void* ptr, uint64_t row_words, uint
     return TERNIX_B200_OK;
 }
 
+// 2-D tensor of 16-bit elements [rows][row_elems] with `pitch` bytes between rows; box = box_rows x box_elems.
+int make_tmap_2d_u16(CUtensorMap* out, const void* ptr, uint64_t row_elems, uint64_t rows, uint64_t pitch,
+                     uint32_t box_elems, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return cuda_fail(cudaErrorNotSupported);
+    const cuuint64_t dims[2] = {row_elems, rows};
+    const cuuint64_t strides[1] = {pitch};
+    const cuuint32_t box[2] = {box_elems, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+    return TERNIX_B200_OK;
+}
+
 bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 int sm_count() {
@@ -556,7 +572,7 @@ int launch_gemm_tc3(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list
     const tb200::Tc2Tile* no_tiles = nullptr;
     const int* no_first = nullptr;
     TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc3_kernel<false>, tmap_a, tmap_w, stores, dC_list[0], M, K, N, ldc,
-                               no_probs, no_tiles, no_first, d_status));
+                               no_probs, no_tiles, no_first, d_status, static_cast<const float*>(nullptr), 1.0f));
     return TERNIX_B200_OK;
 }
 
@@ -706,7 +722,7 @@ int launch_gemm_tc3_group(const ternix_b200_group* g, int32_t* d_status, cudaStr
     tb200::Tc3Stores none{};
     int32_t* no_c = nullptr;
     TB_CUDA(cudaLaunchKernelEx(&cfg, kern, unused, unused, none, no_c, 0, 0, 0, 0LL, g->d_tc3_probs, g->d_tc_tiles,
-                               g->d_tc_first, d_status));
+                               g->d_tc_first, d_status, static_cast<const float*>(nullptr), 1.0f));
     return TERNIX_B200_OK;
 }
 
@@ -792,8 +808,66 @@ __global__ void dequant_rows_kernel(const int32_t* __restrict__ C, long long ldc
     }
 }
 
+// The same product with the dequantising epilogue of the tensor-memory kernel (bfloat16 out, one TMA store per
+// destination).  ERR_UNSUPPORTED when an output has no TMA view and there are several of them.
+int launch_gemm_tc3_bf16(const int8_t* dA, const uint8_t* dW, void* const* dY_list, int n_dest, const float* row_scale,
+                         float w_scale, int M, int K, int N, long long ldy, int32_t* d_status, cudaStream_t st) {
+    auto kern = tb200::ternary_gemm_tc3_kernel<false, true>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(tb200::kTc3SmemBytes));
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    if (n_dest < 1 || n_dest > tb200::kTc3MaxDest) return TERNIX_B200_ERR_UNSUPPORTED;
+    bool tma_ok = (ldy % 8 == 0);
+    for (int d = 0; d < n_dest; ++d) tma_ok = tma_ok && aligned(dY_list[d], 16);
+    if (!tma_ok && n_dest > 1) return TERNIX_B200_ERR_UNSUPPORTED;
+    CUtensorMap tmap_a, tmap_w;
+    int rc = make_tmap_2d(&tmap_a, dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), 128,
+                          128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tmap_w, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K), static_cast<uint64_t>(N / 4),
+                      tb200::kTc3WpRowBytes, tb200::kTc3BK, CU_TENSOR_MAP_SWIZZLE_32B);
+    if (rc) return rc;
+    tb200::Tc3Stores stores{};
+    stores.count = tma_ok ? n_dest : 0;
+    for (int d = 0; d < stores.count; ++d) {
+        rc = make_tmap_2d_u16(&stores.tmap_c[d], dY_list[d], static_cast<uint64_t>(N), static_cast<uint64_t>(M),
+                              static_cast<uint64_t>(ldy) * 2, 128, 32);
+        if (rc) return rc;
+    }
+    const long tiles = static_cast<long>((M + tb200::kTc3TileA - 1) / tb200::kTc3TileA) *
+                       ((N + tb200::kTc3TileW - 1) / tb200::kTc3TileW);
+    const long max_pairs = sm_count() / 2;
+    const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(tb200::kTc3Threads, 1, 1);
+    cfg.dynamicSmemBytes = tb200::kTc3SmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    TB_CUDA(cudaLaunchKernelEx(&cfg, kern, tmap_a, tmap_w, stores, static_cast<int32_t*>(dY_list[0]), M, K, N, ldy,
+                               static_cast<const tb200::Tc3Problem*>(nullptr), static_cast<const tb200::Tc2Tile*>(nullptr),
+                               static_cast<const int*>(nullptr), d_status, row_scale, w_scale));
+    return TERNIX_B200_OK;
+}
+
 int launch_gemm_tc2_bf16(const int8_t* dA, const uint8_t* dW, void* const* dY_list, int n_dest, const float* row_scale,
                          float w_scale, int M, int K, int N, long long ldy, int32_t* d_status, cudaStream_t st) {
+    bool tc3 = true;
+    if (const char* env = std::getenv("TERNIX_B200_TC3")) tc3 = std::atoi(env) != 0;
+    if (tc3) {
+        const int rc3 = launch_gemm_tc3_bf16(dA, dW, dY_list, n_dest, row_scale, w_scale, M, K, N, ldy, d_status, st);
+        if (rc3 != TERNIX_B200_ERR_UNSUPPORTED) return rc3;
+    }
     using G = tb200::Tc2Geom;
     auto kern = tb200::ternary_gemm_tc2_kernel<false, true>;
     static std::once_flag once;
