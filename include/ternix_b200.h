@@ -87,7 +87,9 @@ int ternix_b200_select_kernel(const void *dA, const void *dW, const void *dC, in
  *           src/cuda_kernels.cu:142-156.  HOST pointers: allocates, copies in, runs, copies back,
  *           frees, synchronises.  Also the target of the CPU-named ternix::mul_mat_ternary_* shims.
  *           The device buffer comes from a stream-ordered pool private to this library and is returned to
- *           it before the call ends; the pool keeps the pages so later calls skip the driver allocation. */
+ *           it before the call ends; the pool keeps the pages so later calls skip the driver allocation.
+ *           Above 64 MB of C the call runs as a pipeline over slabs of C on three private streams (inputs of
+ *           the next slab up, current slab computed, previous slab down); the bytes of C are the same. */
 int ternix_b200_matmul_host(const int8_t *A, const uint8_t *W_packed, int32_t *C, int M, int K, int N, int kernel);
 
 /* ---- problem groups: many projections per launch ----------------------------------------------
