@@ -1,7 +1,8 @@
 // Source-compatible with the reference's include/ternix/cuda_kernels.cuh:11-21.
 //
-// C[M,N] (int32) = A[M,K] (int8) x W[K,N] (ternary, packed 4 per byte as K x N/4).
-// Device-pointer variants are asynchronous on `stream` and return the launch status.
+// The product computed by all three: an int32 matrix C of M rows and N columns from int8 activations A (M x K) and
+// ternary weights W (K x N) that stay packed, one byte per four consecutive columns, i.e. K rows of N/4 bytes.
+// The two device-pointer entry points only enqueue work on `stream` and report the launch status.
 #pragma once
 #include <cuda_runtime.h>
 #include <cstdint>
@@ -19,7 +20,8 @@ cudaError_t mul_mat_ternary_cuda_naive(const int8_t* dA, const uint8_t* dB, int3
 cudaError_t mul_mat_ternary_cuda_tiled(const int8_t* dA, const uint8_t* dB, int32_t* dC,
                                        int M, int K, int N, cudaStream_t stream = 0);
 
-// Convenience wrapper on host pointers (allocates, copies, runs, copies back, frees).
+// The same product for operands in host memory: device buffers, both uploads, the kernel, the download of C and a
+// synchronisation all happen inside the call (`tiled` keeps the multiple-of-64 contract above).
 cudaError_t mul_mat_ternary_cuda_host(const int8_t* A, const uint8_t* B_packed, int32_t* C,
                                       int M, int K, int N, bool tiled);
 

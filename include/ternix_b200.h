@@ -41,6 +41,17 @@ extern "C" {
 #define TERNIX_B200_KERNEL_GEMM_TC  3  /* prefill regime: TMA + tcgen05 kind::i8, int32 in TMEM       */
 #define TERNIX_B200_KERNEL_DECODE_MMA 4 /* batched decode (a few to a few dozen rows): TMA-streamed   */
                                        /* packed W decoded in registers into mma.sync.m16n8k32       */
+#define TERNIX_B200_KERNEL_SKINNY_TC 5 /* batched decode, 1..64 rows: TMA-streamed packed W decoded   */
+                                       /* into tensor memory as the A operand of tcgen05 kind::i8     */
+
+/* ---- what a single-product call launched (ternix_b200_last_launched_kernel) ------------------- */
+#define TERNIX_B200_LAUNCHED_GENERIC     1
+#define TERNIX_B200_LAUNCHED_GEMV        2
+#define TERNIX_B200_LAUNCHED_GEMM_TC1    3  /* single-CTA tcgen05 tiles, weights expanded in shared memory */
+#define TERNIX_B200_LAUNCHED_DECODE_MMA  4
+#define TERNIX_B200_LAUNCHED_SKINNY_TC   5
+#define TERNIX_B200_LAUNCHED_GEMM_TC2    6  /* paired CTAs, weights expanded in shared memory              */
+#define TERNIX_B200_LAUNCHED_GEMM_TC3    7  /* paired CTAs, weights decoded into tensor memory             */
 
 const char *ternix_b200_status_string(int status);
 /* cudaError_t (as int) of the last failing CUDA call made by the calling thread, 0 if none. */
@@ -49,6 +60,22 @@ int ternix_b200_last_cuda_error(void);
 const char *ternix_b200_cuda_error_string(int cuda_error);
 /* Library version, major*10000 + minor*100 + patch. */
 int ternix_b200_version(void);
+/* The kernel the calling thread's last ternix_b200_matmul / _matmul_ex / _matmul_bcast call launched
+ * (TERNIX_B200_LAUNCHED_*, 0 if none) and that kernel's name, so a benchmark can report what actually ran. */
+int ternix_b200_last_launched_kernel(void);
+const char *ternix_b200_launched_kernel_name(int launched);
+/* Tuning options.  The defaults are the measured best; tests and experiments force the other paths.  Each option is
+ * read once from the environment variable TERNIX_B200_<NAME> when the library is first used and can be changed
+ * afterwards only here (value NULL or "" restores the default); do not change options while another thread
+ * launches.  Names: tc3 (0|1), tc_bn (0|2|128|256), tc_ksplit (0|1), gemv_plan ("words,ksplit"), group_words
+ * (16|32), mma_rows ("lo,hi"), mma_slices, mma_cluster (0|2|4|8), skinny_rows ("lo,hi"), skinny_group_rows (lo, 0 = never), skinny_split (0|1|2),
+ * host_slab (<columns>|r<rows>|0).  Unknown name: TERNIX_B200_ERR_INVALID_ARG. */
+int ternix_b200_set_option(const char *name, const char *value);
+/* The host-pointer entry point (and the unfused dequantising path) take device memory from a stream-ordered pool
+ * private to this library, which keeps up to 1 GiB of freed blocks per device for the next call, where the
+ * reference's wrapper frees everything before it returns (src/cuda_kernels.cu:153).  This call hands all cached
+ * blocks of every device back to the driver. */
+int ternix_b200_release_cached_memory(void);
 
 /* ---- host side: the packed weight format -------------------------------------------------------
  * replaces: ternix::pack_ternary_weights / unpack_ternary_weights / interleave_weights_offline,
@@ -91,6 +118,31 @@ int ternix_b200_select_kernel(const void *dA, const void *dW, const void *dC, in
  *           Above 64 MB of C the call runs as a pipeline over slabs of C on three private streams (inputs of
  *           the next slab up, current slab computed, previous slab down); the bytes of C are the same. */
 int ternix_b200_matmul_host(const int8_t *A, const uint8_t *W_packed, int32_t *C, int M, int K, int N, int kernel);
+
+/* ---- weight handle -----------------------------------------------------------------------------------
+ * No reference counterpart (the reference has no weight object on this path; interleave_weights_offline,
+ * src/bitpack.cpp:29-33, is its placeholder for one).  create() encodes the TMA descriptors of a packed weight matrix
+ * once, for every kernel family that can take it; matmul() is ternix_b200_matmul_ex with AUTO dispatch that encodes
+ * nothing for operands it has seen on the previous call (the handle remembers the last A and C it was given), so a
+ * steady decode loop makes no cuTensorMapEncodeTiled call at all.  Allocates no device memory.  dW must stay valid
+ * while the handle lives.  A handle may be shared by threads; its calls take a mutex for the descriptor cache. */
+typedef struct ternix_b200_weights ternix_b200_weights;
+int ternix_b200_weights_create(ternix_b200_weights **out, const uint8_t *dW, int K, int N);
+int ternix_b200_weights_matmul(ternix_b200_weights *weights, const int8_t *dA, int32_t *dC, int M, long long ldc,
+                               int32_t *d_status, void *stream);
+void ternix_b200_weights_destroy(ternix_b200_weights *weights);
+
+/* replaces: ternix::pack_ternary_weights (src/bitpack.cpp:5-15) for weights that are already on the device: the same
+ * bytes as ternix_b200_pack_ternary, produced by a kernel.  `size` counts weights; size/4 bytes are written. */
+int ternix_b200_pack_ternary_device(uint8_t *d_packed, const int8_t *d_unpacked, size_t size, void *stream);
+
+/* Self-test of the bounded device-side waits, with no counterpart in the reference: launches one small CTA in which
+ * one warp waits, for at most limit_ns (<= 100 ms), on a shared-memory barrier nobody arrives on; the wait runs out,
+ * the CTA takes the same abort and drain path as the product kernels, writes TERNIX_B200_ERR_TIMEOUT into *d_status
+ * (atomicMax) and the nanoseconds it waited into *d_waited_ns (may be NULL), and returns.  Nothing faults and the
+ * context stays usable. */
+int ternix_b200_selftest_wait_timeout(unsigned long long limit_ns, int32_t *d_status, unsigned long long *d_waited_ns,
+                                      void *stream);
 
 /* ---- problem groups: many projections per launch ----------------------------------------------
  * No reference counterpart (the reference launches one product at a time; its README lists
@@ -143,10 +195,13 @@ void ternix_b200_group_destroy(ternix_b200_group *group);
  *   - Limits: at most 256 problems and 4096 work items (one item per 512-column chunk per group of up to
  *     4 rows) per call; beyond that TERNIX_B200_ERR_TOO_LARGE.  Only decode-regime problems are taken
  *     (M <= 16, K <= 8192, K % 16 == 0, N % 64 == 0, 16-byte aligned A and W), else
- *     TERNIX_B200_ERR_UNSUPPORTED.  The fixed array is 116,992 bytes and every GPU that loads the library
+ *     TERNIX_B200_ERR_UNSUPPORTED.  The fixed array is 117,504 bytes and every GPU that loads the library
  *     holds it until the process exits (ternix_b200_gemv_batch_noalloc_limits reports the numbers).
  *   - The first call on a device looks up the array's device address (with that device current); make that
  *     first call outside any stream capture.
+ *   - A call on a stream that is being captured is refused with TERNIX_B200_ERR_UNSUPPORTED: the tables are
+ *     uploaded from one fixed host buffer, and a graph would read that buffer at replay time, after later calls
+ *     have rewritten it.  A member with K == 0 gets its C zeroed, as in the single-product calls.
  *   - All calls share the one array and each call rewrites the tables it uses, so nothing needs clearing,
  *     but two calls whose work overlaps on the GPU (different streams, or a second call issued before the
  *     first one's kernel has finished on another stream) race on it.  Calls on one stream are safe. */

@@ -37,13 +37,17 @@ KERNEL_GENERIC = 1
 KERNEL_GEMV = 2
 KERNEL_GEMM_TC = 3
 KERNEL_DECODE_MMA = 4
+KERNEL_SKINNY_TC = 5
 KERNELS = {"auto": KERNEL_AUTO, "generic": KERNEL_GENERIC, "gemv": KERNEL_GEMV, "gemm_tc": KERNEL_GEMM_TC,
-           "decode_mma": KERNEL_DECODE_MMA}
+           "decode_mma": KERNEL_DECODE_MMA, "skinny_tc": KERNEL_SKINNY_TC}
 
 # every symbol include/ternix_b200.h declares
 EXPORTS = (
     "ternix_b200_status_string", "ternix_b200_last_cuda_error", "ternix_b200_cuda_error_string",
-    "ternix_b200_version",
+    "ternix_b200_version", "ternix_b200_last_launched_kernel", "ternix_b200_launched_kernel_name",
+    "ternix_b200_set_option", "ternix_b200_release_cached_memory",
+    "ternix_b200_weights_create", "ternix_b200_weights_matmul", "ternix_b200_weights_destroy",
+    "ternix_b200_pack_ternary_device", "ternix_b200_selftest_wait_timeout",
     "ternix_b200_pack_ternary", "ternix_b200_unpack_ternary", "ternix_b200_interleave_offline",
     "ternix_b200_find_non_ternary", "ternix_b200_slice_columns",
     "ternix_b200_matmul", "ternix_b200_matmul_ex", "ternix_b200_select_kernel", "ternix_b200_matmul_host",
@@ -83,6 +87,15 @@ def _load() -> ctypes.CDLL:
         "ternix_b200_last_cuda_error": (i32, []),
         "ternix_b200_cuda_error_string": (c.c_char_p, [i32]),
         "ternix_b200_version": (i32, []),
+        "ternix_b200_last_launched_kernel": (i32, []),
+        "ternix_b200_launched_kernel_name": (c.c_char_p, [i32]),
+        "ternix_b200_set_option": (i32, [c.c_char_p, c.c_char_p]),
+        "ternix_b200_release_cached_memory": (i32, []),
+        "ternix_b200_weights_create": (i32, [c.POINTER(vp), vp, i32, i32]),
+        "ternix_b200_weights_matmul": (i32, [vp, vp, vp, i32, i64, vp, vp]),
+        "ternix_b200_weights_destroy": (None, [vp]),
+        "ternix_b200_pack_ternary_device": (i32, [vp, vp, sz, vp]),
+        "ternix_b200_selftest_wait_timeout": (i32, [c.c_ulonglong, vp, vp, vp]),
         "ternix_b200_pack_ternary": (None, [vp, vp, sz]),
         "ternix_b200_unpack_ternary": (None, [vp, vp, sz]),
         "ternix_b200_interleave_offline": (None, [vp, vp, sz]),
@@ -140,6 +153,22 @@ def _check(status: int, where: str) -> None:
     if status in (ERR_INVALID_SHAPE, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_TOO_LARGE):
         raise ValueError(msg)
     raise TernixError(status, msg)
+
+
+def set_option(name: str, value=None) -> None:
+    """Sets a tuning option of the library (ternix_b200_set_option); value None restores the default."""
+    v = None if value is None else str(value).encode()
+    _check(lib.ternix_b200_set_option(name.encode(), v), f"set_option({name})")
+
+
+def last_launched_kernel() -> str:
+    """Name of the kernel the calling thread's last single-product call launched."""
+    return lib.ternix_b200_launched_kernel_name(lib.ternix_b200_last_launched_kernel()).decode()
+
+
+def release_cached_memory() -> None:
+    """Hands the device memory cached by the host-pointer entry point back to the driver."""
+    _check(lib.ternix_b200_release_cached_memory(), "release_cached_memory")
 
 
 def _np_ptr(a: np.ndarray) -> ctypes.c_void_p:
@@ -255,6 +284,63 @@ def matmul(a, w_packed, out=None, kernel: str = "auto", status=None, stream=None
                                        KERNELS[kernel], status.data_ptr() if status is not None else None,
                                        s.cuda_stream)
     _check(rc, "matmul")
+    return out
+
+
+class TernaryWeights:
+    """A packed weight matrix on the device with its TMA descriptors encoded once (ternix_b200_weights_create):
+    matmul() through the handle encodes nothing for operands it saw on the previous call."""
+
+    def __init__(self, w_packed):
+        import torch
+
+        if not w_packed.is_cuda or w_packed.dtype != torch.uint8 or w_packed.dim() != 2 or not w_packed.is_contiguous():
+            raise ValueError("TernaryWeights takes a contiguous CUDA uint8 (K, N/4) tensor")
+        self.w = w_packed
+        self.K, self.N = w_packed.shape[0], w_packed.shape[1] * 4
+        h = ctypes.c_void_p()
+        with torch.cuda.device(w_packed.device):
+            _check(lib.ternix_b200_weights_create(ctypes.byref(h), w_packed.data_ptr(), self.K, self.N), "weights_create")
+        self._h = h
+
+    def matmul(self, a, out=None, status=None, stream=None):
+        import torch
+
+        if not a.is_cuda or a.dtype != torch.int8 or a.dim() != 2 or not a.is_contiguous() or a.shape[1] != self.K:
+            raise ValueError("A must be a contiguous CUDA int8 (M, K) tensor")
+        M = a.shape[0]
+        if out is None:
+            out = torch.empty((M, self.N), dtype=torch.int32, device=a.device)
+        if out.dtype != torch.int32 or tuple(out.shape) != (M, self.N) or (self.N > 1 and out.stride(1) != 1):
+            raise ValueError("out must be (M, N) int32 with unit column stride")
+        ldc = out.stride(0) if M > 1 else max(self.N, out.stride(0))
+        s = stream if stream is not None else torch.cuda.current_stream(a.device)
+        with torch.cuda.device(a.device):
+            _check(lib.ternix_b200_weights_matmul(self._h, a.data_ptr(), out.data_ptr(), M, ldc,
+                                                  status.data_ptr() if status is not None else None, s.cuda_stream),
+                   "weights_matmul")
+        return out
+
+    def close(self):
+        if getattr(self, "_h", None) and lib is not None:
+            lib.ternix_b200_weights_destroy(self._h)
+        self._h = None
+
+    def __del__(self):
+        self.close()
+
+
+def pack_ternary_device(w):
+    """(K, N) int8 CUDA tensor in {-1,0,+1} -> (K, N/4) uint8 CUDA tensor, packed on the device
+    (ternix_b200_pack_ternary_device); the same bytes as pack_ternary()."""
+    import torch
+
+    if not w.is_cuda or w.dtype != torch.int8 or w.dim() != 2 or not w.is_contiguous() or w.shape[1] % 4:
+        raise ValueError("pack_ternary_device takes a contiguous CUDA int8 (K, N) tensor with N % 4 == 0")
+    out = torch.empty((w.shape[0], w.shape[1] // 4), dtype=torch.uint8, device=w.device)
+    with torch.cuda.device(w.device):
+        _check(lib.ternix_b200_pack_ternary_device(out.data_ptr(), w.data_ptr(), w.numel(),
+                                                   torch.cuda.current_stream(w.device).cuda_stream), "pack_ternary_device")
     return out
 
 

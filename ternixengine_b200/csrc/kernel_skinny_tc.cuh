@@ -1,0 +1,504 @@
+// Batched-decode kernel on the tcgen05 tensor core: up to 64 rows of activations against a stream of packed weights.
+//
+// As in the paired prefill kernel the product is computed transposed, C^T[n][m] = sum_k W[k][n] * A[m][k]: the
+// weights are the A operand of tcgen05.mma and live in TENSOR MEMORY (row = weight column = lane, four K-bytes per
+// 32-bit column), the activations are the B operand, straight from TMA in the K-major 128-byte-swizzle layout, with
+// the batch as the instruction's N (16, 32 or 64).  Nothing expanded is ever written to shared memory.
+//
+// Where it pays.  Measured on B200: a tcgen05.mma with M = 128 occupies the tensor unit for about 120 cycles whatever
+// its N (16, 32 and 64 rows take the same time; the instruction is sized for N = 256), so this kernel streams at most
+// one kilobyte of packed weights per SM and ~120 cycles, about 2.4 TB/s over the GPU, independent of the row count.
+// The warp-level mma.sync kernel (kernel_decode_mma.cuh) streams 5.5 TB/s up to 8 rows and 3.8 TB/s up to 16, but
+// needs one pass per 16 rows; from 17 rows up this kernel is the faster one (210 BitNet-2B projections: 225 us
+// against 288 us at 32 rows, 231 us against 538 us at 64 rows), and the dispatch uses it there.
+//
+// From packed bytes to the operand in 17 instructions per 1024 weights and warp:
+//   * a stage is 128 k-rows x 64 packed bytes (256 weight columns), TMA with the 64-byte swizzle;
+//   * ldmatrix.m16n16.x2.trans.b8 leaves, in lane (c, t) = (lane / 4, lane % 4), the bytes of k-rows 4t..4t+3 of packed
+//     byte column c of a 16-byte chunk -- exactly what lane (c, t) has to supply to tcgen05.st.16x128b for operand
+//     row c, columns t.  So the operand rows (tensor-memory lanes) are simply numbered the way the load delivers
+//     them: lane l of a 32-lane quarter holds weight column 4 (l % 8) + l / 8 of the quarter's 32, and no data moves
+//     between lanes at all.  The epilogue, which reads the accumulator lane by lane, undoes the numbering for free;
+//   * a field is decoded without sign extension: (T << (6 - 2f)) & 0xC0C0C0C0 leaves every byte as 0x00, 0x40 or
+//     0xC0, i.e. 0, +64, -64 as int8 (the two top bits of a byte ARE the sign-extended code).  The accumulators hold
+//     64 * sum; the final arithmetic shift by 6 is exact.  Bound 64 * 128 * K < 2^31, K <= 262143.
+//
+// Tensor memory (512 columns): two accumulator buffers x two 128-column blocks x NB columns, then a ring of operand
+// stages of 2 blocks x 32 columns each (6 stages for NB = 16 and 32, 4 for NB = 64).  Shared memory: a ring of 16
+// packed-weight stages (8 KB each: what is in flight from HBM) and a ring of 16 (8 for NB = 64) activation stages
+// (NB rows x 128 bytes).
+//
+// Roles (16 warps): 0 weight producer, 1 and 3 MMA issuers (one per 128-column block: a single thread's instruction
+// stream -- two waits, four instructions per MMA, a commit -- was what bounded the stage rate before it was split),
+// 2 activation producer, 4-11 expanders (lane quarter = warp % 4, the two warps of a quarter take the stages in
+// turn), 12-15 epilogue (lane quarter = warp % 4).
+//
+// Work.  Grouped launches walk a host-built list of (problem, 256-column block) items over the whole of K.  One
+// problem alone runs as whole-K items too whenever they occupy the machine reasonably (items of 128 columns, half a
+// weight box each, when there are at most as many as SMs; items of 256 columns when those fit in one round): all
+// CTAs then walk the weight rows together, which is the access pattern DRAM likes, and nothing has to be exchanged.
+// Only with more blocks than SMs the (block, stage) units are dealt out as ONE contiguous range per CTA, a block
+// being shared by CTAs with neighbouring indices.  Their partial sums travel through C itself: the CTA with the
+// lowest stages stores its raw partial tile into C and raises a flag, the next one adds its own on top, and the CTA
+// that holds the last stage shifts and stores the result.  Each CTA walks its range from the top, so the part it
+// shares with its successor is done first and nobody ever waits for a CTA with a higher index; every flag wait is
+// bounded like the barrier waits.  No atomics, no zeroing of C, no scratch memory beyond one flag per CTA; flags
+// carry a per-launch epoch, so they never need clearing.
+#pragma once
+#include <cuda.h>
+#include <cstdint>
+#include "kernel_gemm_tc3.cuh"
+#include "ptx_sm100.cuh"
+
+namespace tb200 {
+
+constexpr int kSkWStages = 16;                    // packed-weight ring (shared memory)
+constexpr int kSkBK = 128;                        // k-rows per stage
+constexpr int kSkItemCols = 256;                  // weight columns per item: two MMA blocks of 128
+constexpr int kSkWpRowBytes = kSkItemCols / 4;    // 64
+constexpr int kSkWpBytes = kSkBK * kSkWpRowBytes; // 8192
+constexpr int kSkThreads = 16 * 32;
+constexpr int kSkFirstExpandWarp = 4, kSkFirstEpilogueWarp = 12;
+constexpr uint32_t kSkStageCols = 64;              // operand stage: 2 blocks x 128 K-bytes = 2 x 32 columns
+constexpr int kSkMaxCtas = 256;                   // flags per launch slot
+
+template <int NB>
+struct SkGeom {
+    static_assert(NB == 16 || NB == 32 || NB == 64, "batch rows per instruction");
+    static constexpr int kActBytes = NB * 128;                   // one box: NB rows x 128 K-bytes, 128-byte swizzle
+    static constexpr int kTStages = NB == 64 ? 4 : 6;            // operand ring (tensor memory)
+    static constexpr int kAStages = NB == 64 ? 8 : 16;           // activation ring (shared memory): deep, because every CTA
+                                                                 // asks the L2 for the same few lines at the same time
+    static constexpr uint32_t kRingCol = 4 * NB;                 // after the accumulators: [buffer][block] x NB columns
+    static_assert(kRingCol + kTStages * kSkStageCols <= 512, "tensor memory budget");
+    static constexpr size_t kSmemBytes = 1024 + size_t(kSkWStages) * kSkWpBytes + size_t(kAStages) * kActBytes + 768;
+    // D = s32, A = B = s8, both K-major, N = NB, M = 128
+    static constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(NB >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+};
+
+struct alignas(64) SkProblem {
+    CUtensorMap tmap_w;        // packed W [K][N/4] bytes, box 64 B x 128 rows, 64-byte swizzle
+    CUtensorMap tmap_a;        // A [M][K] bytes, box 128 B x NB rows, 128-byte swizzle
+    int32_t* C;
+    long long ldc;
+    int M, K, N, pad;
+};
+struct SkItem {
+    int problem, block;
+};
+// One problem per launch.  Units are (column block, stage) pairs, CTA i takes the contiguous range
+// [i U / G, (i + 1) U / G).  `half_items`: a unit's column block is 128 columns wide (one half of a 256-column weight
+// box) and a CTA owns whole blocks -- the form for problems with few columns, where whole-K items of 128 columns
+// occupy more SMs than items of 256.  `whole_blocks`: ranges are cut at block boundaries, so no CTA shares a block.
+struct SkSingle {
+    int blocks, stages, whole_blocks, half_items;
+};
+
+// D[tmem] (+)= A[tmem] x B[smem desc], int8 x int8 -> int32, one CTA; the shared-memory descriptor is given as two
+// 32-bit halves (no 64-bit arithmetic in the issue loop).
+__device__ __forceinline__ void tc_mma_i8_tmem_a_lohi(uint32_t tmem_d, uint32_t tmem_a, uint32_t desc_lo, uint32_t desc_hi,
+                                                      uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], db, %4, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "r"(desc_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32_x16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+// 16 lanes x 32 columns (128 K-bytes of 16 operand rows) in one instruction: registers 2i, 2i+1 are rows lane/4 and
+// lane/4 + 8 at column 4i + lane%4.
+__device__ __forceinline__ void tmem_st_16x128_x8(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+// ldmatrix without a memory clobber: the loads of a stage are issued back to back and only ordered by their uses
+// (the stage's shared memory is stable between the barrier wait before and the barrier arrive after them).
+__device__ __forceinline__ void ldmatrix_x2_trans_b8_nc(uint32_t (&r)[4], uint32_t smem_addr) {
+    asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_addr));
+}
+// Field f of every byte of T as int8 scaled by 64: codes 0, 1, 3 -> 0, +64, -64.
+template <int F>
+__device__ __forceinline__ uint32_t decode_field_x64(uint32_t T) {
+    if constexpr (F == 3) return T & 0xC0C0C0C0u;
+    else return (T << (6 - 2 * F)) & 0xC0C0C0C0u;
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait for another CTA's flag to show this launch's epoch.
+__device__ __forceinline__ bool flag_wait(const int* flag, int epoch, volatile int* abort_flag) {
+    uint64_t t0 = 0;
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        if (ld_acquire_gpu(flag) == epoch) return true;
+        __nanosleep(64);
+        if ((spin & 63u) == 63u) {
+            if (*abort_flag) return false;
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) break;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+// The segments of one CTA: runs of stages [s0, s1) of one 256-column weight box, of which the 128-column blocks
+// [h0, h1) are computed.  Every warp role constructs its own walker and sees the same sequence.
+template <bool kGrouped>
+struct SkWalk {
+    const SkProblem* p;
+    int block, s0, s1, h0, h1;
+    bool add_prev;             // stages below s0 belong to the CTA before this one: add what it left in C
+    bool last;                 // holds the block's last stage: shift and store; otherwise store raw and raise the flag
+    // single problem
+    int lo, hi, stages, half_items;
+    // group
+    const SkProblem* probs;
+    const SkItem* items;
+    int idx, end;
+
+    __device__ __forceinline__ bool next() {
+        if constexpr (kGrouped) {
+            if (idx >= end) return false;
+            const SkItem it = items[idx++];
+            p = probs + it.problem;
+            block = it.block;
+            s0 = 0;
+            s1 = (p->K + kSkBK - 1) / kSkBK;
+            h0 = 0;
+            h1 = (block * kSkItemCols + 128 < p->N) ? 2 : 1;      // a ragged last box may hold one block only
+            add_prev = false;
+            last = true;
+            return true;
+        } else {
+            if (hi <= lo) return false;
+            const int b = (hi - 1) / stages;
+            const int first = max(lo, b * stages);
+            s0 = first - b * stages;
+            s1 = hi - b * stages;
+            add_prev = s0 > 0;
+            last = s1 == stages;
+            hi = first;
+            if (half_items) { block = b >> 1; h0 = b & 1; h1 = h0 + 1; }
+            else { block = b; h0 = 0; h1 = (block * kSkItemCols + 128 < p->N) ? 2 : 1; }
+            return true;
+        }
+    }
+};
+
+template <int NB, bool kGrouped>
+__global__ void __launch_bounds__(kSkThreads, 1)
+ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingle sg,
+                         const SkProblem* __restrict__ probs, const SkItem* __restrict__ items,
+                         const int* __restrict__ cta_first, int* __restrict__ flags, int epoch,
+                         int32_t* __restrict__ status) {
+    using G = SkGeom<NB>;
+    constexpr int TS = G::kTStages, AS = G::kAStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sW = base;                                              // [WStages][128 k][64]   64-byte swizzle
+    uint8_t* sAct = sW + kSkWStages * kSkWpBytes;                    // [AS][NB rows][128 k]   128-byte swizzle
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sAct + AS * G::kActBytes);
+    uint64_t* w_full = bars;                       // a packed-weight stage has landed
+    uint64_t* w_empty = w_full + kSkWStages;       // the four quarters have read it
+    uint64_t* a_full = w_empty + kSkWStages;       // an activation stage has landed
+    uint64_t* a_empty = a_full + AS;               // the MMAs that read an activation stage have retired
+    uint64_t* ready = a_empty + AS;                // the four quarters have written an operand stage
+    uint64_t* t_free = ready + TS;                 // the MMAs that read an operand stage have retired
+    uint64_t* acc_full = t_free + TS;              // [2]
+    uint64_t* acc_empty = acc_full + 2;            // [2]
+    uint64_t* drain = acc_empty + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* epi_count = reinterpret_cast<int*>(tmem_slot + 2);    // epilogue warps done with the one partial tile a CTA writes
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    auto make_walk = [&]() {
+        SkWalk<kGrouped> w{};
+        if constexpr (kGrouped) {
+            w.probs = probs; w.items = items;
+            w.idx = cta_first[blockIdx.x]; w.end = cta_first[blockIdx.x + 1];
+        } else {
+            w.p = &single;
+            w.stages = sg.stages;
+            w.half_items = sg.half_items;
+            const long long g = gridDim.x, i = blockIdx.x;
+            if (sg.whole_blocks) {
+                w.lo = static_cast<int>(i * sg.blocks / g) * sg.stages;
+                w.hi = static_cast<int>((i + 1) * sg.blocks / g) * sg.stages;
+            } else {
+                const long long units = static_cast<long long>(sg.blocks) * sg.stages;
+                w.lo = static_cast<int>(i * units / g);
+                w.hi = static_cast<int>((i + 1) * units / g);
+            }
+        }
+        return w;
+    };
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kSkWStages; ++s) {
+            mbar_init(&w_full[s], 1);
+            mbar_init(&w_empty[s], 4);
+        }
+        for (int s = 0; s < AS; ++s) {
+            mbar_init(&a_full[s], 1);
+            mbar_init(&a_empty[s], 1);
+        }
+        for (int s = 0; s < TS; ++s) {
+            mbar_init(&ready[s], 4);
+            mbar_init(&t_free[s], 2);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 2);
+            mbar_init(&acc_empty[b], 4);
+        }
+        mbar_init(drain, 2);
+        *abort_flag = 0;
+        *epi_count = 0;
+        mbar_init_fence();
+    }
+    if (warp == 1) {
+        tmem_alloc<512>(tmem_slot);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ================================================================ packed weights: HBM -> shared memory
+        if (lane == 0) {
+            if constexpr (!kGrouped) tma_prefetch_desc(&single.tmap_w);
+            uint32_t it = 0;
+            bool ok = true;
+            SkWalk<kGrouped> w = make_walk();
+            while (ok && w.next()) {
+                const int x = w.block * kSkWpRowBytes;
+                for (int s = w.s0; s < w.s1; ++s, ++it) {
+                    const uint32_t sl = it % kSkWStages;
+                    if (!mbar_wait_backoff(&w_empty[sl], ((it / kSkWStages) & 1) ^ 1, abort_flag, 32)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&w_full[sl], kSkWpBytes);
+                    tma_load_2d(sW + sl * kSkWpBytes, &w.p->tmap_w, x, s * kSkBK, &w_full[sl]);
+                }
+            }
+            if (!ok) {
+                const uint32_t first = it > kSkWStages ? it - kSkWStages : 0;
+                for (uint32_t j = first; j < it; ++j) mbar_drain(&w_full[j % kSkWStages], (j / kSkWStages) & 1);
+            }
+        }
+    } else if (warp == 2) {
+        // ================================================================ activations: L2 -> shared memory
+        if (lane == 0) {
+            if constexpr (!kGrouped) tma_prefetch_desc(&single.tmap_a);
+            uint32_t it = 0;
+            bool ok = true;
+            SkWalk<kGrouped> w = make_walk();
+            while (ok && w.next()) {
+                for (int s = w.s0; s < w.s1; ++s, ++it) {
+                    const uint32_t sl = it % AS;
+                    if (!mbar_wait_backoff(&a_empty[sl], ((it / AS) & 1) ^ 1, abort_flag, 32)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&a_full[sl], G::kActBytes);
+                    tma_load_2d(sAct + sl * G::kActBytes, &w.p->tmap_a, s * kSkBK, 0, &a_full[sl]);
+                }
+            }
+            if (!ok) {
+                const uint32_t first = it > AS ? it - AS : 0;
+                for (uint32_t j = first; j < it; ++j) mbar_drain(&a_full[j % AS], (j / AS) & 1);
+            }
+        }
+    } else if (warp == 1 || warp == 3) {
+        // ================================================================ MMA issuers
+        // Two threads, one per 128-column block of the box (different accumulators, so the order between them does not
+        // matter).  A single thread's instruction stream -- waits, descriptor arithmetic, four instructions per MMA --
+        // is what bounds the stage rate of this kernel, so it is split in two and kept short: ring positions and
+        // the descriptor's low word advance by additions, no division, no 64-bit arithmetic.
+        if (lane == 0) {
+            const uint32_t hsel = warp == 3 ? 1u : 0u;
+            const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);          // stride 1024 B, version 1, 128-byte swizzle
+            const uint32_t desc_lo0 = ((smem_u32(sAct) & 0x3FFFFu) >> 4) | (1u << 16);  // start address, leading offset 16 B
+            uint32_t sl = 0, ph_t = 0, al = 0, ph_a = 0, lt = 0;
+            bool ok = true;
+            SkWalk<kGrouped> w = make_walk();
+            for (; ok && w.next(); ++lt) {
+                const uint32_t ab = lt & 1;
+                if (!mbar_wait(&acc_empty[ab], ((lt >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const bool mine = hsel >= static_cast<uint32_t>(w.h0) && hsel < static_cast<uint32_t>(w.h1);
+                const uint32_t d = tmem_base + ab * (2 * NB) + hsel * NB;
+                uint32_t acc = 0;
+                for (int s = w.s0; s < w.s1; ++s) {
+                    if (!mbar_wait(&ready[sl], ph_t, abort_flag) || !mbar_wait(&a_full[al], ph_a, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    if (mine) {
+                        const uint32_t a_col = tmem_base + G::kRingCol + sl * kSkStageCols + hsel * 32;
+                        const uint32_t lo = desc_lo0 + al * (G::kActBytes >> 4);
+#pragma unroll
+                        for (int g = 0; g < kSkBK / 32; ++g) {
+                            tc_mma_i8_tmem_a_lohi(d, a_col + 8 * g, lo + 2 * g, desc_hi, G::kIdesc, acc);
+                            acc = 1;
+                        }
+                    }
+                    tc_commit(&t_free[sl]);
+                    if (++sl == TS) { sl = 0; ph_t ^= 1; }
+                    if (++al == AS) { al = 0; ph_a ^= 1; }
+                }
+                if (ok) tc_commit(&acc_full[ab]);
+            }
+            tc_commit(drain);                      // both issuers: nothing of theirs is in flight when tensor memory is freed
+            mbar_wait(drain, 0, abort_flag);
+        }
+    } else if (warp >= kSkFirstExpandWarp && warp < kSkFirstEpilogueWarp) {
+        // ================================================================ expanders: packed bytes -> operand rows in tensor memory
+        // The warp of lane quarter q writes operand rows 32q..32q+31 of both 128-column blocks: packed byte columns
+        // 32h + 8q .. +7 of a row, i.e. half (q & 1) of 16-byte chunk 2h + q / 2.
+        const uint32_t q = warp & 3;
+        const uint32_t turn = (warp - kSkFirstExpandWarp) >> 2;
+        const uint32_t r_in = lane & 15;
+        // ldmatrix.x2: matrix 0 = k-rows 0-15, matrix 1 = k-rows 16-31 of a 32-deep group; 64-byte rows, 64-byte swizzle
+        // (16-byte chunk ^= (row / 2) % 4)
+        const uint32_t row_off = (lane >> 4) * (16 * kSkWpRowBytes) + r_in * kSkWpRowBytes;
+        const uint32_t swz = (r_in >> 1) & 3;
+        const uint32_t off_h[2] = {row_off + ((((q >> 1) + 0) ^ swz) << 4), row_off + ((((q >> 1) + 2) ^ swz) << 4)};
+        const uint32_t w_sa = smem_u32(sW);
+        const uint32_t t_lane = (q * 32) << 16;
+        const bool odd = (q & 1) != 0;
+        uint32_t it = 0;
+        bool ok = true;
+        SkWalk<kGrouped> w = make_walk();
+        while (ok && w.next()) {
+            for (int s = w.s0; s < w.s1; ++s, ++it) {
+                if ((it & 1) != turn) continue;
+                const uint32_t sw = it % kSkWStages, st = it % TS;
+                if (!mbar_wait_backoff(&w_full[sw], (it / kSkWStages) & 1, abort_flag, 32)) { ok = false; break; }
+                const uint32_t wp = w_sa + sw * kSkWpBytes;
+                // all loads of the stage first, so that their latencies overlap
+                uint32_t m[2][kSkBK / 32][4];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    if (h < w.h0 || h >= w.h1) continue;
+#pragma unroll
+                    for (int g = 0; g < kSkBK / 32; ++g) ldmatrix_x2_trans_b8_nc(m[h][g], wp + g * (32 * kSkWpRowBytes) + off_h[h]);
+                }
+                if (!mbar_wait_backoff(&t_free[st], ((it / TS) & 1) ^ 1, abort_flag, 32)) { ok = false; break; }
+                tc_fence_after_sync();
+                // the MMAs of stage it - TS have retired, so its activation slot is free as well: one quarter passes that on
+                // (an ordinary arrive is cheaper than a second tcgen05.commit per stage)
+                if (q == 0 && lane == 0 && it >= static_cast<uint32_t>(TS)) mbar_arrive(&a_empty[(it - TS) % AS]);
+                const uint32_t a_col = tmem_base + G::kRingCol + st * kSkStageCols + t_lane;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    if (h < w.h0 || h >= w.h1) continue;
+                    uint32_t lo[16], hi[16];
+#pragma unroll
+                    for (int g = 0; g < kSkBK / 32; ++g) {
+                        const uint32_t X = odd ? m[h][g][1] : m[h][g][0], Y = odd ? m[h][g][3] : m[h][g][2];
+                        lo[4 * g + 0] = decode_field_x64<0>(X); lo[4 * g + 1] = decode_field_x64<1>(X);
+                        lo[4 * g + 2] = decode_field_x64<0>(Y); lo[4 * g + 3] = decode_field_x64<1>(Y);
+                        hi[4 * g + 0] = decode_field_x64<2>(X); hi[4 * g + 1] = decode_field_x64<3>(X);
+                        hi[4 * g + 2] = decode_field_x64<2>(Y); hi[4 * g + 3] = decode_field_x64<3>(Y);
+                    }
+                    tmem_st_16x128_x8(a_col + 32 * h, lo);
+                    tmem_st_16x128_x8(a_col + 32 * h + (16u << 16), hi);
+                }
+                tmem_st_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&w_empty[sw]);
+                    mbar_arrive(&ready[st]);
+                }
+            }
+        }
+    } else if (warp >= kSkFirstEpilogueWarp) {
+        // ================================================================ epilogue
+        // Thread = operand row = weight column; registers = batch rows.  Lane l of quarter q is weight column
+        // 32q + 4 (l % 8) + l / 8 of its 128-column block.
+        const uint32_t q = warp & 3;
+        const int col_in_block = 32 * q + 4 * (lane & 7) + (lane >> 3);
+        uint32_t lt = 0;
+        bool ok = true;
+        SkWalk<kGrouped> w = make_walk();
+        for (; ok && w.next(); ++lt) {
+            const uint32_t ab = lt & 1;
+            const SkProblem* p = w.p;
+            const int M = p->M, N = p->N;
+            const long long ldc = p->ldc;
+            if (!mbar_wait_backoff(&acc_full[ab], (lt >> 1) & 1, abort_flag, 64)) { ok = false; break; }
+            tc_fence_after_sync();
+            if (w.add_prev && !flag_wait(flags + blockIdx.x - 1, epoch, abort_flag)) { ok = false; break; }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (h < w.h0 || h >= w.h1) continue;
+                const int col = w.block * kSkItemCols + h * 128 + col_in_block;
+                int32_t* out = p->C + col;
+#pragma unroll
+                for (int c = 0; c < NB / 16; ++c) {
+                    uint32_t r[16];
+                    tmem_ld_32x32_x16(tmem_base + ((q * 32) << 16) + ab * (2 * NB) + h * NB + 16 * c, r);
+                    tmem_ld_wait();
+                    if (h == w.h1 - 1 && c == NB / 16 - 1) {      // everything has been read: the next segment may accumulate here
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_empty[ab]);
+                    }
+                    if (col >= N) continue;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int row = 16 * c + j;
+                        if (row < M) {
+                            int32_t* dst = out + static_cast<size_t>(row) * ldc;
+                            int32_t v = static_cast<int32_t>(r[j]);
+                            if (w.add_prev) v += __ldcg(dst);
+                            if (w.last) *dst = v >> 6;
+                            else __stcg(dst, v);
+                        }
+                    }
+                }
+            }
+            if (!w.last) {
+                // raise this CTA's flag once all four epilogue warps have stored their part of the partial tile
+                __threadfence();
+                __syncwarp();
+                if (lane == 0 && atomicAdd(epi_count, 1) == 3) {
+                    __threadfence();
+                    st_release_gpu(flags + blockIdx.x, epoch);
+                }
+            }
+        }
+    }
+
+    __syncwarp();
+    if (*abort_flag && lane == 0 && status) atomicMax(status, kStatusTimeout);
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc<512>(tmem_base);
+    }
+}
+
+}  // namespace tb200

@@ -79,7 +79,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false when the limit ran out or when another thread of the CTA has
 // already given up (*abort_flag != 0); the caller then leaves its loop and goes to teardown.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
     uint64_t t0 = 0;
     for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -87,7 +88,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             if (*abort_flag) return false;
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) break;
+            else if (now - t0 > limit_ns) break;
         }
     }
     *abort_flag = 1;
@@ -111,11 +112,11 @@ __device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity
     return false;
 }
 // Teardown helper: bounded wait with no abort check (used only after a timeout, to let copies land).
-__device__ __forceinline__ void mbar_drain(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ void mbar_drain(uint64_t* bar, uint32_t parity, uint64_t limit_ns = kWaitLimitNs) {
     const uint64_t t0 = global_timer_ns();
     for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
         if (mbar_try_wait(bar, parity)) return;
-        if ((spin & 63u) == 63u && global_timer_ns() - t0 > kWaitLimitNs) return;
+        if ((spin & 63u) == 63u && global_timer_ns() - t0 > limit_ns) return;
     }
 }
 

@@ -6,10 +6,12 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cctype>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 #include <new>
 #include <queue>
@@ -17,16 +19,17 @@
 
 #include "kernel_gemm_tc.cuh"
 #include "kernel_gemm_tc2.cuh"
-#include "kernel_gemm_tc2w.cuh"
 #include "kernel_gemm_tc3.cuh"
 #include "kernel_gemv.cuh"
 #include "kernel_decode_mma.cuh"
 #include "kernel_gemv_group.cuh"
 #include "kernel_generic.cuh"
+#include "kernel_skinny_tc.cuh"
 
 namespace {
 
 thread_local int g_last_cuda_error = 0;
+thread_local int g_last_launched = 0;      // TERNIX_B200_LAUNCHED_* of the calling thread's last single-product launch
 
 int cuda_fail(cudaError_t e) {
     g_last_cuda_error = static_cast<int>(e);
@@ -108,25 +111,125 @@ int make_tmap_2d_u16(CUtensorMap* out, const void* ptr, uint64_t row_elems, uint
 
 bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
-int sm_count() {
-    static int n = [] {
-        int dev = 0, v = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
-        return v;
-    }();
-    return n;
+constexpr int kMaxDevices = 64;
+
+int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    return dev;
 }
 
-// Stream-ordered memory pool of the host-pointer entry point, one per device, created on first use.
-int host_call_pool(cudaMemPool_t* out) {
+// SM count of the current device (cached per device).
+int sm_count() {
+    static std::atomic<int> cache[kMaxDevices] = {};
+    const int dev = current_device();
+    int n = cache[dev].load(std::memory_order_relaxed);
+    if (n > 0) return n;
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    cache[dev].store(v, std::memory_order_relaxed);
+    return v;
+}
+
+// Opt-in to more than 48 KB of dynamic shared memory.  The attribute belongs to the (kernel, device) pair, so it is
+// set once per device, with that device current; the state is per kernel because the kernel is a template argument.
+template <auto Kern>
+int ensure_smem_attr(size_t bytes) {
     static std::mutex mu;
-    static cudaMemPool_t pools[64] = {};
+    static unsigned char done[kMaxDevices] = {};
+    const int dev = current_device();
+    std::lock_guard<std::mutex> lock(mu);
+    if (done[dev]) return TERNIX_B200_OK;
+    const cudaError_t e = cudaFuncSetAttribute(Kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+    if (e != cudaSuccess) return cuda_fail(e);
+    done[dev] = 1;
+    return TERNIX_B200_OK;
+}
+
+// ---------------------------------------------------------------- tuning options
+// Defaults are the measured best; the tests force the other paths.  Read once from the environment
+// (TERNIX_B200_<NAME>) when the library is first used and changed afterwards only through ternix_b200_set_option;
+// the launch path reads plain fields.
+struct Options {
+    int tc3 = 1;                       // 0: the kernels that expand weights into shared memory instead of tensor memory
+    int tc_bn = 0;                     // 128 | 256: single-CTA tiles of that width; 2: paired CTAs; 0: by shape
+    int tc_ksplit = 1;                 // 0: no K split in the single-CTA kernel
+    int gemv_words = 0, gemv_split = 0;   // plan of the one-row kernel ("words,ksplit"), 0 = heuristic
+    int group_words = 0;               // 16 | 32: item width of the grouped one-row kernel, 0 = by membership
+    int mma_lo = 2, mma_hi = 64;       // rows served by the mma.sync decode kernel when skinny_hi < rows
+    int mma_slices = 0;                // K slices of a single mma.sync decode problem, 0 = cost model
+    int mma_cluster = -1;              // 0 | 2 | 4 | 8: cluster form of the same, -1 = largest that fits
+    int skinny_lo = 33, skinny_hi = 64; // rows of a single product served by the tensor-memory decode kernel (0,0 = never)
+    int skinny_group_lo = 17;          // the same for members of a problem group (one launch serves many products there)
+    int skinny_split = 1;              // 0: never share a block between CTAs; 1: only when blocks outnumber SMs; 2: whenever it evens the load
+    int host_slab = -1;                // slab extent of the pipelined host-pointer call; 0 = off, -1 = plan
+    bool host_slab_rows = false;
+};
+Options g_opt;
+std::mutex g_opt_mutex;
+
+int apply_option(const char* name, const char* value) {
+    const Options def;
+    const bool reset = !value || !*value;
+    auto num = [&](int d) { return reset ? d : std::atoi(value); };
+    if (!std::strcmp(name, "tc3")) g_opt.tc3 = num(def.tc3);
+    else if (!std::strcmp(name, "tc_bn")) g_opt.tc_bn = num(def.tc_bn);
+    else if (!std::strcmp(name, "tc_ksplit")) g_opt.tc_ksplit = num(def.tc_ksplit);
+    else if (!std::strcmp(name, "group_words")) g_opt.group_words = num(def.group_words);
+    else if (!std::strcmp(name, "mma_slices")) g_opt.mma_slices = num(def.mma_slices);
+    else if (!std::strcmp(name, "mma_cluster")) g_opt.mma_cluster = num(def.mma_cluster);
+    else if (!std::strcmp(name, "skinny_split")) g_opt.skinny_split = num(def.skinny_split);
+    else if (!std::strcmp(name, "gemv_plan")) {
+        g_opt.gemv_words = def.gemv_words; g_opt.gemv_split = def.gemv_split;
+        if (!reset) std::sscanf(value, "%d,%d", &g_opt.gemv_words, &g_opt.gemv_split);
+    } else if (!std::strcmp(name, "mma_rows")) {
+        g_opt.mma_lo = def.mma_lo; g_opt.mma_hi = def.mma_hi;
+        if (!reset) std::sscanf(value, "%d,%d", &g_opt.mma_lo, &g_opt.mma_hi);
+    } else if (!std::strcmp(name, "skinny_rows")) {
+        g_opt.skinny_lo = def.skinny_lo; g_opt.skinny_hi = def.skinny_hi;
+        if (!reset) std::sscanf(value, "%d,%d", &g_opt.skinny_lo, &g_opt.skinny_hi);
+    } else if (!std::strcmp(name, "skinny_group_rows")) {
+        g_opt.skinny_group_lo = reset ? def.skinny_group_lo : std::atoi(value);
+    } else if (!std::strcmp(name, "host_slab")) {
+        g_opt.host_slab = def.host_slab; g_opt.host_slab_rows = false;
+        if (!reset) {
+            g_opt.host_slab_rows = value[0] == 'r';
+            g_opt.host_slab = std::atoi(value + (g_opt.host_slab_rows ? 1 : 0));
+        }
+    } else return TERNIX_B200_ERR_INVALID_ARG;
+    return TERNIX_B200_OK;
+}
+
+const Options& options() {
+    static std::once_flag once;
+    std::call_once(once, [] {
+        static const char* const names[] = {"tc3", "tc_bn", "tc_ksplit", "gemv_plan", "group_words", "mma_rows", "mma_slices",
+                                            "mma_cluster", "skinny_rows", "skinny_group_rows", "skinny_split", "host_slab"};
+        std::lock_guard<std::mutex> lock(g_opt_mutex);
+        for (const char* n : names) {
+            char env[64] = "TERNIX_B200_";
+            size_t len = std::strlen(env);
+            for (const char* c = n; *c && len + 1 < sizeof env; ++c) env[len++] = static_cast<char>(std::toupper(*c));
+            env[len] = 0;
+            if (const char* v = std::getenv(env)) apply_option(n, v);
+        }
+    });
+    return g_opt;
+}
+
+// Stream-ordered memory pool of the host-pointer entry point, one per device, created on first use.  Freed blocks
+// stay in the pool up to kPoolKeepBytes so that repeated calls skip the driver allocation; what is above that goes
+// back to the driver at the next synchronisation, and ternix_b200_release_cached_memory() returns all of it.
+constexpr unsigned long long kPoolKeepBytes = 1ull << 30;
+std::mutex g_pool_mutex;
+cudaMemPool_t g_pools[kMaxDevices] = {};
+
+int host_call_pool(cudaMemPool_t* out) {
     int dev = 0;
     TB_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return TERNIX_B200_ERR_UNSUPPORTED;
-    std::lock_guard<std::mutex> lock(mu);
-    if (!pools[dev]) {
+    if (dev < 0 || dev >= kMaxDevices) return TERNIX_B200_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_pool_mutex);
+    if (!g_pools[dev]) {
         cudaMemPoolProps props{};
         props.allocType = cudaMemAllocationTypePinned;
         props.handleTypes = cudaMemHandleTypeNone;
@@ -134,11 +237,11 @@ int host_call_pool(cudaMemPool_t* out) {
         props.location.id = dev;
         cudaMemPool_t p = nullptr;
         TB_CUDA(cudaMemPoolCreate(&p, &props));
-        unsigned long long keep = ~0ull;          // keep freed pages for the next call
+        unsigned long long keep = kPoolKeepBytes;
         TB_CUDA(cudaMemPoolSetAttribute(p, cudaMemPoolAttrReleaseThreshold, &keep));
-        pools[dev] = p;
+        g_pools[dev] = p;
     }
-    *out = pools[dev];
+    *out = g_pools[dev];
     return TERNIX_B200_OK;
 }
 
@@ -159,18 +262,10 @@ constexpr int kGroupMmaMinRows = 2, kGroupMmaMaxRows = 64;
 bool decode_mma_ok(const void* dA, const void* dW, int M, int K, int N) {
     return M >= 1 && (N % 64) == 0 && (K % 16) == 0 && K >= 16 && K <= 65536 && aligned(dA, 16) && aligned(dW, 16);
 }
-// Rows from which the automatic choice prefers it to the one-row kernel's row groups, and up to which it prefers it
-// to the tcgen05 tiles (TERNIX_B200_MMA_ROWS="lo,hi" overrides; tuning aid).
-void decode_mma_rows(int* lo, int* hi) {
-    static int s_lo = 0, s_hi = 0;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        s_lo = 2;
-        s_hi = 64;
-        if (const char* env = std::getenv("TERNIX_B200_MMA_ROWS")) std::sscanf(env, "%d,%d", &s_lo, &s_hi);
-    });
-    *lo = s_lo;
-    *hi = s_hi;
+// Tensor-memory decode kernel (kernel_skinny_tc.cuh): up to 64 rows.
+bool skinny_ok(const void* dA, const void* dW, int M, int K, int N) {
+    return M >= 1 && M <= 64 && (N % 64) == 0 && (K % 16) == 0 && K >= 16 && K <= kMaxScaledK && aligned(dA, 16) &&
+           aligned(dW, 16);
 }
 
 bool gemm_tc2_ok(const void* dA, const void* dW, int M, int K, int N) {
@@ -178,9 +273,9 @@ bool gemm_tc2_ok(const void* dA, const void* dW, int M, int K, int N) {
 }
 
 int select_kernel(const void* dA, const void* dW, int M, int K, int N) {
-    int mma_lo = 0, mma_hi = 0;
-    decode_mma_rows(&mma_lo, &mma_hi);
-    if (M >= mma_lo && M <= mma_hi && decode_mma_ok(dA, dW, M, K, N)) return TERNIX_B200_KERNEL_DECODE_MMA;
+    const Options& o = options();
+    if (M >= o.skinny_lo && M <= o.skinny_hi && skinny_ok(dA, dW, M, K, N)) return TERNIX_B200_KERNEL_SKINNY_TC;
+    if (M >= o.mma_lo && M <= o.mma_hi && decode_mma_ok(dA, dW, M, K, N)) return TERNIX_B200_KERNEL_DECODE_MMA;
     if (gemv_ok(dW, M, K, N)) return TERNIX_B200_KERNEL_GEMV;
     if (gemm_tc_ok(dA, dW, K, N)) return TERNIX_B200_KERNEL_GEMM_TC;
     return TERNIX_B200_KERNEL_GENERIC;
@@ -228,11 +323,9 @@ GemvPlan plan_gemv_with(int M, int K, int N, int force_words, int force_split) {
 }
 
 GemvPlan plan_gemv(int M, int K, int N) {
-    // TERNIX_B200_GEMV_PLAN="words,ksplit" overrides the heuristic where that plan is feasible (tuning aid).
-    int force_words = 0, force_split = 0;
-    if (const char* env = std::getenv("TERNIX_B200_GEMV_PLAN")) std::sscanf(env, "%d,%d", &force_words, &force_split);
-    if (force_words || force_split) {
-        const GemvPlan p = plan_gemv_with(M, K, N, force_words, force_split);
+    const Options& o = options();      // option gemv_plan = "words,ksplit" overrides the heuristic where feasible
+    if (o.gemv_words || o.gemv_split) {
+        const GemvPlan p = plan_gemv_with(M, K, N, o.gemv_words, o.gemv_split);
         if (p.words) return p;
     }
     return plan_gemv_with(M, K, N, 0, 0);
@@ -243,13 +336,9 @@ int launch_gemv_t(const CUtensorMap& tmap, const int8_t* dA, int32_t* dC, int M,
                   const GemvPlan& p, int32_t* d_status, cudaStream_t st) {
     auto kern = tb200::ternary_gemv_kernel<MR, WORDS>;
     const size_t smem = tb200::gemv_smem_bytes<MR, WORDS>(p.krange);
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(tb200::gemv_smem_bytes<MR, WORDS>(tb200::kGemvMaxASlice / MR)));
-    });
-    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    if (const int rc = ensure_smem_attr<tb200::ternary_gemv_kernel<MR, WORDS>>(
+            tb200::gemv_smem_bytes<MR, WORDS>(tb200::kGemvMaxASlice / MR)))
+        return rc;
     const int chunks = (N + WORDS * 16 - 1) / (WORDS * 16);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(chunks * p.ksplit, (M + MR - 1) / MR, 1);
@@ -312,17 +401,11 @@ int make_mma_problem(tb200::MmaProblem* out, const int8_t* dA, const uint8_t* dW
 
 template <bool kSingle, int NG>
 int decode_mma_attr() {
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(tb200::ternary_decode_mma_kernel<kSingle, NG>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tb200::kMmaSmemBytes));
-    });
-    return attr_err == cudaSuccess ? TERNIX_B200_OK : cuda_fail(attr_err);
+    return ensure_smem_attr<tb200::ternary_decode_mma_kernel<kSingle, NG>>(tb200::kMmaSmemBytes);
 }
 
 // One problem: items enumerated in the kernel.  When whole-K items would leave most of the GPU idle the K range is
-// cut into slices that add into a zeroed C (TERNIX_B200_MMA_SLICES=<n> forces the slice count; tuning aid).
+// cut into slices that add into a zeroed C.
 template <int NG>
 int launch_decode_mma_t(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,
                         int32_t* d_status, cudaStream_t st) {
@@ -339,7 +422,8 @@ int launch_decode_mma_t(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M,
     const int resident = sm_count() * tb200::kMmaCtasPerSm;
     const int base_items = sg.chunks * sg.row_groups;
     // Slices of K buy parallelism (a lone CTA streams about 23 GB/s) and cost one red.global.add per output and
-    // slice (the L2 retires about 160 of them per ns), plus the zeroing of C.  Take the count with the smallest sum.
+    // slice (the L2 retires about 160 of them per ns), plus the zeroing of C.  Take the count with the smallest sum
+    // (option mma_slices forces the count).
     int slices = 1;
     {
         const double w_bytes = static_cast<double>(K) * (N / 4) * sg.row_groups;
@@ -353,16 +437,17 @@ int launch_decode_mma_t(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M,
             if (sl == 1 || total < best) { best = total; slices = sl; }
         }
     }
-    if (const char* env = std::getenv("TERNIX_B200_MMA_SLICES")) slices = std::max(1, std::min(std::atoi(env), sg.total_tiles));
-    // Cluster form: the largest cluster that still leaves one item per resident CTA (TERNIX_B200_MMA_CLUSTER=0|2|4|8
-    // overrides; tuning aid).
+    const Options& o = options();
+    if (o.mma_slices > 0) slices = std::max(1, std::min(o.mma_slices, sg.total_tiles));
+    // Cluster form: the largest cluster that still leaves one item per resident CTA (option mma_cluster = 0|2|4|8
+    // overrides; a forced slice count switches the cluster form off).
     int cluster = 0;
     for (int c : {8, 4, 2})
         if (base_items * c <= resident && sg.total_tiles >= 2 * c) { cluster = c; break; }
-    if (const char* env = std::getenv("TERNIX_B200_MMA_CLUSTER")) {
-        const int c = std::atoi(env);
+    if (o.mma_cluster >= 0) {
+        const int c = o.mma_cluster;
         cluster = ((c == 2 || c == 4 || c == 8) && base_items * c <= resident) ? c : 0;
-    } else if (std::getenv("TERNIX_B200_MMA_SLICES")) {
+    } else if (o.mma_slices > 0) {
         cluster = 0;
     }
     if (cluster) {
@@ -410,13 +495,7 @@ int launch_gemm_tc_t(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, in
                      int32_t* d_status, cudaStream_t st) {
     using G = tb200::TcGeom<BN>;
     auto kern = tb200::ternary_gemm_tc_kernel<BN>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(G::kSmemBytes));
-    });
-    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    if (const int arc = ensure_smem_attr<tb200::ternary_gemm_tc_kernel<BN>>(G::kSmemBytes)) return arc;
     CUtensorMap tmap_a, tmap_w;
     int rc = make_tmap_2d(&tmap_a, dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K),
                           tb200::kTcBK, tb200::kTcBM, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -429,7 +508,7 @@ int launch_gemm_tc_t(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, in
     int k_slices = 1;
     const int k_blocks = (K + tb200::kTcBK - 1) / tb200::kTcBK;
     if (tiles * 2 <= sm_count() && k_blocks >= 8) k_slices = static_cast<int>(std::min<long>(sm_count() / tiles, k_blocks / 4));
-    if (const char* env = std::getenv("TERNIX_B200_TC_KSPLIT")) { if (std::atoi(env) == 0) k_slices = 1; }
+    if (!options().tc_ksplit) k_slices = 1;
     if (k_slices > 1)
         TB_CUDA(cudaMemset2DAsync(dC, static_cast<size_t>(ldc) * 4, 0, static_cast<size_t>(N) * 4, M, st));
     const long items = tiles * k_slices;
@@ -440,32 +519,20 @@ int launch_gemm_tc_t(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, in
     return TERNIX_B200_OK;
 }
 
-// Paired-CTA kernels: clusters of two CTAs, one 256 x 256 (or, wide, 256 x 512) tile per cluster at a time.
-template <bool kWide>
-int launch_gemm_tc2_t(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
-                      long long ldc, int32_t* d_status, cudaStream_t st) {
-    constexpr size_t smem = kWide ? tb200::TcwGeom::kSmemBytes : tb200::Tc2Geom::kSmemBytes;
-    constexpr int tile_n = kWide ? tb200::kTcwTileN : tb200::kTc2TileN;
-    constexpr int wp_row_bytes = kWide ? tb200::TcwGeom::kWpRowBytes : tb200::Tc2Geom::kWpRowBytes;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        if constexpr (kWide)
-            attr_err = cudaFuncSetAttribute(tb200::ternary_gemm_tc2w_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(smem));
-        else
-            attr_err = cudaFuncSetAttribute(tb200::ternary_gemm_tc2_kernel<false>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    });
-    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+// Paired-CTA kernel that expands the weights into shared memory: clusters of two CTAs, one 256 x 256 tile per
+// cluster at a time.  Serves outputs the TMA unit cannot describe (and option tc3 = 0).
+int launch_gemm_tc2_expand(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
+                           long long ldc, int32_t* d_status, cudaStream_t st) {
+    constexpr size_t smem = tb200::Tc2Geom::kSmemBytes;
+    if (const int arc = ensure_smem_attr<tb200::ternary_gemm_tc2_kernel<false>>(smem)) return arc;
     CUtensorMap tmap_a, tmap_w;
     int rc = make_tmap_2d(&tmap_a, dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K),
                           tb200::kTcBK, tb200::kTcBM, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     rc = make_tmap_2d(&tmap_w, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K),
-                      static_cast<uint64_t>(N / 4), wp_row_bytes, tb200::kTcBK, CU_TENSOR_MAP_SWIZZLE_NONE);
+                      static_cast<uint64_t>(N / 4), tb200::Tc2Geom::kWpRowBytes, tb200::kTcBK, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
-    const long tiles = static_cast<long>((M + 255) / 256) * ((N + tile_n - 1) / tile_n);
+    const long tiles = static_cast<long>((M + 255) / 256) * ((N + tb200::kTc2TileN - 1) / tb200::kTc2TileN);
     const long max_pairs = sm_count() / 2;
     const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
     tb200::Tc2Dest dest{};
@@ -487,71 +554,30 @@ int launch_gemm_tc2_t(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_li
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if constexpr (kWide) {
-        // K-sliced tail: when the last round of tiles would occupy at most half of the pairs, split each of its
-        // tiles along K over the pairs (results are added into C, which is zeroed here for those tiles).
-        int tail_slices = 0;
-        const int m_tiles = (M + 255) / 256;
-        const int rest = static_cast<int>(tiles % pairs);
-        const int k_blocks = (K + tb200::kTcBK - 1) / tb200::kTcBK;
-        bool want_tail = n_dest == 1 && tiles > pairs && rest > 0 && rest * 2 <= pairs && k_blocks >= 16;
-        if (const char* env = std::getenv("TERNIX_B200_TC_TAIL")) want_tail = want_tail && std::atoi(env) != 0;
-        if (want_tail) {
-            tail_slices = std::min(pairs / rest, k_blocks / 4);
-            const long first = tiles - rest;
-            for (long tile = first; tile < tiles;) {               // zero C of the tail tiles, one memset per tile column
-                const long n_t = tile / m_tiles, m0 = tile % m_tiles;
-                long m1 = m0;
-                while (tile < tiles && tile / m_tiles == n_t) { m1 = tile % m_tiles; ++tile; }
-                const long r0 = m0 * 256, r1 = std::min<long>(M, (m1 + 1) * 256);
-                const long c0 = n_t * tile_n, c1 = std::min<long>(N, c0 + tile_n);
-                TB_CUDA(cudaMemset2DAsync(dC_list[0] + r0 * ldc + c0, static_cast<size_t>(ldc) * 4, 0,
-                                          static_cast<size_t>(c1 - c0) * 4, static_cast<size_t>(r1 - r0), st));
-            }
-        }
-        TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc2w_kernel, tmap_a, tmap_w, dest, M, K, N, ldc, c_vec_ok,
-                                   tail_slices, d_status));
-    } else {
-        TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc2_kernel<false>, tmap_a, tmap_w, dest, M, K, N, ldc,
-                                   c_vec_ok, static_cast<const tb200::Tc2Problem*>(nullptr),
-                                   static_cast<const tb200::Tc2Tile*>(nullptr), static_cast<const int*>(nullptr), d_status,
-                                   static_cast<const float*>(nullptr), 1.0f));
-    }
+    TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc2_kernel<false>, tmap_a, tmap_w, dest, M, K, N, ldc,
+                               c_vec_ok, static_cast<const tb200::Tc2Problem*>(nullptr),
+                               static_cast<const tb200::Tc2Tile*>(nullptr), static_cast<const int*>(nullptr), d_status,
+                               static_cast<const float*>(nullptr), 1.0f));
     return TERNIX_B200_OK;
 }
 
-// Wide tiles for large single-destination products.  With peer destinations the 256-wide kernel is used: its
-// accumulator is double-buffered, so the slower NVLink stores of the epilogue hide under the next tile's main
-// loop, which the single-buffered wide kernel cannot do.  TERNIX_B200_TC_WIDE=0|1 forces the choice.
 // Paired CTAs with the weights as the A operand in tensor memory (kernel_gemm_tc3.cuh).  Several destinations need
 // every C to be describable to the TMA unit (16-byte aligned base and pitch); ERR_UNSUPPORTED otherwise.
-int launch_gemm_tc3(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
-                    long long ldc, int32_t* d_status, cudaStream_t st) {
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(tb200::ternary_gemm_tc3_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(tb200::kTc3SmemBytes));
-    });
-    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
-    if (n_dest < 1 || n_dest > tb200::kTc3MaxDest) return TERNIX_B200_ERR_UNSUPPORTED;
-    bool tma_ok = (ldc % 4 == 0);
-    for (int d = 0; d < n_dest; ++d) tma_ok = tma_ok && aligned(dC_list[d], 16);
-    if (!tma_ok && n_dest > 1) return TERNIX_B200_ERR_UNSUPPORTED;
-    CUtensorMap tmap_a, tmap_w;
-    int rc = make_tmap_2d(&tmap_a, dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K),
-                          tb200::kTcBK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc) return rc;
-    rc = make_tmap_2d(&tmap_w, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K), static_cast<uint64_t>(N / 4),
-                      tb200::kTc3WpRowBytes, tb200::kTc3BK, CU_TENSOR_MAP_SWIZZLE_32B);
-    if (rc) return rc;
-    tb200::Tc3Stores stores{};
-    stores.count = tma_ok ? n_dest : 0;
-    for (int d = 0; d < stores.count; ++d) {
-        rc = make_tmap_2d_u32(&stores.tmap_c[d], dC_list[d], static_cast<uint64_t>(N), static_cast<uint64_t>(M),
-                              static_cast<uint64_t>(ldc) * 4, 128, 32);
-        if (rc) return rc;
-    }
+int make_tc3_act_map(CUtensorMap* out, const int8_t* dA, int M, int K) {
+    return make_tmap_2d(out, dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), tb200::kTcBK,
+                        128, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+int make_tc3_weight_map(CUtensorMap* out, const uint8_t* dW, int K, int N) {
+    return make_tmap_2d(out, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K), static_cast<uint64_t>(N / 4),
+                        tb200::kTc3WpRowBytes, tb200::kTc3BK, CU_TENSOR_MAP_SWIZZLE_32B);
+}
+int make_tc3_store_map(CUtensorMap* out, int32_t* dC, int M, int N, long long ldc) {
+    return make_tmap_2d_u32(out, dC, static_cast<uint64_t>(N), static_cast<uint64_t>(M), static_cast<uint64_t>(ldc) * 4, 128, 32);
+}
+
+int launch_gemm_tc3_maps(const CUtensorMap& tmap_a, const CUtensorMap& tmap_w, const tb200::Tc3Stores& stores, int32_t* dC0,
+                         int M, int K, int N, long long ldc, int32_t* d_status, cudaStream_t st) {
+    if (const int arc = ensure_smem_attr<tb200::ternary_gemm_tc3_kernel<false>>(tb200::kTc3SmemBytes)) return arc;
     const long tiles = static_cast<long>((M + tb200::kTc3TileA - 1) / tb200::kTc3TileA) *
                        ((N + tb200::kTc3TileW - 1) / tb200::kTc3TileW);
     const long max_pairs = sm_count() / 2;
@@ -571,39 +597,54 @@ int launch_gemm_tc3(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list
     const tb200::Tc3Problem* no_probs = nullptr;
     const tb200::Tc2Tile* no_tiles = nullptr;
     const int* no_first = nullptr;
-    TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc3_kernel<false>, tmap_a, tmap_w, stores, dC_list[0], M, K, N, ldc,
+    TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc3_kernel<false>, tmap_a, tmap_w, stores, dC0, M, K, N, ldc,
                                no_probs, no_tiles, no_first, d_status, static_cast<const float*>(nullptr), 1.0f));
     return TERNIX_B200_OK;
 }
 
-int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
+int launch_gemm_tc3(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
                     long long ldc, int32_t* d_status, cudaStream_t st) {
-    // The kernel that keeps the decoded weights in tensor memory, unless TERNIX_B200_TC3=0 asks for the kernels that
-    // expand them into shared memory (tuning aid) or a C among several destinations has no TMA view.
-    bool tc3 = true;
-    if (const char* env = std::getenv("TERNIX_B200_TC3")) tc3 = std::atoi(env) != 0;
-    if (tc3) {
+    if (n_dest < 1 || n_dest > tb200::kTc3MaxDest) return TERNIX_B200_ERR_UNSUPPORTED;
+    bool tma_ok = (ldc % 4 == 0);
+    for (int d = 0; d < n_dest; ++d) tma_ok = tma_ok && aligned(dC_list[d], 16);
+    if (!tma_ok && n_dest > 1) return TERNIX_B200_ERR_UNSUPPORTED;
+    CUtensorMap tmap_a, tmap_w;
+    int rc = make_tc3_act_map(&tmap_a, dA, M, K);
+    if (rc) return rc;
+    rc = make_tc3_weight_map(&tmap_w, dW, K, N);
+    if (rc) return rc;
+    tb200::Tc3Stores stores{};
+    stores.count = tma_ok ? n_dest : 0;
+    for (int d = 0; d < stores.count; ++d)
+        if ((rc = make_tc3_store_map(&stores.tmap_c[d], dC_list[d], M, N, ldc))) return rc;
+    return launch_gemm_tc3_maps(tmap_a, tmap_w, stores, dC_list[0], M, K, N, ldc, d_status, st);
+}
+
+int launch_gemm_tc2(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
+                    long long ldc, int32_t* d_status, cudaStream_t st, int* used = nullptr) {
+    // The kernel that keeps the decoded weights in tensor memory, unless option tc3 = 0 asks for the kernel that
+    // expands them into shared memory or a C among several destinations has no TMA view.
+    if (options().tc3) {
         const int rc = launch_gemm_tc3(dA, dW, dC_list, n_dest, M, K, N, ldc, d_status, st);
-        if (rc != TERNIX_B200_ERR_UNSUPPORTED) return rc;
+        if (rc != TERNIX_B200_ERR_UNSUPPORTED) {
+            if (used) *used = TERNIX_B200_LAUNCHED_GEMM_TC3;
+            return rc;
+        }
     }
-    bool wide = n_dest == 1 && N >= 1024 && K >= 1024;
-    if (const char* env = std::getenv("TERNIX_B200_TC_WIDE")) wide = std::atoi(env) != 0;
-    if (wide) return launch_gemm_tc2_t<true>(dA, dW, dC_list, n_dest, M, K, N, ldc, d_status, st);
-    return launch_gemm_tc2_t<false>(dA, dW, dC_list, n_dest, M, K, N, ldc, d_status, st);
+    if (used) *used = TERNIX_B200_LAUNCHED_GEMM_TC2;
+    return launch_gemm_tc2_expand(dA, dW, dC_list, n_dest, M, K, N, ldc, d_status, st);
 }
 
 int launch_gemm_tc(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,
-                   int32_t* d_status, cudaStream_t st) {
-    // TERNIX_B200_TC_BN=128|256 forces the single-CTA kernel at that tile width, TERNIX_B200_TC_BN=2 the
-    // paired-CTA kernel (tuning aids).  Default: pairs whenever there are rows for both CTAs of a pair.
-    int bn = 0;
-    if (const char* env = std::getenv("TERNIX_B200_TC_BN")) bn = std::atoi(env);
-    // Pairs from 65 rows up: the tensor-memory kernel pads a half-empty activation tile for nothing (rows beyond M
-    // arrive as zeros from TMA) and still beats the single-CTA tiles; TERNIX_B200_TC3=0 keeps the old limit of 128.
-    bool tc3_on = true;
-    if (const char* env = std::getenv("TERNIX_B200_TC3")) tc3_on = std::atoi(env) != 0;
-    const int pair_min_rows = tc3_on ? 64 : 128;
-    if (bn == 2 || (bn == 0 && M > pair_min_rows && N >= 256)) return launch_gemm_tc2(dA, dW, &dC, 1, M, K, N, ldc, d_status, st);
+                   int32_t* d_status, cudaStream_t st, int* used = nullptr) {
+    // Option tc_bn = 128|256 forces the single-CTA kernel at that tile width, tc_bn = 2 the paired-CTA kernels.
+    // Default: pairs from 65 rows up.  The tensor-memory kernel pads a half-empty activation tile for nothing (rows
+    // beyond M arrive as zeros from TMA) and still beats the single-CTA tiles; with tc3 = 0 the limit is 128 rows.
+    const Options& o = options();
+    int bn = o.tc_bn;
+    const int pair_min_rows = o.tc3 ? 64 : 128;
+    if (bn == 2 || (bn == 0 && M > pair_min_rows && N >= 256))
+        return launch_gemm_tc2(dA, dW, &dC, 1, M, K, N, ldc, d_status, st, used);
     if (bn != 128 && bn != 256) {
         const long m_tiles = (M + tb200::kTcBM - 1) / tb200::kTcBM;
         const long tiles256 = m_tiles * ((N + 255) / 256);
@@ -614,8 +655,202 @@ int launch_gemm_tc(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int 
         const bool split256 = tiles128 * 2 > sm_count() && tiles256 * 2 <= sm_count() && K >= 1024;
         bn = (N % 256 == 0 || N > 256) && (fill256 || split256) ? 256 : 128;
     }
+    if (used) *used = TERNIX_B200_LAUNCHED_GEMM_TC1;
     if (bn == 256) return launch_gemm_tc_t<256>(dA, dW, dC, M, K, N, ldc, d_status, st);
     return launch_gemm_tc_t<128>(dA, dW, dC, M, K, N, ldc, d_status, st);
+}
+
+// ---------------------------------------------------------------- tensor-memory decode kernel (kernel_skinny_tc.cuh)
+// CTAs of one launch that share a 256-column block hand their partial sums on through C and signal each other with
+// one flag per CTA.  The flags live in a file-scope device array (no allocation); a launch gets the slot of its
+// (device, stream) pair, because launches on one stream run one after the other and launches on different streams
+// may overlap.  When all slots of a device are taken by other streams the launch falls back to whole blocks per CTA,
+// which needs no flags.  Flags carry the launch's epoch, so nothing is ever cleared.
+constexpr int kSkFlagSlots = 32;
+__device__ int g_sk_flags[kSkFlagSlots * tb200::kSkMaxCtas];
+std::mutex g_sk_mutex;
+int* g_sk_flags_dev[kMaxDevices] = {};
+cudaStream_t g_sk_slot_stream[kMaxDevices][kSkFlagSlots] = {};
+bool g_sk_slot_used[kMaxDevices][kSkFlagSlots] = {};
+std::atomic<unsigned> g_sk_epoch{0};
+
+// Device address of the flag slot for (current device, stream); *out = nullptr when every slot belongs to another stream.
+int skinny_flag_slot(cudaStream_t st, int** out) {
+    *out = nullptr;
+    const int dev = current_device();
+    std::lock_guard<std::mutex> lock(g_sk_mutex);
+    if (!g_sk_flags_dev[dev]) {
+        void* p = nullptr;
+        TB_CUDA(cudaGetSymbolAddress(&p, g_sk_flags));      // with this device current: the symbol's copy on it
+        g_sk_flags_dev[dev] = static_cast<int*>(p);
+    }
+    int free_slot = -1;
+    for (int i = 0; i < kSkFlagSlots; ++i) {
+        if (g_sk_slot_used[dev][i] && g_sk_slot_stream[dev][i] == st) { *out = g_sk_flags_dev[dev] + i * tb200::kSkMaxCtas; return TERNIX_B200_OK; }
+        if (!g_sk_slot_used[dev][i] && free_slot < 0) free_slot = i;
+    }
+    if (free_slot >= 0) {
+        g_sk_slot_used[dev][free_slot] = true;
+        g_sk_slot_stream[dev][free_slot] = st;
+        *out = g_sk_flags_dev[dev] + free_slot * tb200::kSkMaxCtas;
+    }
+    return TERNIX_B200_OK;
+}
+
+int next_skinny_epoch() {
+    unsigned e = ++g_sk_epoch;
+    if ((e & 0x7fffffffu) == 0) e = ++g_sk_epoch;          // never 0: that is what fresh flags hold
+    return static_cast<int>(e & 0x7fffffffu);
+}
+
+int skinny_rows_class(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : 64; }
+
+int make_skinny_problem(tb200::SkProblem* out, const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N,
+                        long long ldc) {
+    *out = tb200::SkProblem{};
+    int rc = make_tmap_2d(&out->tmap_w, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K),
+                          static_cast<uint64_t>(N / 4), tb200::kSkWpRowBytes, tb200::kSkBK, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+    rc = make_tmap_2d(&out->tmap_a, dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), 128,
+                      skinny_rows_class(M), CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    out->C = dC;
+    out->ldc = ldc;
+    out->M = M;
+    out->K = K;
+    out->N = N;
+    return TERNIX_B200_OK;
+}
+
+template <int NB, bool kGrouped>
+int launch_skinny_t(const tb200::SkProblem& single, const tb200::SkSingle& sg, const tb200::SkProblem* d_probs,
+                    const tb200::SkItem* d_items, const int* d_first, int grid, int* d_flags, int epoch,
+                    int32_t* d_status, cudaStream_t st) {
+    if (const int arc = ensure_smem_attr<tb200::ternary_skinny_tc_kernel<NB, kGrouped>>(tb200::SkGeom<NB>::kSmemBytes))
+        return arc;
+    tb200::ternary_skinny_tc_kernel<NB, kGrouped><<<grid, tb200::kSkThreads, tb200::SkGeom<NB>::kSmemBytes, st>>>(
+        single, sg, d_probs, d_items, d_first, d_flags, epoch, d_status);
+    TB_CUDA(cudaGetLastError());
+    return TERNIX_B200_OK;
+}
+
+// The plan of one problem.  Whole-K items keep all CTAs on the same weight rows at the same time (the matrix streams
+// row by row, which is what DRAM likes) and need no exchange of partial sums, so they are taken whenever they occupy
+// the machine reasonably: items of 128 columns when there are at most as many as SMs, items of 256 columns when
+// those fit in one round.  Otherwise (more 256-column blocks than SMs, or option skinny_split = 2) the
+// (block, stage) units are dealt out as one contiguous range per CTA, a block being shared by at most a few CTAs
+// with neighbouring indices; that form needs a flag slot.
+void plan_skinny(int K, int N, bool can_split, int split_mode, tb200::SkSingle* sg, int* grid) {
+    const int blocks256 = (N + tb200::kSkItemCols - 1) / tb200::kSkItemCols, blocks128 = (N + 127) / 128;
+    sg->stages = (K + tb200::kSkBK - 1) / tb200::kSkBK;
+    const int sms = std::min(sm_count(), tb200::kSkMaxCtas);
+    sg->half_items = 0;
+    sg->whole_blocks = 1;
+    if (blocks128 <= sms && split_mode < 2) {
+        sg->half_items = 1;
+        sg->blocks = blocks128;
+        *grid = blocks128;
+        return;
+    }
+    sg->blocks = blocks256;
+    const bool want_split = can_split && (split_mode >= 2 || blocks256 > sms);
+    const long long units = static_cast<long long>(blocks256) * sg->stages;
+    const int min_units = std::max(2, (sg->stages + 1) / 2);       // at most three CTAs share a block
+    const int g = static_cast<int>(std::max<long long>(1, std::min<long long>(sms, units / min_units)));
+    if (want_split && !(g <= blocks256 && blocks256 % g == 0)) {
+        sg->whole_blocks = 0;
+        *grid = g;
+    } else {
+        *grid = std::min(sms, blocks256);
+    }
+}
+
+int launch_skinny_problem(const tb200::SkProblem& prob, int32_t* d_status, cudaStream_t st) {
+    tb200::SkSingle sg{};
+    int grid = 0;
+    int* d_flags = nullptr;
+    const int split_mode = options().skinny_split;
+    if (split_mode) {
+        const int rc = skinny_flag_slot(st, &d_flags);
+        if (rc) return rc;
+    }
+    plan_skinny(prob.K, prob.N, d_flags != nullptr, split_mode, &sg, &grid);
+    const int epoch = sg.whole_blocks ? 0 : next_skinny_epoch();
+    switch (skinny_rows_class(prob.M)) {
+        case 16: return launch_skinny_t<16, false>(prob, sg, nullptr, nullptr, nullptr, grid, d_flags, epoch, d_status, st);
+        case 32: return launch_skinny_t<32, false>(prob, sg, nullptr, nullptr, nullptr, grid, d_flags, epoch, d_status, st);
+        default: return launch_skinny_t<64, false>(prob, sg, nullptr, nullptr, nullptr, grid, d_flags, epoch, d_status, st);
+    }
+}
+
+int launch_skinny(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N, long long ldc,
+                  int32_t* d_status, cudaStream_t st) {
+    tb200::SkProblem prob;
+    const int rc = make_skinny_problem(&prob, dA, dW, dC, M, K, N, ldc);
+    if (rc) return rc;
+    return launch_skinny_problem(prob, d_status, st);
+}
+
+// ---------------------------------------------------------------- self-test of the bounded waits
+// What every kernel of this library does when a wait runs out, in isolation and with a short limit: warp 0 waits
+// for a shared-memory barrier that nobody will ever arrive on; when the limit ends it raises the CTA's abort flag;
+// warp 1, waiting on a second barrier, sees the flag and leaves too; the "copy in flight" is drained with the same
+// bounded helper; the CTA reports TERNIX_B200_ERR_TIMEOUT through the status word and returns.  No TMA, no tensor
+// memory, nothing that faults: the context stays usable.
+__global__ void wait_timeout_selftest_kernel(unsigned long long limit_ns, int32_t* __restrict__ status,
+                                             unsigned long long* __restrict__ waited_ns) {
+    __shared__ uint64_t bars[2];
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        tb200::mbar_init(&bars[0], 1);
+        tb200::mbar_init(&bars[1], 1);
+        abort_flag = 0;
+        tb200::mbar_init_fence();
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint64_t t0 = tb200::global_timer_ns();
+    bool ok = true;
+    if (lane == 0) {
+        if (warp == 0) ok = tb200::mbar_wait(&bars[0], 0, &abort_flag, limit_ns);
+        else ok = tb200::mbar_wait_backoff(&bars[1], 0, &abort_flag, 64);       // leaves through the abort flag
+        if (!ok && warp == 0) tb200::mbar_drain(&bars[1], 0, limit_ns);         // teardown path, bounded as well
+    }
+    __syncwarp();
+    if (abort_flag && lane == 0 && status) atomicMax(status, tb200::kStatusTimeout);
+    __syncthreads();
+    if (threadIdx.x == 0 && waited_ns) *waited_ns = tb200::global_timer_ns() - t0;
+}
+
+// Device-side packer: four consecutive int8 weights -> one byte, the arithmetic of the host packer
+// (code = 1 for +1, 3 for -1, else 0; field j in bits 2j..2j+1).  One thread packs 16 weights into 4 bytes.
+__global__ void pack_ternary_kernel(const int8_t* __restrict__ w, uint8_t* __restrict__ packed, size_t n_bytes) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    const size_t n_words = n_bytes / 4;
+    auto code4 = [](uint32_t v) {      // four int8 in a word -> four 2-bit codes in the low byte
+        uint32_t out = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int8_t x = static_cast<int8_t>(v >> (8 * j));
+            out |= (x == 1 ? 1u : x == -1 ? 3u : 0u) << (2 * j);
+        }
+        return out;
+    };
+    const bool vec = (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(packed) & 3) == 0;
+    if (vec) {
+        for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n_words; i += stride) {
+            const uint4 v = reinterpret_cast<const uint4*>(w)[i];
+            reinterpret_cast<uint32_t*>(packed)[i] = code4(v.x) | (code4(v.y) << 8) | (code4(v.z) << 16) | (code4(v.w) << 24);
+        }
+    }
+    // tail bytes (and everything, when the pointers are not aligned for the vector path)
+    const size_t first = vec ? n_words * 4 : 0;
+    for (size_t b = first + blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; b < n_bytes; b += stride) {
+        uint32_t v = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v |= static_cast<uint32_t>(static_cast<uint8_t>(w[4 * b + j])) << (8 * j);
+        packed[b] = static_cast<uint8_t>(code4(v));
+    }
 }
 
 // Rank-major gather buffer -> row-major C.
@@ -675,9 +910,37 @@ struct ternix_b200_group {
         int grid = 0;
     } mma[2];
     size_t mma_grouped = 0;
+    // batched-decode members served by the tensor-memory kernel: one launch per batch class (16, 32, 64 rows)
+    struct SkTables {
+        void* d_blob = nullptr;                 // [SkProblem[] | SkItem[] | int cta_first[]]
+        const tb200::SkProblem* d_probs = nullptr;
+        const tb200::SkItem* d_items = nullptr;
+        const int* d_first = nullptr;
+        int grid = 0;
+    } sk[3];
+    size_t sk_grouped = 0;
     // members the grouped kernels could not take but that have peer destinations: copied after their launch
     struct PeerCopy { ternix_b200_problem q; std::vector<int32_t*> peers; };
     std::vector<PeerCopy> single_peers;
+};
+
+// A weight matrix with its TMA descriptors encoded once (ternix_b200_weights_create).  A single-product launch
+// otherwise spends more host time in cuTensorMapEncodeTiled than the decode kernels run for; with the handle a
+// launch encodes nothing for operands it has seen before.
+struct ternix_b200_weights {
+    const uint8_t* dW = nullptr;
+    int K = 0, N = 0, device = 0;
+    bool fast = false;                 // N % 64 == 0, K % 16 == 0, 16-byte aligned: the TMA kernels apply
+    CUtensorMap tmap_w_skinny{}, tmap_w_tc3{};
+    std::mutex mu;                     // guards the one-entry caches below
+    // last activation operand seen per kernel family, and last output
+    const int8_t* a_ptr[2] = {nullptr, nullptr};
+    int a_rows[2] = {0, 0};
+    CUtensorMap tmap_a[2] = {};
+    int32_t* c_ptr = nullptr;
+    int c_rows = 0;
+    long long c_ld = 0;
+    CUtensorMap tmap_c{};
 };
 
 namespace {
@@ -686,12 +949,7 @@ template <int MR, int WORDS, bool PRE>
 int launch_gemv_group_t(const ternix_b200_group* g, int32_t* d_status, cudaStream_t st) {
     auto kern = tb200::ternary_gemv_group_kernel<MR, WORDS, PRE>;
     constexpr size_t smem = tb200::gemv_group_smem_bytes<MR, WORDS>();
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    });
-    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    if (const int arc = ensure_smem_attr<tb200::ternary_gemv_group_kernel<MR, WORDS, PRE>>(smem)) return arc;
     kern<<<g->grid, tb200::kGemvThreads, smem, st>>>(g->d_probs, g->d_items, g->d_cta_first, d_status);
     TB_CUDA(cudaGetLastError());
     return TERNIX_B200_OK;
@@ -699,13 +957,7 @@ int launch_gemv_group_t(const ternix_b200_group* g, int32_t* d_status, cudaStrea
 
 int launch_gemm_tc3_group(const ternix_b200_group* g, int32_t* d_status, cudaStream_t st) {
     auto kern = tb200::ternary_gemm_tc3_kernel<true>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(tb200::kTc3SmemBytes));
-    });
-    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    if (const int arc = ensure_smem_attr<tb200::ternary_gemm_tc3_kernel<true>>(tb200::kTc3SmemBytes)) return arc;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * g->tc_pairs, 1, 1);
     cfg.blockDim = dim3(tb200::kTc3Threads, 1, 1);
@@ -730,13 +982,7 @@ int launch_gemm_tc2_group(const ternix_b200_group* g, int32_t* d_status, cudaStr
     if (g->d_tc3_probs) return launch_gemm_tc3_group(g, d_status, st);
     using G = tb200::Tc2Geom;
     auto kern = tb200::ternary_gemm_tc2_kernel<true>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(G::kSmemBytes));
-    });
-    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    if (const int arc = ensure_smem_attr<tb200::ternary_gemm_tc2_kernel<true>>(G::kSmemBytes)) return arc;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * g->tc_pairs, 1, 1);
     cfg.blockDim = dim3(tb200::kTc2Threads, 1, 1);
@@ -813,13 +1059,7 @@ __global__ void dequant_rows_kernel(const int32_t* __restrict__ C, long long ldc
 int launch_gemm_tc3_bf16(const int8_t* dA, const uint8_t* dW, void* const* dY_list, int n_dest, const float* row_scale,
                          float w_scale, int M, int K, int N, long long ldy, int32_t* d_status, cudaStream_t st) {
     auto kern = tb200::ternary_gemm_tc3_kernel<false, true>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(tb200::kTc3SmemBytes));
-    });
-    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    if (const int arc = ensure_smem_attr<tb200::ternary_gemm_tc3_kernel<false, true>>(tb200::kTc3SmemBytes)) return arc;
     if (n_dest < 1 || n_dest > tb200::kTc3MaxDest) return TERNIX_B200_ERR_UNSUPPORTED;
     bool tma_ok = (ldy % 8 == 0);
     for (int d = 0; d < n_dest; ++d) tma_ok = tma_ok && aligned(dY_list[d], 16);
@@ -862,21 +1102,13 @@ int launch_gemm_tc3_bf16(const int8_t* dA, const uint8_t* dW, void* const* dY_li
 
 int launch_gemm_tc2_bf16(const int8_t* dA, const uint8_t* dW, void* const* dY_list, int n_dest, const float* row_scale,
                          float w_scale, int M, int K, int N, long long ldy, int32_t* d_status, cudaStream_t st) {
-    bool tc3 = true;
-    if (const char* env = std::getenv("TERNIX_B200_TC3")) tc3 = std::atoi(env) != 0;
-    if (tc3) {
+    if (options().tc3) {
         const int rc3 = launch_gemm_tc3_bf16(dA, dW, dY_list, n_dest, row_scale, w_scale, M, K, N, ldy, d_status, st);
         if (rc3 != TERNIX_B200_ERR_UNSUPPORTED) return rc3;
     }
     using G = tb200::Tc2Geom;
     auto kern = tb200::ternary_gemm_tc2_kernel<false, true>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(G::kSmemBytes));
-    });
-    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    if (const int arc = ensure_smem_attr<tb200::ternary_gemm_tc2_kernel<false, true>>(G::kSmemBytes)) return arc;
     CUtensorMap tmap_a, tmap_w;
     int rc = make_tmap_2d(&tmap_a, dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K),
                           tb200::kTcBK, tb200::kTcBM, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -918,11 +1150,11 @@ int launch_gemm_tc2_bf16(const int8_t* dA, const uint8_t* dW, void* const* dY_li
 // cudaMalloc'ed block.  Every GPU that loads the library carries it until the process exits.
 constexpr int kNoAllocMaxProblems = 256;
 constexpr int kNoAllocMaxItems = 4096;
-constexpr int kNoAllocMaxCtas = 512;
+constexpr int kNoAllocMaxCtas = 640;          // 148 SMs x 4 resident CTAs of the one-row kernel, with room
 constexpr size_t kNoAllocProbBytes = size_t(kNoAllocMaxProblems) * sizeof(tb200::GroupProblem);
 constexpr size_t kNoAllocItemBytes = size_t(kNoAllocMaxItems) * sizeof(tb200::GroupItem);
 constexpr size_t kNoAllocFirstBytes = ((size_t(kNoAllocMaxCtas) + 1) * sizeof(int) + 255) & ~size_t(255);
-constexpr size_t kNoAllocBytes = kNoAllocProbBytes + kNoAllocItemBytes + kNoAllocFirstBytes;   // 116,992 bytes
+constexpr size_t kNoAllocBytes = kNoAllocProbBytes + kNoAllocItemBytes + kNoAllocFirstBytes;   // 117,504 bytes
 static_assert(kNoAllocProbBytes % 256 == 0 && kNoAllocItemBytes % 256 == 0, "sub-tables stay 256-byte aligned");
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
@@ -962,12 +1194,7 @@ int launch_gemv_group_tables(const tb200::GroupProblem* d_probs, const tb200::Gr
                              int grid, int32_t* d_status, cudaStream_t st) {
     auto kern = tb200::ternary_gemv_group_kernel<MR, WORDS>;
     constexpr size_t smem = tb200::gemv_group_smem_bytes<MR, WORDS>();
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    });
-    if (attr_err != cudaSuccess) return cuda_fail(attr_err);
+    if (const int arc = ensure_smem_attr<tb200::ternary_gemv_group_kernel<MR, WORDS>>(smem)) return arc;
     kern<<<grid, tb200::kGemvThreads, smem, st>>>(d_probs, d_items, d_first, d_status);
     TB_CUDA(cudaGetLastError());
     return TERNIX_B200_OK;
@@ -994,7 +1221,35 @@ int ternix_b200_last_cuda_error(void) { return g_last_cuda_error; }
 const char* ternix_b200_cuda_error_string(int cuda_error) {
     return cudaGetErrorString(static_cast<cudaError_t>(cuda_error));
 }
-int ternix_b200_version(void) { return 100; }
+int ternix_b200_version(void) { return 200; }
+
+int ternix_b200_set_option(const char* name, const char* value) {
+    if (!name) return TERNIX_B200_ERR_INVALID_ARG;
+    options();                                   // the environment is read first, once
+    std::lock_guard<std::mutex> lock(g_opt_mutex);
+    return apply_option(name, value);
+}
+
+int ternix_b200_last_launched_kernel(void) { return g_last_launched; }
+const char* ternix_b200_launched_kernel_name(int id) {
+    switch (id) {
+        case TERNIX_B200_LAUNCHED_GENERIC: return "ternary_generic_kernel";
+        case TERNIX_B200_LAUNCHED_GEMV: return "ternary_gemv_kernel";
+        case TERNIX_B200_LAUNCHED_GEMM_TC1: return "ternary_gemm_tc_kernel";
+        case TERNIX_B200_LAUNCHED_DECODE_MMA: return "ternary_decode_mma_kernel";
+        case TERNIX_B200_LAUNCHED_SKINNY_TC: return "ternary_skinny_tc_kernel";
+        case TERNIX_B200_LAUNCHED_GEMM_TC2: return "ternary_gemm_tc2_kernel";
+        case TERNIX_B200_LAUNCHED_GEMM_TC3: return "ternary_gemm_tc3_kernel";
+        default: return "none";
+    }
+}
+
+int ternix_b200_release_cached_memory(void) {
+    std::lock_guard<std::mutex> lock(g_pool_mutex);
+    for (int dev = 0; dev < kMaxDevices; ++dev)
+        if (g_pools[dev]) TB_CUDA(cudaMemPoolTrimTo(g_pools[dev], 0));
+    return TERNIX_B200_OK;
+}
 
 int ternix_b200_select_kernel(const void* dA, const void* dW, const void* dC, int M, int K, int N, long long ldc) {
     (void)dC;
@@ -1009,7 +1264,7 @@ int ternix_b200_matmul_ex(const int8_t* dA, const uint8_t* dW, int32_t* dC, int 
     // tests/test_cuda_matmul.cu:41-43).
     if (M < 0 || K < 0 || N < 0 || (N % 4) != 0) return TERNIX_B200_ERR_INVALID_SHAPE;
     if (ldc < N) return TERNIX_B200_ERR_INVALID_ARG;
-    if (kernel < TERNIX_B200_KERNEL_AUTO || kernel > TERNIX_B200_KERNEL_DECODE_MMA) return TERNIX_B200_ERR_INVALID_ARG;
+    if (kernel < TERNIX_B200_KERNEL_AUTO || kernel > TERNIX_B200_KERNEL_SKINNY_TC) return TERNIX_B200_ERR_INVALID_ARG;
     if (M == 0 || N == 0) return TERNIX_B200_OK;
     if (!dC || (K > 0 && (!dA || !dW))) return TERNIX_B200_ERR_INVALID_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -1021,14 +1276,21 @@ int ternix_b200_matmul_ex(const int8_t* dA, const uint8_t* dW, int32_t* dC, int 
     switch (kernel) {
         case TERNIX_B200_KERNEL_GEMV:
             if (!gemv_ok(dW, M, K, N)) return TERNIX_B200_ERR_UNSUPPORTED;
+            g_last_launched = TERNIX_B200_LAUNCHED_GEMV;
             return launch_gemv(dA, dW, dC, M, K, N, ldc, d_status, st);
         case TERNIX_B200_KERNEL_GEMM_TC:
             if (!gemm_tc_ok(dA, dW, K, N)) return TERNIX_B200_ERR_UNSUPPORTED;
-            return launch_gemm_tc(dA, dW, dC, M, K, N, ldc, d_status, st);
+            return launch_gemm_tc(dA, dW, dC, M, K, N, ldc, d_status, st, &g_last_launched);
         case TERNIX_B200_KERNEL_DECODE_MMA:
             if (!decode_mma_ok(dA, dW, M, K, N)) return TERNIX_B200_ERR_UNSUPPORTED;
+            g_last_launched = TERNIX_B200_LAUNCHED_DECODE_MMA;
             return launch_decode_mma(dA, dW, dC, M, K, N, ldc, d_status, st);
+        case TERNIX_B200_KERNEL_SKINNY_TC:
+            if (!skinny_ok(dA, dW, M, K, N)) return TERNIX_B200_ERR_UNSUPPORTED;
+            g_last_launched = TERNIX_B200_LAUNCHED_SKINNY_TC;
+            return launch_skinny(dA, dW, dC, M, K, N, ldc, d_status, st);
         default:
+            g_last_launched = TERNIX_B200_LAUNCHED_GENERIC;
             return launch_generic(dA, dW, dC, M, K, N, ldc, st);
     }
 }
@@ -1173,7 +1435,7 @@ int matmul_host_pipelined(const int8_t* A, const uint8_t* Wp, int32_t* C, int M,
 // Slab plan of a host-pointer product: the slab extent (0 = single-shot path) and whether slabs are rows.  About
 // 64 MB of C per slab, at most 16 slabs.  Column slabs (multiples of 512 columns, at least 4096 wide so that the
 // pitched copy of C keeps long rows) are taken when A is the smaller operand to wait for; row slabs (multiples of
-// 256 rows) otherwise.  TERNIX_B200_HOST_SLAB=<columns>, or r<rows>, overrides; 0 switches the pipeline off.
+// 256 rows) otherwise.  Option host_slab = <columns>, or r<rows>, overrides; 0 switches the pipeline off.
 int host_slab_plan(int M, int K, int N, bool* by_rows) {
     *by_rows = false;
     if (K <= 0 || (N % 64) != 0) return 0;
@@ -1182,11 +1444,11 @@ int host_slab_plan(int M, int K, int N, bool* by_rows) {
         while ((extent + v - 1) / v > HostPipe::kMaxSlabs) v += unit;
         return v >= extent ? 0ll : v;
     };
-    if (const char* env = std::getenv("TERNIX_B200_HOST_SLAB")) {
-        *by_rows = env[0] == 'r';
-        const long long want = std::atoll(env + (*by_rows ? 1 : 0));
-        if (want <= 0) return 0;
-        return static_cast<int>(*by_rows ? fit(M, want, 256) : fit(N, want, 512));
+    const Options& o = options();
+    if (o.host_slab >= 0) {
+        *by_rows = o.host_slab_rows;
+        if (o.host_slab == 0) return 0;
+        return static_cast<int>(*by_rows ? fit(M, o.host_slab, 256) : fit(N, o.host_slab, 512));
     }
     const size_t c_bytes = static_cast<size_t>(M) * N * sizeof(int32_t);
     if (c_bytes < (size_t(64) << 20)) return 0;
@@ -1202,7 +1464,7 @@ extern "C" {
 
 int ternix_b200_matmul_host(const int8_t* A, const uint8_t* Wp, int32_t* C, int M, int K, int N, int kernel) {
     if (M < 0 || K < 0 || N < 0 || (N % 4) != 0) return TERNIX_B200_ERR_INVALID_SHAPE;
-    if (kernel < TERNIX_B200_KERNEL_AUTO || kernel > TERNIX_B200_KERNEL_DECODE_MMA) return TERNIX_B200_ERR_INVALID_ARG;
+    if (kernel < TERNIX_B200_KERNEL_AUTO || kernel > TERNIX_B200_KERNEL_SKINNY_TC) return TERNIX_B200_ERR_INVALID_ARG;
     if (M == 0 || N == 0) return TERNIX_B200_OK;
     if (!C || (K > 0 && (!A || !Wp))) return TERNIX_B200_ERR_INVALID_ARG;
     bool by_rows = false;
@@ -1298,21 +1560,24 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
 
     // Item width: 256 columns (64-byte rows) when every decode member has one row: the finer items balance better
     // over the SMs (measured +1..4 %); 512 columns (128-byte rows) for row groups, where the wider item wins.
-    // TERNIX_B200_GROUP_WORDS=16|32 overrides (tuning aid).
+    // Option group_words = 16|32 overrides.
     g->prepacked = prepacked;
+    const Options& opt = options();
+    // rows below this stay with the dp4a kernel: the batched-decode kernels take over from their first row count
+    const int decode_rows_end = opt.skinny_group_lo > 0 ? std::min(kGroupMmaMinRows, opt.skinny_group_lo) : kGroupMmaMinRows;
     int decode_max_m = 0;
     for (int i = 0; i < count; ++i)
         if (problems[i].M > 0 && problems[i].N > 0 && group_gemv_ok(problems[i]) &&
             !(problems[i].K > 0 && gemm_tc2_ok(problems[i].dA, problems[i].dW, problems[i].M, problems[i].K, problems[i].N)))
-            if (prepacked || problems[i].M < kGroupMmaMinRows) decode_max_m = std::max(decode_max_m, problems[i].M);
+            if (prepacked || problems[i].M < decode_rows_end) decode_max_m = std::max(decode_max_m, problems[i].M);
     g->words = (!prepacked && decode_max_m == 1) ? 16 : 32;
-    if (const char* env = std::getenv("TERNIX_B200_GROUP_WORDS")) g->words = (!prepacked && std::atoi(env) == 16) ? 16 : 32;
+    if (options().group_words) g->words = (!prepacked && options().group_words == 16) ? 16 : 32;
     const int item_cols = g->words * 16;
     std::vector<tb200::Tc2Problem> tc_probs;
     std::vector<tb200::Tc3Problem> tc3_probs;
-    bool tc3_group = true;                                // TERNIX_B200_TC3=0: the expanding kernel (tuning aid)
-    if (const char* env = std::getenv("TERNIX_B200_TC3")) tc3_group = std::atoi(env) != 0;
+    bool tc3_group = options().tc3 != 0;                  // option tc3 = 0: the expanding kernel
     std::vector<tb200::MmaProblem> mma_probs[2];          // row groups of 8, of 16
+    std::vector<tb200::SkProblem> sk_probs[3];            // batch classes 16, 32, 64
     std::vector<tb200::GroupProblem> probs;
     struct HostItem { tb200::GroupItem item; long cost; };
     std::vector<HostItem> items;
@@ -1367,6 +1632,15 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
             ternix_b200_group::PeerCopy pc{q, {}};
             for (int j = 0; j < n_peers; ++j) pc.peers.push_back(peer_dC[static_cast<size_t>(i) * n_peers + j]);
             g->single_peers.push_back(pc);
+        }
+        if (!prepacked && opt.skinny_group_lo > 0 && q.M >= opt.skinny_group_lo && q.M <= 64 && q.K > 0 &&
+            skinny_ok(q.dA, q.dW, q.M, q.K, q.N)) {
+            tb200::SkProblem sp;
+            const int rc = make_skinny_problem(&sp, q.dA, q.dW, q.dC, q.M, q.K, q.N, q.ldc);
+            if (rc) { delete g; return rc; }
+            sk_probs[q.M <= 16 ? 0 : q.M <= 32 ? 1 : 2].push_back(sp);
+            ++g->sk_grouped;
+            continue;
         }
         if (!prepacked && q.M >= kGroupMmaMinRows && q.M <= kGroupMmaMaxRows && q.K > 0 && q.ldc >= q.N &&
             decode_mma_ok(q.dA, q.dW, q.M, q.K, q.N)) {
@@ -1542,6 +1816,55 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
         mt.d_first = reinterpret_cast<const int*>(d + b_probs + b_items);
         mt.grid = ctas;
     }
+    for (int v = 0; v < 3; ++v) {
+        if (sk_probs[v].empty()) continue;
+        // whole-K items of 256 columns in (problem, block) order, dealt out to the least-loaded CTA: with equal costs
+        // neighbouring CTAs stream neighbouring blocks of the same weight rows at the same time
+        struct HostSkItem { tb200::SkItem item; long cost; };
+        std::vector<HostSkItem> hi;
+        for (int pi = 0; pi < static_cast<int>(sk_probs[v].size()); ++pi) {
+            const tb200::SkProblem& sp = sk_probs[v][pi];
+            const int blocks = (sp.N + tb200::kSkItemCols - 1) / tb200::kSkItemCols;
+            for (int b = 0; b < blocks; ++b) hi.push_back({{pi, b}, static_cast<long>(sp.K) + 256});
+        }
+        const int ctas = static_cast<int>(std::min<size_t>(hi.size(), static_cast<size_t>(sm_count())));
+        std::stable_sort(hi.begin(), hi.end(), [](const HostSkItem& a, const HostSkItem& b) { return a.cost > b.cost; });
+        using Load = std::pair<long, int>;
+        std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
+        for (int c = 0; c < ctas; ++c) heap.push({0, c});
+        std::vector<std::vector<tb200::SkItem>> per_cta(ctas);
+        for (const HostSkItem& h : hi) {
+            Load l = heap.top();
+            heap.pop();
+            per_cta[l.second].push_back(h.item);
+            heap.push({l.first + h.cost, l.second});
+        }
+        std::vector<tb200::SkItem> flat;
+        std::vector<int> first(ctas + 1, 0);
+        for (int c = 0; c < ctas; ++c) {
+            first[c] = static_cast<int>(flat.size());
+            flat.insert(flat.end(), per_cta[c].begin(), per_cta[c].end());
+        }
+        first[ctas] = static_cast<int>(flat.size());
+        const size_t b_probs = sk_probs[v].size() * sizeof(tb200::SkProblem);
+        const size_t b_items = (flat.size() * sizeof(tb200::SkItem) + 63) & ~size_t(63);
+        const size_t b_first = first.size() * sizeof(int);
+        auto& t = g->sk[v];
+        cudaError_t e = cudaMalloc(&t.d_blob, b_probs + b_items + b_first);
+        if (e != cudaSuccess) { ternix_b200_group_destroy(g); return cuda_fail(e); }
+        uint8_t* d = static_cast<uint8_t*>(t.d_blob);
+        if ((e = cudaMemcpy(d, sk_probs[v].data(), b_probs, cudaMemcpyHostToDevice)) != cudaSuccess ||
+            (e = cudaMemcpy(d + b_probs, flat.data(), flat.size() * sizeof(tb200::SkItem), cudaMemcpyHostToDevice)) !=
+                cudaSuccess ||
+            (e = cudaMemcpy(d + b_probs + b_items, first.data(), b_first, cudaMemcpyHostToDevice)) != cudaSuccess) {
+            ternix_b200_group_destroy(g);
+            return cuda_fail(e);
+        }
+        t.d_probs = reinterpret_cast<const tb200::SkProblem*>(d);
+        t.d_items = reinterpret_cast<const tb200::SkItem*>(d + b_probs);
+        t.d_first = reinterpret_cast<const int*>(d + b_probs + b_items);
+        t.grid = ctas;
+    }
     *out = g;
     return TERNIX_B200_OK;
 }
@@ -1619,6 +1942,17 @@ int ternix_b200_group_run(const ternix_b200_group* g, int32_t* d_status, void* s
                 none, sg, mt.d_probs, mt.d_items, mt.d_first, d_status);
         TB_CUDA(cudaGetLastError());
     }
+    for (int v = 0; v < 3; ++v) {
+        const auto& t = g->sk[v];
+        if (t.grid == 0) continue;
+        const tb200::SkProblem none{};
+        const tb200::SkSingle sg{};
+        int rc;
+        if (v == 0) rc = launch_skinny_t<16, true>(none, sg, t.d_probs, t.d_items, t.d_first, t.grid, nullptr, 0, d_status, st);
+        else if (v == 1) rc = launch_skinny_t<32, true>(none, sg, t.d_probs, t.d_items, t.d_first, t.grid, nullptr, 0, d_status, st);
+        else rc = launch_skinny_t<64, true>(none, sg, t.d_probs, t.d_items, t.d_first, t.grid, nullptr, 0, d_status, st);
+        if (rc) return rc;
+    }
     for (const ternix_b200_problem& q : g->singles) {
         const int rc = ternix_b200_matmul_ex(q.dA, q.dW, q.dC, q.M, q.K, q.N, q.ldc, TERNIX_B200_KERNEL_AUTO, d_status,
                                              stream);
@@ -1633,8 +1967,10 @@ int ternix_b200_group_run(const ternix_b200_group* g, int32_t* d_status, void* s
 
 int ternix_b200_group_launches(const ternix_b200_group* g) {
     if (!g) return 0;
-    return (g->grid > 0 ? 1 : 0) + (g->tc_pairs > 0 ? 1 : 0) + (g->mma[0].grid > 0 ? 1 : 0) + (g->mma[1].grid > 0 ? 1 : 0) +
-           static_cast<int>(g->singles.size());
+    int n = (g->grid > 0 ? 1 : 0) + (g->tc_pairs > 0 ? 1 : 0) + static_cast<int>(g->singles.size());
+    for (const auto& mt : g->mma) n += mt.grid > 0 ? 1 : 0;
+    for (const auto& t : g->sk) n += t.grid > 0 ? 1 : 0;
+    return n;
 }
 
 void ternix_b200_group_destroy(ternix_b200_group* g) {
@@ -1643,6 +1979,8 @@ void ternix_b200_group_destroy(ternix_b200_group* g) {
     if (g->d_tc_blob) cudaFree(g->d_tc_blob);
     for (auto& mt : g->mma)
         if (mt.d_blob) cudaFree(mt.d_blob);
+    for (auto& t : g->sk)
+        if (t.d_blob) cudaFree(t.d_blob);
     delete g;
 }
 
@@ -1655,7 +1993,7 @@ int ternix_b200_matmul_bcast(const int8_t* dA, const uint8_t* dW, int32_t* const
         if (!dC_list[d]) return TERNIX_B200_ERR_INVALID_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (K > 0 && dA && dW && gemm_tc2_ok(dA, dW, M, K, N))
-        return launch_gemm_tc2(dA, dW, dC_list, n_dest, M, K, N, ldc, d_status, st);
+        return launch_gemm_tc2(dA, dW, dC_list, n_dest, M, K, N, ldc, d_status, st, &g_last_launched);
     // Any other problem: compute into the first destination, then copy it to the others.
     const int rc = ternix_b200_matmul_ex(dA, dW, dC_list[0], M, K, N, ldc, TERNIX_B200_KERNEL_AUTO, d_status, stream);
     if (rc) return rc;
@@ -1702,9 +2040,14 @@ int ternix_b200_gemv_batch_noalloc(const ternix_b200_problem* problems, int coun
         if (q.M < 0 || q.K < 0 || q.N < 0 || (q.N % 4) != 0) return TERNIX_B200_ERR_INVALID_SHAPE;
         if (q.ldc < q.N) return TERNIX_B200_ERR_INVALID_ARG;
         if (q.M == 0 || q.N == 0) continue;
-        if (!q.dC || !q.dA || !q.dW) return TERNIX_B200_ERR_INVALID_ARG;
-        if (!group_gemv_ok(q)) return TERNIX_B200_ERR_UNSUPPORTED;     // decode-regime problems only
+        if (!q.dC || (q.K > 0 && (!q.dA || !q.dW))) return TERNIX_B200_ERR_INVALID_ARG;
+        if (q.K > 0 && !group_gemv_ok(q)) return TERNIX_B200_ERR_UNSUPPORTED;     // decode-regime problems only
     }
+    // The tables are staged in one fixed host buffer and uploaded with asynchronous copies.  A captured call would
+    // record copies that read that buffer when the graph runs, after later calls have rewritten it: refuse.
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    TB_CUDA(cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &capturing));
+    if (capturing != cudaStreamCaptureStatusNone) return TERNIX_B200_ERR_UNSUPPORTED;
     std::lock_guard<std::mutex> lock(g_noalloc_mutex);     // one caller at a time builds, copies and launches
     unsigned char* d_scratch = nullptr;
     int rc = noalloc_scratch_for_current_device(&d_scratch);
@@ -1715,6 +2058,11 @@ int ternix_b200_gemv_batch_noalloc(const ternix_b200_problem* problems, int coun
     for (int i = 0; i < count; ++i) {
         const ternix_b200_problem& q = problems[i];
         if (q.M == 0 || q.N == 0) continue;
+        if (q.K == 0) {        // empty sum: C = 0, as the single-product entry points do (a memset allocates nothing)
+            TB_CUDA(cudaMemset2DAsync(q.dC, static_cast<size_t>(q.ldc) * 4, 0, static_cast<size_t>(q.N) * 4, q.M,
+                                      static_cast<cudaStream_t>(stream)));
+            continue;
+        }
         tb200::GroupProblem& gp = h.probs[n_probs];
         gp = tb200::GroupProblem{};
         rc = make_tmap_2d(&gp.tmap_w, q.dW, static_cast<uint64_t>(q.N / 4), static_cast<uint64_t>(q.K),
@@ -1783,6 +2131,108 @@ int ternix_b200_gemv_batch_noalloc_limits(int* max_problems, int* max_items, lon
     if (max_problems) *max_problems = kNoAllocMaxProblems;
     if (max_items) *max_items = kNoAllocMaxItems;
     if (scratch_bytes) *scratch_bytes = static_cast<long long>(kNoAllocBytes);
+    return TERNIX_B200_OK;
+}
+
+int ternix_b200_weights_create(ternix_b200_weights** out, const uint8_t* dW, int K, int N) {
+    if (!out) return TERNIX_B200_ERR_INVALID_ARG;
+    *out = nullptr;
+    if (K < 0 || N < 0 || (N % 4) != 0) return TERNIX_B200_ERR_INVALID_SHAPE;
+    if (K > 0 && N > 0 && !dW) return TERNIX_B200_ERR_INVALID_ARG;
+    ternix_b200_weights* w = new (std::nothrow) ternix_b200_weights();
+    if (!w) return TERNIX_B200_ERR_INVALID_ARG;
+    w->dW = dW;
+    w->K = K;
+    w->N = N;
+    w->device = current_device();
+    w->fast = K >= 16 && N >= 64 && (N % 64) == 0 && (K % 16) == 0 && K <= kMaxScaledK && aligned(dW, 16);
+    if (w->fast) {
+        int rc = make_tmap_2d(&w->tmap_w_skinny, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K),
+                              static_cast<uint64_t>(N / 4), tb200::kSkWpRowBytes, tb200::kSkBK, CU_TENSOR_MAP_SWIZZLE_64B);
+        if (!rc) rc = make_tc3_weight_map(&w->tmap_w_tc3, dW, K, N);
+        if (rc) { delete w; return rc; }
+    }
+    *out = w;
+    return TERNIX_B200_OK;
+}
+
+void ternix_b200_weights_destroy(ternix_b200_weights* w) { delete w; }
+
+int ternix_b200_weights_matmul(ternix_b200_weights* w, const int8_t* dA, int32_t* dC, int M, long long ldc,
+                               int32_t* d_status, void* stream) {
+    if (!w) return TERNIX_B200_ERR_INVALID_ARG;
+    if (M < 0) return TERNIX_B200_ERR_INVALID_SHAPE;
+    if (ldc < w->N) return TERNIX_B200_ERR_INVALID_ARG;
+    if (M == 0 || w->N == 0) return TERNIX_B200_OK;
+    const int K = w->K, N = w->N;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int kernel = (w->fast && dA && dC) ? select_kernel(dA, w->dW, M, K, N) : TERNIX_B200_KERNEL_AUTO;
+    if (kernel == TERNIX_B200_KERNEL_SKINNY_TC) {
+        tb200::SkProblem prob{};
+        {
+            std::lock_guard<std::mutex> lock(w->mu);
+            if (w->a_ptr[0] != dA || w->a_rows[0] != M) {
+                const int rc = make_tmap_2d(&w->tmap_a[0], dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
+                                            static_cast<uint64_t>(K), 128, skinny_rows_class(M), CU_TENSOR_MAP_SWIZZLE_128B);
+                if (rc) return rc;
+                w->a_ptr[0] = dA;
+                w->a_rows[0] = M;
+            }
+            prob.tmap_a = w->tmap_a[0];
+        }
+        prob.tmap_w = w->tmap_w_skinny;
+        prob.C = dC; prob.ldc = ldc; prob.M = M; prob.K = K; prob.N = N;
+        g_last_launched = TERNIX_B200_LAUNCHED_SKINNY_TC;
+        return launch_skinny_problem(prob, d_status, st);
+    }
+    if (kernel == TERNIX_B200_KERNEL_GEMM_TC && options().tc3 && options().tc_bn == 0 && M > 64 && N >= 256 && (ldc % 4) == 0 &&
+        aligned(dC, 16)) {
+        CUtensorMap tmap_a;
+        tb200::Tc3Stores stores{};
+        {
+            std::lock_guard<std::mutex> lock(w->mu);
+            if (w->a_ptr[1] != dA || w->a_rows[1] != M) {
+                const int rc = make_tc3_act_map(&w->tmap_a[1], dA, M, K);
+                if (rc) return rc;
+                w->a_ptr[1] = dA;
+                w->a_rows[1] = M;
+            }
+            if (w->c_ptr != dC || w->c_rows != M || w->c_ld != ldc) {
+                const int rc = make_tc3_store_map(&w->tmap_c, dC, M, N, ldc);
+                if (rc) return rc;
+                w->c_ptr = dC;
+                w->c_rows = M;
+                w->c_ld = ldc;
+            }
+            tmap_a = w->tmap_a[1];
+            stores.tmap_c[0] = w->tmap_c;
+        }
+        stores.count = 1;
+        g_last_launched = TERNIX_B200_LAUNCHED_GEMM_TC3;
+        return launch_gemm_tc3_maps(tmap_a, w->tmap_w_tc3, stores, dC, M, K, N, ldc, d_status, st);
+    }
+    return ternix_b200_matmul_ex(dA, w->dW, dC, M, K, N, ldc, TERNIX_B200_KERNEL_AUTO, d_status, stream);
+}
+
+int ternix_b200_selftest_wait_timeout(unsigned long long limit_ns, int32_t* d_status, unsigned long long* d_waited_ns,
+                                      void* stream) {
+    if (limit_ns == 0 || limit_ns > 100000000ull) return TERNIX_B200_ERR_INVALID_ARG;      // at most 100 ms
+    wait_timeout_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns, d_status, d_waited_ns);
+    TB_CUDA(cudaGetLastError());
+    return TERNIX_B200_OK;
+}
+
+int ternix_b200_pack_ternary_device(uint8_t* d_packed, const int8_t* d_unpacked, size_t size, void* stream) {
+    const size_t n_bytes = size / 4;
+    if (n_bytes == 0) return TERNIX_B200_OK;
+    if (!d_packed || !d_unpacked) return TERNIX_B200_ERR_INVALID_ARG;
+    const size_t threads_wanted = (n_bytes + 3) / 4;
+    size_t blocks = (threads_wanted + 255) / 256;
+    const size_t cap = static_cast<size_t>(sm_count()) * 16;
+    if (blocks > cap) blocks = cap;
+    pack_ternary_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(d_unpacked, d_packed,
+                                                                                                     n_bytes);
+    TB_CUDA(cudaGetLastError());
     return TERNIX_B200_OK;
 }
 

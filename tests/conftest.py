@@ -26,3 +26,18 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture
+def option():
+    """Sets tuning options of the library for one test (ternix_b200_set_option) and restores the defaults after it."""
+    import ternixengine_b200 as tb
+    touched = []
+
+    def set_option(name, value):
+        tb.set_option(name, value)
+        touched.append(name)
+
+    yield set_option
+    for name in touched:
+        tb.set_option(name, None)

@@ -1,0 +1,226 @@
+"""The tensor-memory decode kernel (1..64 rows), the weight handle, the device-side packer, the bounded-wait
+self-test, a second GPU in one process and the C++ boundary harness.  Needs a B200."""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+import oracle_lib
+import ternixengine_b200 as tb
+from test_gpu_parity import BITNET_LAYER, assert_same, device_matmul, synth
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("split", ["1", "0"])
+def test_skinny_tc_rows_shapes_and_edges(option, split):
+    """Every batch class and its edges (1, 16, 17, 32, 33, 64 rows), K that is not a multiple of the 128-row stage,
+    column counts that leave the second 128-column block of an item empty or ragged, a padded C, single-stage and
+    deep problems; with blocks shared between CTAs (partial sums handed on through C) and with whole blocks only."""
+    option("skinny_split", split)
+    for (m, k, n, pad) in [(1, 64, 64, 0), (1, 2560, 6912, 0), (2, 2560, 640, 0), (3, 1040, 320, 1), (7, 4112, 1088, 0),
+                           (15, 16, 64, 3), (16, 6912, 2560, 0), (17, 272, 576, 0), (32, 4096, 11008, 0),
+                           (33, 8192, 128, 4), (48, 1024, 2112, 0), (64, 2560, 6912, 0), (64, 144, 704, 8),
+                           (5, 65536, 256, 0)]:
+        a, wp = synth(m, k, n, 90 + m + k)
+        assert_same(device_matmul(a, wp, "skinny_tc", pad_cols=pad), oracle_lib.matmul(a, wp),
+                    f"skinny_tc split={split} {m}x{k}x{n} pad {pad}")
+    for m in (1, 16, 64):                                  # largest magnitudes: 64 * 128 * K stays inside int32
+        k, n = 8192, 512
+        a = np.full((m, k), -128, dtype=np.int8)
+        wp = np.full((k, n // 4), 0xFF, dtype=np.uint8)
+        assert (device_matmul(a, wp, "skinny_tc") == 128 * k).all()
+    with pytest.raises(ValueError):                        # 65 rows are the prefill kernels' business
+        a, wp = synth(65, 256, 256, 1)
+        device_matmul(a, wp, "skinny_tc")
+
+
+@pytest.mark.parametrize("shape,launches", [((32, 4096, 11008), 200), ((16, 8192, 28672), 40), ((1, 2560, 6912), 200),
+                                            ((64, 1024, 1536), 200)])
+def test_skinny_tc_repeated_launches(shape, launches):
+    """Races in the rings or in the hand-over of partial sums between CTAs would show as rare, launch-dependent
+    errors: every one of many back-to-back launches (flags are reused with a new epoch each time) equals the oracle."""
+    import torch
+    m, k, n = shape
+    a, wp = synth(m, k, n, 3 * m + n)
+    expect = torch.from_numpy(oracle_lib.matmul(a, wp)).cuda()
+    da, dw = torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    outs = [torch.empty((m, n), dtype=torch.int32, device="cuda") for _ in range(2)]
+    bad = 0
+    for i in range(launches):
+        c = outs[i & 1]
+        c.fill_(-1)
+        tb.matmul(da, dw, out=c, kernel="skinny_tc", status=status)
+        bad += int(bool((c != expect).any()))
+    assert int(status.item()) == 0
+    assert bad == 0, f"{bad} of {launches} launches differ from the oracle"
+    assert tb.last_launched_kernel() == "ternary_skinny_tc_kernel"
+
+
+def test_skinny_tc_two_streams_use_two_flag_slots():
+    """Launches on different streams may overlap, so each stream has its own flags: interleaved launches of two
+    different problems on two streams all equal the oracle."""
+    import torch
+    jobs = []
+    for i, (m, k, n) in enumerate([(32, 4096, 11008), (8, 4096, 4096)]):
+        a, wp = synth(m, k, n, 700 + i)
+        jobs.append((torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda(),
+                     torch.from_numpy(oracle_lib.matmul(a, wp)).cuda(), torch.cuda.Stream()))
+    torch.cuda.synchronize()
+    outs = [[torch.full_like(j[2], -1) for _ in range(20)] for j in jobs]
+    for r in range(20):
+        for (da, dw, _, s), o in zip(jobs, outs):
+            tb.matmul(da, dw, out=o[r], kernel="skinny_tc", stream=s)
+    torch.cuda.synchronize()
+    for (_, _, expect, _), o in zip(jobs, outs):
+        assert all(bool((x == expect).all()) for x in o)
+
+
+@pytest.mark.parametrize("M", [2, 8, 16, 24, 64])
+@pytest.mark.parametrize("skinny_from", ["default", "2", "0"])
+def test_projection_group_batched_decode(option, M, skinny_from):
+    """config 5 at a few rows: one BitNet-shaped layer plus odd members in one group.  Members with several rows run
+    on the tensor-memory decode kernel from 17 rows up (default), from 2 rows up, or never (then the mma.sync kernel
+    takes them all)."""
+    import torch
+    if skinny_from != "default":
+        option("skinny_group_rows", skinny_from)
+    lo = {"default": 17, "2": 2, "0": 65}[skinny_from]
+    shapes = [(M, k, n) for (_, k, n) in BITNET_LAYER] + [(3, 1040, 320), (40, 144, 64), (1, 2560, 640)]
+    probs, expect = [], []
+    for i, (m, k, n) in enumerate(shapes):
+        a, wp = synth(m, k, n, 31 * M + i)
+        expect.append(oracle_lib.matmul(a, wp))
+        wide = torch.full((m, n + 8), -999, dtype=torch.int32, device="cuda")
+        probs.append((torch.from_numpy(a).cuda(), torch.from_numpy(wp).cuda(), wide[:, :n]))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    group = tb.ProjectionGroup(probs)
+    rows = [m for (m, _, _) in shapes]
+    skinny_classes = {16 if m <= 16 else 32 if m <= 32 else 64 for m in rows if lo <= m <= 64}
+    mma_sizes = {8 if m <= 8 else 16 for m in rows if 2 <= m < lo}
+    assert group.launches == 1 + len(skinny_classes) + len(mma_sizes)
+    for _ in range(3):
+        for p in probs:
+            p[2].fill_(-1)
+        group.run(status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for (a, w, out), e in zip(probs, expect):
+        assert_same(out.cpu().numpy(), e, f"group member {tuple(a.shape)}")
+    group.close()
+
+
+def test_weight_handle_matches_and_caches():
+    """ternix_b200_weights_*: same results as the plain entry point in every regime, across changing activations,
+    outputs and row counts (the handle's one-entry descriptor caches must notice each change)."""
+    import torch
+    for (k, n) in [(4096, 11008), (2560, 640), (129, 4)]:
+        wp = tb.synth_packed_weights(k, n, 5 + k)
+        dw = torch.from_numpy(wp).cuda()
+        handle = tb.TernaryWeights(dw)
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        for rep, m in enumerate([32, 32, 1, 300, 300, 7, 64, 64, 48, 65]):
+            a = tb.synth_activations((m, k), 1000 + rep)
+            da = torch.from_numpy(a).cuda()
+            out = torch.full((m, n + 4), -5, dtype=torch.int32, device="cuda")
+            for _ in range(2):                               # the second call reuses every cached descriptor
+                handle.matmul(da, out=out[:, :n], status=status)
+            torch.cuda.synchronize()
+            assert_same(out[:, :n].cpu().numpy(), oracle_lib.matmul(a, wp), f"weight handle {m}x{k}x{n}")
+            assert bool((out[:, n:] == -5).all())
+        assert int(status.item()) == 0
+        handle.close()
+
+
+def test_pack_ternary_on_the_device():
+    """ternix_b200_pack_ternary_device writes the bytes of the host packer (and of the oracle's), for aligned and
+    unaligned buffers and for sizes that are not multiples of 16."""
+    import torch
+    for (k, n) in [(2560, 6912), (33, 24), (1, 4), (129, 4), (7, 52)]:
+        w = tb.synth_weights(k, n, 77 + k)
+        expect = tb.pack_ternary(w)
+        assert np.array_equal(expect, oracle_lib.pack(w))
+        dw = torch.from_numpy(w).cuda()
+        assert np.array_equal(tb.pack_ternary_device(dw).cpu().numpy(), expect), (k, n)
+    # unaligned source and destination: the byte path
+    w = tb.synth_weights(64, 64, 3)
+    flat = torch.zeros(w.size + 1, dtype=torch.int8, device="cuda")
+    flat[1:] = torch.from_numpy(w.reshape(-1)).cuda()
+    out = torch.full((w.size // 4 + 3,), 0xEE, dtype=torch.uint8, device="cuda")
+    rc = tb.lib.ternix_b200_pack_ternary_device(out.data_ptr() + 1, flat.data_ptr() + 1, w.size,
+                                                torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert rc == 0
+    got = out.cpu().numpy()
+    assert np.array_equal(got[1:1 + w.size // 4], tb.pack_ternary(w).reshape(-1))
+    assert got[0] == 0xEE and (got[1 + w.size // 4:] == 0xEE).all()
+
+
+def test_bounded_wait_runs_out_and_the_context_survives():
+    """A wait that nobody answers ends after its limit: the CTA takes the abort and drain path of the product kernels,
+    reports TERNIX_B200_ERR_TIMEOUT in the status word and returns; the next launches work as usual."""
+    import torch
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    waited = torch.zeros(1, dtype=torch.int64, device="cuda")
+    limit_ns = 1_000_000
+    rc = tb.lib.ternix_b200_selftest_wait_timeout(limit_ns, status.data_ptr(), waited.data_ptr(),
+                                                  torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert int(status.item()) == tb.ERR_TIMEOUT
+    ns = int(waited.item())
+    assert limit_ns <= ns < 100 * limit_ns, f"waited {ns} ns for a {limit_ns} ns limit"
+    assert tb.lib.ternix_b200_selftest_wait_timeout(0, None, None, None) == tb.ERR_INVALID_ARG
+    assert tb.lib.ternix_b200_selftest_wait_timeout(10**9, None, None, None) == tb.ERR_INVALID_ARG
+    # the context is intact: a product right after it is exact and reports no timeout
+    a, wp = synth(32, 1024, 512, 4)
+    assert_same(device_matmul(a, wp, "auto"), oracle_lib.matmul(a, wp), "product after the timeout self-test")
+
+
+def test_second_gpu_in_the_same_process():
+    """Per-device state (shared-memory opt-ins, SM counts, flag and scratch addresses): every kernel family on
+    device 1 after device 0 in one process."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    shapes = [(1, 2560, 6912), (32, 4096, 1024), (300, 1040, 832), (7, 129, 4), (100, 1024, 128)]
+    for dev in (0, 1, 0):
+        with torch.cuda.device(dev):
+            for (m, k, n) in shapes:
+                a, wp = synth(m, k, n, 11 * m + n)
+                expect = oracle_lib.matmul(a, wp)
+                da, dw = torch.from_numpy(a).cuda(dev), torch.from_numpy(wp).cuda(dev)
+                for kern in ("auto", "gemv", "decode_mma", "skinny_tc", "gemm_tc"):
+                    if kern != "auto" and tb.lib.ternix_b200_select_kernel(da.data_ptr(), dw.data_ptr(), 0, m, k, n, n) < 0:
+                        continue
+                    try:
+                        c = tb.matmul(da, dw, kernel=kern)
+                    except ValueError:
+                        continue                               # that kernel does not take this shape
+                    torch.cuda.synchronize(dev)
+                    assert_same(c.cpu().numpy(), expect, f"device {dev} [{kern}] {m}x{k}x{n}")
+            # the allocation-free batch on this device
+            a, wp = synth(1, 2560, 640, 5)
+            da, dw = torch.from_numpy(a).cuda(dev), torch.from_numpy(wp).cuda(dev)
+            out = torch.full((1, 640), -1, dtype=torch.int32, device=f"cuda:{dev}")
+            prob = (tb._Problem * 1)(tb._Problem(da.data_ptr(), dw.data_ptr(), out.data_ptr(), 1, 2560, 640, 640))
+            rc = tb.lib.ternix_b200_gemv_batch_noalloc(prob, 1, None, torch.cuda.current_stream(dev).cuda_stream)
+            torch.cuda.synchronize(dev)
+            assert rc == 0
+            assert_same(out.cpu().numpy(), oracle_lib.matmul(a, wp), f"noalloc batch on device {dev}")
+
+
+def test_cpp_boundary_harness():
+    """tests/cpp/boundary_check.cpp: the ternix:: C++ functions with the reference tests' inputs (built by the csrc
+    Makefile, links libternix_b200.so)."""
+    exe = os.path.join(ROOT, "tests", "cpp", "_build", "boundary_check")
+    if not os.path.exists(exe):
+        subprocess.run(["make", "-C", os.path.join(ROOT, "ternixengine_b200", "csrc")], check=True, capture_output=True)
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    assert "boundary_check: PASS" in r.stdout

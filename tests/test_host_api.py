@@ -109,8 +109,19 @@ def test_kernel_selection_by_shape_and_alignment():
     assert sel(1, 2560, 6912) == tb.KERNEL_GEMV
     assert sel(16, 4096, 11008) == tb.KERNEL_DECODE_MMA
     assert sel(32, 4096, 11008) == tb.KERNEL_DECODE_MMA                 # config 2
-    assert sel(64, 4096, 11008) == tb.KERNEL_DECODE_MMA
+    assert sel(33, 4096, 11008) == tb.KERNEL_SKINNY_TC                  # three mma.sync passes or one tcgen05 pass
+    assert sel(64, 4096, 11008) == tb.KERNEL_SKINNY_TC
     assert sel(65, 4096, 11008) == tb.KERNEL_GEMM_TC
+    tb.set_option("skinny_rows", "2,64")                                # the row range of the tensor-memory decode kernel
+    try:
+        assert sel(32, 4096, 11008) == tb.KERNEL_SKINNY_TC
+        tb.set_option("skinny_rows", "0,0")
+        assert sel(64, 4096, 11008) == tb.KERNEL_DECODE_MMA
+        assert sel(65, 4096, 11008) == tb.KERNEL_GEMM_TC
+    finally:
+        tb.set_option("skinny_rows", None)
+    with pytest.raises(ValueError):
+        tb.set_option("no_such_option", "1")
     assert sel(4, 2560, 6912, a_ptr=8) == tb.KERNEL_GEMV                # small M, A not 16-byte aligned: no TMA view of A
     assert sel(4096, 8192, 28672) == tb.KERNEL_GEMM_TC
     for (m, k, n) in [(1, 3001, 1028), (7, 129, 4), (37, 4099, 2052), (255, 2561, 6916)]:
