@@ -490,10 +490,36 @@ def gathered_to_row_major(gathered: np.ndarray, N: int, granule: int = 64) -> np
     return out
 
 
-def should_shard(M: int, K: int, N: int, world: int, granule: int = 64) -> bool:
-    """Small projections stay on one GPU: a shard must keep at least one full 256-column tile per
-    rank and the problem must be in the tensor-core regime."""
-    return world > 1 and M > 16 and N // world >= 256 and N % granule == 0
+# Rates behind should_shard(), measured on B200: what one GPU sustains on the paired tensor-core GEMM, and what one
+# rank's epilogue stores sustain towards its peers over NVLink (per direction).
+_GEMM_OPS_PER_S = 3.0e15
+_PEER_STORE_BYTES_PER_S = 6.0e11
+_GATHER_FIXED_S = 30e-6            # the stream barrier after the stores, the tail of stores behind the last tile
+
+
+def should_shard(M: int, K: int, N: int, world: int, granule: int = 64, out_bytes: int = 4) -> bool:
+    """Whether N-column sharding of one projection over `world` GPUs beats computing it whole on one GPU when every
+    GPU needs the full C.  Sharding divides the compute by `world` but each rank must ship its columns to world - 1
+    peers and all ranks meet at a barrier: per step max(compute / world, out_bytes * M * N * (world - 1) / world /
+    link) + a fixed cost, against compute.  With int32 outputs that favours sharding only for large products with
+    deep K (K > ~10000 * (world - 1) / world): config 3 (K = 8192) gains at 2 and 4 GPUs, BitNet-2B projections
+    (K = 2560, 6912; microseconds each) never do.  Small or skinny problems stay whole:
+    a shard must keep at least one 256-column tile per rank and the problem must be in the tensor-core regime."""
+    if not (world > 1 and M > 64 and N // world >= 256 and N % granule == 0):
+        return False
+    compute = 2.0 * M * K * N / _GEMM_OPS_PER_S
+    gather = out_bytes * M * N * (world - 1) / world / _PEER_STORE_BYTES_PER_S
+    return max(compute / world, gather) + _GATHER_FIXED_S < compute
+
+
+def gather_buffer_index(step: int) -> int:
+    """Which of a rank's two gathered-C buffers step `step` fills.  Two buffers, because the barrier after a step
+    only says that every rank's stores have landed: a fast rank may start its next step, and store into its peers,
+    while a slow rank still reads the step before.  With alternating buffers those stores go to the buffer the slow
+    rank is not reading; the buffer of step i is written again only by step i + 2, which no rank can start before
+    every rank has passed the barrier of step i + 1, i.e. has enqueued its own step i + 1 behind its readers of
+    step i."""
+    return step & 1
 
 
 class _DeviceBuffer:
@@ -564,42 +590,68 @@ class ShardedTernaryLinear:
         self._gather = None
         self._block = None
         self._M = None
-        self._c_buf = None
+        self._c_bufs = None
         self._c = None
         self._peer_ptrs = None
         self._token = None
+        self._step = 0
 
     def local(self, a, out=None):
         """This rank's columns only: (M, n_cols) int32."""
         return matmul(a, self.w_local, out=out)
 
-    # ---- peer mode plumbing: one C buffer per rank, mapped by all ranks
-    def _setup_peer(self, M):
+    # ---- peer mode plumbing: two C buffers per rank (see gather_buffer_index), mapped by all ranks
+    def _map_peer_buffers(self, nbytes, n_buffers=2):
+        """Allocates n_buffers exportable buffers on this rank and maps every peer's: returns (own buffers,
+        ptrs[buffer][rank])."""
         import torch
         import torch.distributed as dist
 
         with torch.cuda.device(self.device):
-            self._c_buf = _DeviceBuffer(M * self.N * 4)
-            self._c = self._c_buf.as_tensor((M, self.N), torch.int32, self.device)
+            bufs = [_DeviceBuffer(nbytes) for _ in range(n_buffers)]
             handles = [None] * self.world
-            dist.all_gather_object(handles, self._c_buf.export(), group=self.group)
+            dist.all_gather_object(handles, [b.export() for b in bufs], group=self.group)
             ptrs = []
-            for r, h in enumerate(handles):
-                if r == self.rank:
-                    ptrs.append(self._c_buf.ptr)
-                else:
-                    p = ctypes.c_void_p()
-                    _check(lib.ternix_b200_peer_import(h, ctypes.byref(p)), "peer_import")
-                    ptrs.append(p.value)
+            for b in range(n_buffers):
+                row = []
+                for r, hs in enumerate(handles):
+                    if r == self.rank:
+                        row.append(bufs[b].ptr)
+                    else:
+                        p = ctypes.c_void_p()
+                        _check(lib.ternix_b200_peer_import(hs[b], ctypes.byref(p)), "peer_import")
+                        row.append(p.value)
+                ptrs.append(row)
+        return bufs, ptrs
+
+    def _setup_peer(self, M):
+        import torch
+
+        self._c_bufs, ptrs = self._map_peer_buffers(M * self.N * 4)
+        self._c = [b.as_tensor((M, self.N), torch.int32, self.device) for b in self._c_bufs]
         # own buffer first, then the peers, each offset to this rank's first column
         order = [self.rank] + [r for r in range(self.world) if r != self.rank]
-        self._peer_ptrs = (ctypes.c_void_p * self.world)(*[ptrs[r] + 4 * self.shard.n0 for r in order])
+        self._peer_ptrs = [(ctypes.c_void_p * self.world)(*[row[r] + 4 * self.shard.n0 for r in order]) for row in ptrs]
         self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._M = M
+        self._step = 0
 
-    def forward(self, a, out=None, status=None):
+    def stream_barrier(self):
+        """A barrier on the current stream: when it has passed, every rank's kernels enqueued before it have finished."""
         import torch
         import torch.distributed as dist
+
+        if self.world > 1:
+            if self._token is None:
+                self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+            dist.all_reduce(self._token, group=self.group)
+
+    def forward(self, a, out=None, status=None, barrier=True):
+        """Full row-major C[M, N] on every rank.  In peer mode the result is a view of one of two internal buffers
+        that alternate from call to call: it stays valid until the call after the next one, and whatever reads it
+        must be ordered on the calling stream before the next forward().  barrier=False leaves out the barrier
+        that makes the peers' columns complete (for timing the pieces)."""
+        import torch
 
         M = a.shape[0]
         if self.mode == "local":
@@ -609,57 +661,50 @@ class ShardedTernaryLinear:
         if self.mode == "peer":
             if self._M != M:
                 if self._M is not None:
-                    raise ValueError("peer mode keeps one C buffer: M must not change between calls")
+                    raise ValueError("peer mode keeps its C buffers: M must not change between calls")
                 self._setup_peer(M)
+            b = gather_buffer_index(self._step)
+            self._step += 1
             s = torch.cuda.current_stream(a.device)
             if self.shard.n_cols:
                 with torch.cuda.device(a.device):
-                    _check(lib.ternix_b200_matmul_bcast(a.data_ptr(), self.w_local.data_ptr(), self._peer_ptrs,
+                    _check(lib.ternix_b200_matmul_bcast(a.data_ptr(), self.w_local.data_ptr(), self._peer_ptrs[b],
                                                         self.world, M, self.K, self.shard.n_cols, self.N,
                                                         status.data_ptr() if status is not None else None,
                                                         s.cuda_stream), "matmul_bcast")
-            dist.all_reduce(self._token, group=self.group)      # barrier on the stream: every rank's stores are done
+            if barrier:
+                self.stream_barrier()      # every rank's stores of this step have landed
             if out is not None:
-                out.copy_(self._c)
+                out.copy_(self._c[b])
                 return out
-            return self._c
+            return self._c[b]
         return self._forward_nccl(a, out, status)
 
     def forward_dequant(self, a, row_scale, w_scale: float, status=None):
         """bfloat16 C = (A x W) * row_scale[:, None] * w_scale on every rank.  With more than one rank the GEMM
         epilogue of each rank scales, rounds and stores its columns into all ranks' bfloat16 C: half the NVLink
-        bytes of the int32 gather."""
+        bytes of the int32 gather.  The result alternates between two buffers like forward()'s."""
         import torch
-        import torch.distributed as dist
 
         M = a.shape[0]
         if self.world == 1:
             return matmul_dequant(a, self.w_local, row_scale, w_scale, status=status)
         if getattr(self, "_y_M", None) != M:
             if getattr(self, "_y_M", None) is not None:
-                raise ValueError("one bfloat16 C buffer is kept: M must not change between calls")
-            with torch.cuda.device(self.device):
-                self._y_buf = _DeviceBuffer(M * self.N * 2)
-                handles = [None] * self.world
-                dist.all_gather_object(handles, self._y_buf.export(), group=self.group)
-                ptrs = []
-                for r, h in enumerate(handles):
-                    if r == self.rank:
-                        ptrs.append(self._y_buf.ptr)
-                    else:
-                        p = ctypes.c_void_p()
-                        _check(lib.ternix_b200_peer_import(h, ctypes.byref(p)), "peer_import")
-                        ptrs.append(p.value)
-            self._y = self._y_buf.as_tensor((M, self.N), torch.bfloat16, self.device)
-            self._y_peers = tuple(ptrs[r] + 2 * self.shard.n0 for r in range(self.world) if r != self.rank)
-            if self._token is None:
-                self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+                raise ValueError("the bfloat16 C buffers are kept: M must not change between calls")
+            self._y_bufs, ptrs = self._map_peer_buffers(M * self.N * 2)
+            self._y = [b.as_tensor((M, self.N), torch.bfloat16, self.device) for b in self._y_bufs]
+            self._y_peers = [tuple(row[r] + 2 * self.shard.n0 for r in range(self.world) if r != self.rank) for row in ptrs]
             self._y_M = M
+            self._y_step = 0
+        b = gather_buffer_index(self._y_step)
+        self._y_step += 1
         if self.shard.n_cols:
-            matmul_dequant(a, self.w_local, row_scale, w_scale, out=self._y[:, self.shard.n0:self.shard.n0 + self.shard.n_cols],
-                           status=status, extra_dest_ptrs=self._y_peers)
-        dist.all_reduce(self._token, group=self.group)
-        return self._y
+            matmul_dequant(a, self.w_local, row_scale, w_scale,
+                           out=self._y[b][:, self.shard.n0:self.shard.n0 + self.shard.n_cols], status=status,
+                           extra_dest_ptrs=self._y_peers[b])
+        self.stream_barrier()
+        return self._y[b]
 
     def _forward_nccl(self, a, out, status):
         import torch
@@ -684,14 +729,16 @@ class ShardedTernaryLinear:
 
 
 class ShardedProjectionSet:
-    """Many projections at once (e.g. every linear layer of a model), each N-column-sharded over the ranks where
-    that pays off (should_shard) and kept whole otherwise.  One process per GPU.  All outputs of a rank live in one
-    buffer that every other rank maps; run() is one launch per regime on each rank (ternix_b200_group_run): the
-    paired-CTA GEMM writes every sharded projection's columns into all ranks' outputs from its epilogue, and a
-    4-byte all-reduce on the stream is the barrier.  Unsharded projections are computed by every rank for itself.
+    """Many projections at once (e.g. every linear layer of a model).  One process per GPU.  Each projection is
+    N-column-sharded over the ranks where that pays off (shard="auto": should_shard(); shard=True: wherever the shape
+    allows it; shard=False: never) and computed whole by every rank otherwise.  run() is one launch per regime on
+    each rank (ternix_b200_group_run): the paired-CTA GEMM writes every sharded projection's columns into all ranks'
+    outputs from its epilogue, and a 4-byte all-reduce on the stream is the barrier.  With sharded members the
+    outputs live in two buffers that alternate from run to run (gather_buffer_index): the tensors run() returns stay
+    valid until the run after the next one.
     """
 
-    def __init__(self, weights_host, activations, group=None, granule: int = 64, device=None):
+    def __init__(self, weights_host, activations, group=None, granule: int = 64, device=None, shard="auto"):
         """weights_host: list of packed (K, N/4) uint8 arrays; activations: list of (M, K) int8 CUDA tensors."""
         import torch
         import torch.distributed as dist
@@ -705,53 +752,70 @@ class ShardedProjectionSet:
         for w, a in zip(weights_host, activations):
             K, N = w.shape[0], w.shape[1] * 4
             M = a.shape[0]
-            sharded = should_shard(M, K, N, self.world, granule)
+            if shard == "auto":
+                sharded = should_shard(M, K, N, self.world, granule)
+            else:
+                sharded = bool(shard) and self.world > 1 and M > 16 and N // self.world >= 256 and N % granule == 0
             sh = shard_columns(N, self.world, self.rank, granule) if sharded else ColumnShard(N, 1, 0, granule, 0, N)
             plans.append((M, K, N, sharded, sh))
             offsets.append(total)
             total += M * N * 4
             total = (total + 255) & ~255
-        with torch.cuda.device(self.device):
-            self._buf = _DeviceBuffer(max(total, 256))
-            ptrs = [self._buf.ptr]
-            if self.world > 1:
-                handles = [None] * self.world
-                dist.all_gather_object(handles, self._buf.export(), group=self.group)
-                ptrs = []
-                for r, h in enumerate(handles):
-                    if r == self.rank:
-                        ptrs.append(self._buf.ptr)
-                    else:
-                        p = ctypes.c_void_p()
-                        _check(lib.ternix_b200_peer_import(h, ctypes.byref(p)), "peer_import")
-                        ptrs.append(p.value)
-        self.outputs, self._w_local, problems, peer_rows = [], [], [], []
-        others = [r for r in range(self.world) if r != self.rank]
-        for (M, K, N, sharded, sh), off, w, a in zip(plans, offsets, weights_host, activations):
-            view = _OffsetView(self._buf, off).as_tensor((M, N), torch.int32, self.device)
-            self.outputs.append(view)
-            local = slice_columns(w, sh.n0, sh.n_cols) if sharded else w
-            w_dev = torch.from_numpy(np.ascontiguousarray(local)).to(self.device)
-            self._w_local.append(w_dev)
-            if sh.n_cols == 0:
-                continue
-            problems.append((a, w_dev, view[:, sh.n0:sh.n0 + sh.n_cols]))
-            if self.world > 1:
-                # sharded: the same columns in every peer's buffer; unsharded: nobody else needs them, but the
-                # table wants equally many pointers per problem, so point the "peers" at this rank's own C
-                base = [ptrs[r] if sharded else self._buf.ptr for r in others]
-                peer_rows.append([b + off + 4 * sh.n0 for b in base])
         self.any_sharded = any(p[3] for p in plans)
-        self._group = ProjectionGroup(problems, peer_ptrs=peer_rows if (self.world > 1 and self.any_sharded) else None)
-        self.launches = self._group.launches
+        self.sharded_count = sum(1 for p in plans if p[3])
+        n_buffers = 2 if self.any_sharded else 1
+        with torch.cuda.device(self.device):
+            self._bufs = [_DeviceBuffer(max(total, 256)) for _ in range(n_buffers)]
+            ptrs = [[b.ptr] for b in self._bufs]
+            if self.world > 1 and self.any_sharded:
+                handles = [None] * self.world
+                dist.all_gather_object(handles, [b.export() for b in self._bufs], group=self.group)
+                ptrs = []
+                for bi in range(n_buffers):
+                    row = []
+                    for r, hs in enumerate(handles):
+                        if r == self.rank:
+                            row.append(self._bufs[bi].ptr)
+                        else:
+                            p = ctypes.c_void_p()
+                            _check(lib.ternix_b200_peer_import(hs[bi], ctypes.byref(p)), "peer_import")
+                            row.append(p.value)
+                    ptrs.append(row)
+        others = [r for r in range(self.world) if r != self.rank]
+        self._w_local = []
+        for (M, K, N, sharded, sh), w in zip(plans, weights_host):
+            local = slice_columns(w, sh.n0, sh.n_cols) if sharded else w
+            self._w_local.append(torch.from_numpy(np.ascontiguousarray(local)).to(self.device))
+        self._outputs, self._groups = [], []
+        for bi in range(n_buffers):
+            outputs, problems, peer_rows = [], [], []
+            for (M, K, N, sharded, sh), off, w_dev, a in zip(plans, offsets, self._w_local, activations):
+                view = _OffsetView(self._bufs[bi], off).as_tensor((M, N), torch.int32, self.device)
+                outputs.append(view)
+                if sh.n_cols == 0:
+                    continue
+                problems.append((a, w_dev, view[:, sh.n0:sh.n0 + sh.n_cols]))
+                if self.any_sharded:
+                    # sharded: the same columns in every peer's buffer; unsharded: nobody else needs them, but the
+                    # table wants equally many pointers per problem, so point the "peers" at this rank's own C
+                    base = [ptrs[bi][r] if sharded else self._bufs[bi].ptr for r in others]
+                    peer_rows.append([b + off + 4 * sh.n0 for b in base])
+            self._outputs.append(outputs)
+            self._groups.append(ProjectionGroup(problems, peer_ptrs=peer_rows if self.any_sharded else None))
+        self.outputs = self._outputs[0]
+        self.launches = self._groups[0].launches
         self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._step = 0
 
     def run(self, status=None):
         import torch.distributed as dist
 
-        self._group.run(status=status)
+        b = gather_buffer_index(self._step) if self.any_sharded else 0
+        self._step += 1
+        self._groups[b].run(status=status)
         if self.world > 1 and self.any_sharded:
             dist.all_reduce(self._token, group=self.group)
+        self.outputs = self._outputs[b]
         return self.outputs
 
 

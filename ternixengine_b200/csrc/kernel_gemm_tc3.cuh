@@ -402,11 +402,17 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     fence_proxy_async_smem();
                     asm volatile("bar.sync %0, 128;" ::"r"(2 + eg) : "memory");
                     if (elected) {
-                        for (int d = 0; d < dst->count; ++d)
+                        // destinations in an order that rotates with the pair and the step, so that the CTAs running
+                        // together do not all store to the same peer (the same NVLink path) at the same moment
+                        const int n_dst = dst->count;
+                        int d = n_dst > 1 ? static_cast<int>((pair + step) % static_cast<uint32_t>(n_dst)) : 0;
+                        for (int i = 0; i < n_dst; ++i) {
                             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
                                              reinterpret_cast<uint64_t>(&dst->tmap_c[d])),
                                          "r"(col0), "r"(row0), "r"(buf)
                                          : "memory");
+                            if (++d == n_dst) d = 0;
+                        }
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                 } else {

@@ -132,6 +132,16 @@ def test_kernel_selection_by_shape_and_alignment():
     assert sel(4, 8, 6) < 0                                             # N % 4 != 0
 
 
+def test_benchmark_numpy_generator_matches_the_library():
+    """bench.py's reference arm regenerates the inputs with numpy, without loading this library: same bytes."""
+    sys.path.insert(0, ROOT)
+    import bench
+    for seed, shape in [(20240531, (7, 1000)), (5, (3, 4097))]:
+        assert np.array_equal(bench.np_synth_activations(shape, seed), tb.synth_activations(shape, seed))
+    for seed, (k, n) in [(20240532, (33, 1028)), (9, (257, 64))]:
+        assert np.array_equal(bench.np_synth_packed_weights(k, n, seed), tb.synth_packed_weights(k, n, seed))
+
+
 def test_shape_errors_come_before_pointer_checks():
     # the reference promises cudaErrorInvalidValue with null pointers (tests/test_cuda_matmul.cu:41-43)
     assert tb.lib.ternix_b200_matmul(None, None, None, 4, 8, 6, None) == tb.ERR_INVALID_SHAPE

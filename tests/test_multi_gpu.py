@@ -54,18 +54,52 @@ def _rank_main(rank, world, port, out_dir):
                 dist.barrier()
                 assert int(status.item()) == 0
                 assert np.array_equal(c.cpu().numpy(), expect), f"rank {rank}: {mode} gather differs ({m},{k},{n})"
-        # a small projection set: two sharded members, one kept whole (N = 640), one decode-regime member
-        shapes = [(256, 2560, 2560), (256, 2560, 640), (256, 2560, 6912), (1, 2560, 2560)]
-        weights = [tb.synth_packed_weights(k, n, 70 + i) for i, (m, k, n) in enumerate(shapes)]
-        acts_h = [tb.synth_activations((m, k), 80 + i) for i, (m, k, n) in enumerate(shapes)]
-        pset = tb.ShardedProjectionSet(weights, [torch.from_numpy(x).to(dev) for x in acts_h], device=dev)
-        for _ in range(2):
-            outs = pset.run(status=status)
+        # activations that change every step, a reader that is late on one rank: the result of step i must not be
+        # overwritten by a peer that is already storing step i + 1 (two alternating C buffers)
+        m, k, n = 1024, 2048, 4096
+        wp = tb.synth_packed_weights(k, n, 5)
+        layer = tb.ShardedTernaryLinear(wp, device=dev, mode="peer")
+        steps = 6
+        acts = [tb.synth_activations((m, k), 200 + i) for i in range(steps)]
+        d_acts = [torch.from_numpy(x).to(dev) for x in acts]
+        busy = torch.randn((4096, 4096), device=dev)
+        kept = []
+        for i in range(steps):
+            c = layer.forward(d_acts[i], status=status)
+            if rank == 0:
+                for _ in range(8):
+                    busy = busy @ busy * 1e-3               # this rank's reader comes late, on the same stream
+            kept.append(c.clone())
         torch.cuda.synchronize()
         dist.barrier()
         assert int(status.item()) == 0
-        for i, out in enumerate(outs):
-            assert np.array_equal(out.cpu().numpy(), oracle_lib.matmul(acts_h[i], weights[i])), f"rank {rank}: member {i}"
+        for i in range(steps):
+            assert np.array_equal(kept[i].cpu().numpy(), oracle_lib.matmul(acts[i], wp)), f"rank {rank}: step {i} torn"
+        # a small projection set, sharding forced where the shape allows it: two sharded members, one kept whole
+        # (N = 640), one decode-regime member; then the automatic plan (BitNet-sized members stay whole)
+        shapes = [(256, 2560, 2560), (256, 2560, 640), (256, 2560, 6912), (1, 2560, 2560)]
+        weights = [tb.synth_packed_weights(k, n, 70 + i) for i, (m, k, n) in enumerate(shapes)]
+        for shard in (True, "auto"):
+            for rep in range(3):
+                acts_h = [tb.synth_activations((m, k), 80 + i + 10 * rep) for i, (m, k, n) in enumerate(shapes)]
+                d_in = [torch.from_numpy(x).to(dev) for x in acts_h]
+                if rep == 0:
+                    inputs = d_in
+                    pset = tb.ShardedProjectionSet(weights, inputs, device=dev, shard=shard)
+                    # forced: every member with more than 16 rows and at least 256 columns per rank; automatic: the
+                    # gather of a BitNet-sized projection costs more than the compute it saves, so none
+                    forced = sum(1 for (m, k, n) in shapes if m > 16 and n // world >= 256)
+                    assert pset.sharded_count == (forced if shard is True else 0)
+                else:
+                    for dst, src in zip(inputs, d_in):
+                        dst.copy_(src)                       # same buffers, new activations
+                outs = pset.run(status=status)
+                torch.cuda.synchronize()
+                dist.barrier()
+                assert int(status.item()) == 0
+                for i, out in enumerate(outs):
+                    assert np.array_equal(out.cpu().numpy(), oracle_lib.matmul(acts_h[i], weights[i])), \
+                        f"rank {rank}: member {i} (shard={shard}, rep {rep})"
         open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
     finally:
         dist.destroy_process_group()
