@@ -68,13 +68,33 @@ constexpr int kTc3ExpandWarps = TB200_TC3_EXPAND_WARPS;      // 4, 8 or 12: one,
 constexpr int kTc3WarpsPerQuarter = kTc3ExpandWarps / 4;     // they take the stages in turn (stage it -> warp it % n)
 static_assert(TB200_TC3_STAGES % (TB200_TC3_EXPAND_WARPS / 4) == 0,
               "a warp must meet every phase of the barriers it waits on: stages a multiple of warps per quarter");
-constexpr int kTc3FirstExpandWarp = 2;
-constexpr int kTc3FirstEpilogueWarp = kTc3FirstExpandWarp + kTc3ExpandWarps;    // 18
+// Roles sit in whole warpgroups (4 warps) because registers are moved between them at kernel start: warps 0-3
+// control (TMA producer, MMA issuer, two idle), then the expanders, then the epilogue.
+constexpr int kTc3FirstExpandWarp = 4;
+constexpr int kTc3FirstEpilogueWarp = kTc3FirstExpandWarp + kTc3ExpandWarps;    // 12
 #ifndef TB200_TC3_EPI_GROUPS
 #define TB200_TC3_EPI_GROUPS 2
 #endif
 constexpr int kTc3EpiGroups = TB200_TC3_EPI_GROUPS;                              // groups of 4 epilogue warps (one per lane quarter)
-constexpr int kTc3Threads = (kTc3FirstEpilogueWarp + 4 * kTc3EpiGroups) * 32;
+constexpr int kTc3Threads = (kTc3FirstEpilogueWarp + 4 * kTc3EpiGroups) * 32;     // 640
+constexpr int kTc3StepsPerWarp = kTc3TileA / 32 / kTc3EpiGroups;                   // accumulator steps of 32 rows per epilogue warp
+// Registers per thread after the hand-over at kernel start (setmaxnreg): an epilogue warp holds its whole share of
+// the accumulator (kTc3StepsPerWarp x 32 registers) so that tensor memory is free again a few hundred cycles after
+// the last MMA of a tile, long before the stores have drained.  The kernel is launched with 96 registers per thread
+// (640 x 96 = 61,440), and 128 x 48 + 256 x 64 + 256 x 152 = 61,440 is exactly that.
+constexpr int kTc3RegsControl = 48, kTc3RegsExpand = 64, kTc3RegsEpilogue = 152;
+static_assert(kTc3EpiGroups == 2 && kTc3ExpandWarps == 8, "the register budget above is worked out for this role layout");
+static_assert(128 * kTc3RegsControl + kTc3ExpandWarps * 32 * kTc3RegsExpand + kTc3EpiGroups * 128 * kTc3RegsEpilogue <=
+                  kTc3Threads * 96,
+              "register hand-over exceeds what the CTA owns at launch");
+template <int kRegs>
+__device__ __forceinline__ void warpgroup_regs_release() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void warpgroup_regs_acquire() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
 #ifndef TB200_TC3_EPI_BUFS
 #define TB200_TC3_EPI_BUFS 2
 #endif
@@ -242,7 +262,10 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0) {
+    // Each role branch opens with its register hand-over, so that the compiler sees the budget of the code behind it.
+    if (warp < kTc3FirstExpandWarp) {
+      warpgroup_regs_release<kTc3RegsControl>();
+      if (warp == 0) {
         // ================================================================ TMA producer
         if (lane == 0) {
             if constexpr (!kGrouped) {
@@ -270,7 +293,7 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 for (uint32_t j = first; j < it; ++j) mbar_drain(&full[j % kTc3Stages], (j / kTc3Stages) & 1);
             }
         }
-    } else if (warp == 1) {
+      } else if (warp == 1) {
         // ================================================================ MMA issuer (leader CTA only)
         if (leader && lane == 0) {
             uint32_t it = 0, lt = 0;
@@ -297,7 +320,9 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             tc_commit_pair(drain);
             mbar_wait(drain, 0, abort_flag);
         }
+      }     // warps 2, 3 have nothing to do: they only fill the control warpgroup
     } else if (warp < kTc3FirstEpilogueWarp) {
+        warpgroup_regs_release<kTc3RegsExpand>();
         // ================================================================ expanders: packed bytes -> int8 rows of the A operand
         // Lane L of the A operand is weight column L of the CTA's 128: byte column L / 4, field L % 4.  The warp of
         // lane quarter q therefore needs byte columns 8q .. 8q+7 (half of the 16-byte chunk q / 2 of a row) in all
@@ -350,6 +375,7 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             }
         }
     } else {
+        warpgroup_regs_acquire<kTc3RegsEpilogue>();
         // ================================================================ epilogue: 128 weight columns x 256 activation rows
         // Lane = weight column, registers = activation rows.  A step moves 32 activation rows x 128 columns from
         // tensor memory into a staging buffer in shared memory, row-major as in C (a warp writes 128 contiguous bytes
@@ -372,32 +398,42 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             if (!mbar_wait_backoff(acc_full, lt & 1, abort_flag, 256)) { ok = false; break; }
             tc_fence_after_sync();
             const int col0 = w.w_t * kTc3TileW + rank * 128;
-#pragma unroll 1
-            for (int c = eg; c < kTc3TileA / 32; c += kTc3EpiGroups, ++step) {
+            // this warp's share of the accumulator into registers, all of it, and tensor memory is free again
+            uint32_t r[kTc3StepsPerWarp][32];
+#pragma unroll
+            for (int i = 0; i < kTc3StepsPerWarp; ++i)
+                tmem_ld_32x32(tmem_base + ((q * 32) << 16) + 32 * (eg + kTc3EpiGroups * i), r[i]);
+            tmem_ld_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if (leader) mbar_arrive(acc_empty);
+                else mbar_arrive_remote(acc_empty, 0);
+            }
+#pragma unroll
+            for (int i = 0; i < kTc3StepsPerWarp; ++i, ++step) {
+                const int c = eg + kTc3EpiGroups * i;
                 const uint32_t buf = epi_sa + (eg * kTc3EpiBufs + step % kTc3EpiBufs) * kTc3EpiBytes;
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((q * 32) << 16) + 32 * c, r);
                 // the store that last read this buffer has finished reading
                 if (elected) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kTc3EpiBufs - 1) : "memory");
-                tmem_ld_wait();
                 asm volatile("bar.sync %0, 128;" ::"r"(2 + eg) : "memory");
                 const int row0 = a_t * kTc3TileA + 32 * c;
                 if constexpr (kBf16) {
-                    // in place: r[j] becomes the bfloat16 bit pattern of the scaled value
+                    // in place: r[i][j] becomes the bfloat16 bit pattern of the scaled value
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const float rs = row0 + j < M ? __ldg(row_scale + row0 + j) : 0.0f;
-                        const __nv_bfloat16 y = __float2bfloat16_rn((static_cast<float>(static_cast<int32_t>(r[j])) * rs) * w_scale);
-                        r[j] = static_cast<uint32_t>(__bfloat16_as_ushort(y));
+                        const __nv_bfloat16 y = __float2bfloat16_rn((static_cast<float>(static_cast<int32_t>(r[i][j])) * rs) * w_scale);
+                        r[i][j] = static_cast<uint32_t>(__bfloat16_as_ushort(y));
                     }
                 }
                 if (dst->count > 0) {
                     if constexpr (kBf16) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) sts_u16(buf + ((j * 128 + q * 32 + lane) << 1), static_cast<uint16_t>(r[j]));
+                        for (int j = 0; j < 32; ++j) sts_u16(buf + ((j * 128 + q * 32 + lane) << 1), static_cast<uint16_t>(r[i][j]));
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) sts_u32(buf + ((j * 128 + q * 32 + lane) << 2), r[j]);
+                        for (int j = 0; j < 32; ++j) sts_u32(buf + ((j * 128 + q * 32 + lane) << 2), r[i][j]);
                     }
                     fence_proxy_async_smem();
                     asm volatile("bar.sync %0, 128;" ::"r"(2 + eg) : "memory");
@@ -406,7 +442,7 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         // together do not all store to the same peer (the same NVLink path) at the same moment
                         const int n_dst = dst->count;
                         int d = n_dst > 1 ? static_cast<int>((pair + step) % static_cast<uint32_t>(n_dst)) : 0;
-                        for (int i = 0; i < n_dst; ++i) {
+                        for (int k = 0; k < n_dst; ++k) {
                             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
                                              reinterpret_cast<uint64_t>(&dst->tmap_c[d])),
                                          "r"(col0), "r"(row0), "r"(buf)
@@ -423,21 +459,15 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                             uint16_t* out = reinterpret_cast<uint16_t*>(C) + static_cast<size_t>(row0) * ldc + col;
 #pragma unroll
                             for (int j = 0; j < 32; ++j)
-                                if (row0 + j < M) out[static_cast<size_t>(j) * ldc] = static_cast<uint16_t>(r[j]);
+                                if (row0 + j < M) out[static_cast<size_t>(j) * ldc] = static_cast<uint16_t>(r[i][j]);
                         } else {
                             int32_t* out = C + static_cast<size_t>(row0) * ldc + col;
 #pragma unroll
                             for (int j = 0; j < 32; ++j)
-                                if (row0 + j < M) out[static_cast<size_t>(j) * ldc] = static_cast<int32_t>(r[j]);
+                                if (row0 + j < M) out[static_cast<size_t>(j) * ldc] = static_cast<int32_t>(r[i][j]);
                         }
                     }
                 }
-            }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                if (leader) mbar_arrive(acc_empty);
-                else mbar_arrive_remote(acc_empty, 0);
             }
         }
         if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // nothing in flight when the CTA leaves
