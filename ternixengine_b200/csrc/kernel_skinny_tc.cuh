@@ -6,7 +6,8 @@
 // the batch as the instruction's N (16, 32 or 64).  Nothing expanded is ever written to shared memory.
 //
 // Where it pays.  Measured on B200: a tcgen05.mma with M = 128 occupies the tensor unit for about 120 cycles whatever
-// its N (16, 32 and 64 rows take the same time; the instruction is sized for N = 256), so this kernel streams at most
+// its N (16, 32 and 64 rows take the same time, and alternating between independent accumulators changes nothing: it
+// is occupancy of the unit, sized for N = 256, not a dependency between MMAs), so this kernel streams at most
 // one kilobyte of packed weights per SM and ~120 cycles, about 2.4 TB/s over the GPU, independent of the row count.
 // The warp-level mma.sync kernel (kernel_decode_mma.cuh) streams 5.5 TB/s up to 8 rows and 3.8 TB/s up to 16, but
 // needs one pass per 16 rows; from 17 rows up this kernel is the faster one (210 BitNet-2B projections: 225 us
@@ -66,17 +67,10 @@ template <int NB>
 struct SkGeom {
     static_assert(NB == 16 || NB == 32 || NB == 64, "batch rows per instruction");
     static constexpr int kActBytes = NB * 128;                   // one box: NB rows x 128 K-bytes, 128-byte swizzle
-#ifndef TB200_SK_CHAINS
-#define TB200_SK_CHAINS 1
-#endif
-    // Independent accumulators per 128-column block: consecutive 32-deep MMAs alternate between them, so that an MMA
-    // does not have to wait for the one before it to have written the accumulator it adds to.
-    static constexpr int kChains = NB == 64 ? 1 : TB200_SK_CHAINS;
-    static constexpr int kAccCols = 4 * NB * kChains;            // [buffer][block][chain] x NB columns
-    static constexpr int kTStages = (512 - kAccCols) / 64 >= 6 ? 6 : 4;   // operand ring (tensor memory)
+    static constexpr int kTStages = NB == 64 ? 4 : 6;            // operand ring (tensor memory)
     static constexpr int kAStages = NB == 64 ? 8 : 16;           // activation ring (shared memory): deep, because every CTA
                                                                  // asks the L2 for the same few lines at the same time
-    static constexpr uint32_t kRingCol = kAccCols;               // after the accumulators
+    static constexpr uint32_t kRingCol = 4 * NB;                 // after the accumulators: [buffer][block] x NB columns
     static_assert(kRingCol + kTStages * kSkStageCols <= 512, "tensor memory budget");
     static constexpr size_t kSmemBytes = 1024 + size_t(kSkWStages) * kSkWpBytes + size_t(kAStages) * kActBytes + 768;
     // D = s32, A = B = s8, both K-major, N = NB, M = 128
@@ -355,10 +349,8 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
                 if (!mbar_wait(&acc_empty[ab], ((lt >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
                 const bool mine = hsel >= static_cast<uint32_t>(w.h0) && hsel < static_cast<uint32_t>(w.h1);
-                const uint32_t d = tmem_base + (ab * 2 + hsel) * (G::kChains * NB);
-                uint32_t acc[G::kChains];
-#pragma unroll
-                for (int ch = 0; ch < G::kChains; ++ch) acc[ch] = 0;
+                const uint32_t d = tmem_base + (ab * 2 + hsel) * NB;
+                uint32_t acc = 0;
                 for (int s = w.s0; s < w.s1; ++s) {
                     if (!mbar_wait(&ready[sl], ph_t, abort_flag) || !mbar_wait(&a_full[al], ph_a, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
@@ -367,9 +359,8 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
                         const uint32_t lo = desc_lo0 + al * (G::kActBytes >> 4);
 #pragma unroll
                         for (int g = 0; g < kSkBK / 32; ++g) {
-                            tc_mma_i8_tmem_a_lohi(d + (g % G::kChains) * NB, a_col + 8 * g, lo + 2 * g, desc_hi, G::kIdesc,
-                                                  acc[g % G::kChains]);
-                            acc[g % G::kChains] = 1;
+                            tc_mma_i8_tmem_a_lohi(d, a_col + 8 * g, lo + 2 * g, desc_hi, G::kIdesc, acc);
+                            acc = 1;
                         }
                     }
                     tc_commit(&t_free[sl]);
@@ -468,18 +459,7 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
 #pragma unroll
                 for (int c = 0; c < NB / 16; ++c) {
                     uint32_t r[16];
-                    const uint32_t acc0 = tmem_base + ((q * 32) << 16) + (ab * 2 + h) * (G::kChains * NB) + 16 * c;
-                    tmem_ld_32x32_x16(acc0, r);
-                    if constexpr (G::kChains > 1) {
-#pragma unroll
-                        for (int ch = 1; ch < G::kChains; ++ch) {
-                            uint32_t r2[16];
-                            tmem_ld_32x32_x16(acc0 + ch * NB, r2);
-                            tmem_ld_wait();
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) r[j] += r2[j];
-                        }
-                    }
+                    tmem_ld_32x32_x16(tmem_base + ((q * 32) << 16) + (ab * 2 + h) * NB + 16 * c, r);
                     tmem_ld_wait();
                     if (h == w.h1 - 1 && c == NB / 16 - 1) {      // everything has been read: the next segment may accumulate here
                         tc_fence_before_sync();
