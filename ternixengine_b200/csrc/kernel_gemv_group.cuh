@@ -135,6 +135,8 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int item_lo = cta_first[blockIdx.x], item_hi = cta_first[blockIdx.x + 1];
+    // a dependent launch (the next decode batch on the stream) may start filling SMs as this grid's CTAs retire
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (tid == 0) {
         for (int s = 0; s < kGroupStages; ++s) {
@@ -156,6 +158,18 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
         if (lane == 0) {
             uint32_t t = 0;
             bool ok = true;
+            auto load_tile = [&](const GroupProblem* p, const GroupItem& it, int tt) {
+                const uint32_t s = t % kGroupStages;
+                if (!mbar_wait(&empty[s], ((t / kGroupStages) & 1) ^ 1, abort_flag)) return false;
+                mbar_arrive_expect_tx(&full[s], kGroupStageBytes);
+                if constexpr (PRE)   // [K/4 rows][N/4 words]: 128 words x 16 rows = the same 64 k-rows x 512 columns
+                    tma_load_2d(stages + s * kGroupStageBytes, &p->tmap_w, it.chunk * WORDS * 4, tt * (kGroupStageRows / 4),
+                                &full[s]);
+                else
+                    tma_load_2d(stages + s * kGroupStageBytes, &p->tmap_w, it.chunk * WORDS * 4, tt * kGroupStageRows, &full[s]);
+                ++t;
+                return true;
+            };
             for (int i = item_lo; ok && i < item_hi; ++i) {
                 const GroupItem it = items[i];
                 const GroupProblem* p = probs + it.problem;
@@ -163,23 +177,23 @@ ternary_gemv_group_kernel(const GroupProblem* __restrict__ probs, const GroupIte
                 const uint32_t n = i - item_lo, buf = n & 1;
                 int rows = p->M - it.row0;
                 if (rows > MR) rows = MR;
+                const int ntiles = (K + kGroupStageRows - 1) / kGroupStageRows;
+                int tt = 0;
+                if (i == item_lo) {
+                    // Launched as a programmatic dependent of the kernel before it, this CTA may already be running
+                    // while that kernel's last CTAs finish.  Weights are never written by a kernel of this library, so
+                    // the first ring of weight tiles is requested right away; everything a predecessor may have
+                    // produced (the activations) and every store waits for its completion.
+                    for (; ok && tt < ntiles && tt < kGroupStages; ++tt) ok = load_tile(p, it, tt);
+                    asm volatile("griddepcontrol.wait;" ::: "memory");
+                    if (!ok) break;
+                }
                 if (!mbar_wait(&a_empty[buf], ((n >> 1) & 1) ^ 1, abort_flag)) break;
                 mbar_arrive_expect_tx(&a_full[buf], static_cast<uint32_t>(rows) * K);
                 for (int r = 0; r < rows; ++r)
                     bulk_copy_g2s(a_buf + (buf * MR + r) * kGroupMaxK, p->A + static_cast<size_t>(it.row0 + r) * K, K,
                                   &a_full[buf]);
-                const int ntiles = (K + kGroupStageRows - 1) / kGroupStageRows;
-                for (int tt = 0; tt < ntiles; ++tt, ++t) {
-                    const uint32_t s = t % kGroupStages;
-                    if (!mbar_wait(&empty[s], ((t / kGroupStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                    mbar_arrive_expect_tx(&full[s], kGroupStageBytes);
-                    if constexpr (PRE)   // [K/4 rows][N/4 words]: 128 words x 16 rows = the same 64 k-rows x 512 columns
-                        tma_load_2d(stages + s * kGroupStageBytes, &p->tmap_w, it.chunk * WORDS * 4, tt * (kGroupStageRows / 4),
-                                    &full[s]);
-                    else
-                        tma_load_2d(stages + s * kGroupStageBytes, &p->tmap_w, it.chunk * WORDS * 4, tt * kGroupStageRows,
-                                    &full[s]);
-                }
+                for (; ok && tt < ntiles; ++tt) ok = load_tile(p, it, tt);
             }
             if (*abort_flag) {
                 const uint32_t first = t > kGroupStages ? t - kGroupStages : 0;

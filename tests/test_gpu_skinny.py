@@ -115,6 +115,44 @@ def test_projection_group_batched_decode(option, M, skinny_from):
     group.close()
 
 
+@pytest.mark.parametrize("pdl", ["1", "0", "-1"])
+def test_decode_batches_back_to_back_as_programmatic_dependents(option, pdl):
+    """Decode batches launched back to back: with gemv_pdl the next grid starts while the previous one finishes and
+    prefetches weights early, but reads activations and writes C only after it.  Each run's activations are the previous
+    run's outputs (a chain), so an early read or a late write would change the bytes."""
+    import torch
+    option("gemv_pdl", pdl)
+    k = n = 2560
+    wps = [tb.synth_packed_weights(k, n, 40 + i) for i in range(3)]
+    dws = [torch.from_numpy(w).cuda() for w in wps]
+    a0 = tb.synth_activations((1, k), 9)
+    acts = [torch.from_numpy(a0).cuda()] + [torch.zeros((1, k), dtype=torch.int8, device="cuda") for _ in range(3)]
+    outs = [torch.zeros((1, n), dtype=torch.int32, device="cuda") for _ in range(3)]
+    groups = [tb.ProjectionGroup([(acts[i], dws[i], outs[i])]) for i in range(3)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    # layer i: out_i = act_i x W_i; act_{i+1} = low byte of out_i (a tiny torch kernel between the batches keeps the
+    # chain honest for the first pass; the second pass runs the three batches with nothing in between on fixed inputs)
+    expect, a = [], a0
+    for i in range(3):
+        c = oracle_lib.matmul(a, wps[i], "scalar")
+        expect.append(c)
+        a = c.astype(np.int8)
+    for i in range(3):
+        groups[i].run(status=status)
+        if i < 2:
+            acts[i + 1].copy_(outs[i].to(torch.int8))
+    torch.cuda.synchronize()
+    for i in range(3):
+        assert_same(outs[i].cpu().numpy(), expect[i], f"chained batch {i} (pdl={pdl})")
+    for rep in range(20):                      # back to back, same inputs: every run must reproduce the same bytes
+        for i in range(3):
+            groups[i].run(status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for i in range(3):
+        assert_same(outs[i].cpu().numpy(), expect[i], f"back-to-back batch {i} (pdl={pdl})")
+
+
 def test_weight_handle_matches_and_caches():
     """ternix_b200_weights_*: same results as the plain entry point in every regime, across changing activations,
     outputs and row counts (the handle's one-entry descriptor caches must notice each change)."""
