@@ -16,16 +16,18 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("split", ["1", "0"])
+@pytest.mark.parametrize("split", ["1", "2", "0"])
 def test_skinny_tc_rows_shapes_and_edges(option, split):
     """Every batch class and its edges (1, 16, 17, 32, 33, 64 rows), K that is not a multiple of the 128-row stage,
     column counts that leave the second 128-column block of an item empty or ragged, a padded C, single-stage and
-    deep problems; with blocks shared between CTAs (partial sums handed on through C) and with whole blocks only."""
+    deep problems; with the default plan (whole-K items unless blocks outnumber SMs), with blocks shared between CTAs
+    wherever that evens the load (2: partial sums handed on through C, chains of up to three CTAs) and with whole
+    blocks only (0)."""
     option("skinny_split", split)
     for (m, k, n, pad) in [(1, 64, 64, 0), (1, 2560, 6912, 0), (2, 2560, 640, 0), (3, 1040, 320, 1), (7, 4112, 1088, 0),
                            (15, 16, 64, 3), (16, 6912, 2560, 0), (17, 272, 576, 0), (32, 4096, 11008, 0),
                            (33, 8192, 128, 4), (48, 1024, 2112, 0), (64, 2560, 6912, 0), (64, 144, 704, 8),
-                           (5, 65536, 256, 0)]:
+                           (5, 65536, 256, 0), (40, 512, 40960, 0)]:        # the last one: more 256-column blocks than SMs
         a, wp = synth(m, k, n, 90 + m + k)
         assert_same(device_matmul(a, wp, "skinny_tc", pad_cols=pad), oracle_lib.matmul(a, wp),
                     f"skinny_tc split={split} {m}x{k}x{n} pad {pad}")
@@ -39,12 +41,14 @@ def test_skinny_tc_rows_shapes_and_edges(option, split):
         device_matmul(a, wp, "skinny_tc")
 
 
+@pytest.mark.parametrize("split", ["1", "2"])
 @pytest.mark.parametrize("shape,launches", [((32, 4096, 11008), 200), ((16, 8192, 28672), 40), ((1, 2560, 6912), 200),
                                             ((64, 1024, 1536), 200)])
-def test_skinny_tc_repeated_launches(shape, launches):
+def test_skinny_tc_repeated_launches(option, shape, launches, split):
     """Races in the rings or in the hand-over of partial sums between CTAs would show as rare, launch-dependent
     errors: every one of many back-to-back launches (flags are reused with a new epoch each time) equals the oracle."""
     import torch
+    option("skinny_split", split)
     m, k, n = shape
     a, wp = synth(m, k, n, 3 * m + n)
     expect = torch.from_numpy(oracle_lib.matmul(a, wp)).cuda()
@@ -66,6 +70,7 @@ def test_skinny_tc_two_streams_use_two_flag_slots():
     """Launches on different streams may overlap, so each stream has its own flags: interleaved launches of two
     different problems on two streams all equal the oracle."""
     import torch
+    tb.set_option("skinny_split", "2")          # shared blocks, so that the flags are in use
     jobs = []
     for i, (m, k, n) in enumerate([(32, 4096, 11008), (8, 4096, 4096)]):
         a, wp = synth(m, k, n, 700 + i)
@@ -77,6 +82,7 @@ def test_skinny_tc_two_streams_use_two_flag_slots():
         for (da, dw, _, s), o in zip(jobs, outs):
             tb.matmul(da, dw, out=o[r], kernel="skinny_tc", stream=s)
     torch.cuda.synchronize()
+    tb.set_option("skinny_split", None)
     for (_, _, expect, _), o in zip(jobs, outs):
         assert all(bool((x == expect).all()) for x in o)
 
