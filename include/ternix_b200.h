@@ -41,7 +41,7 @@ extern "C" {
 #define TERNIX_B200_KERNEL_GEMM_TC  3  /* prefill regime: TMA + tcgen05 kind::i8, int32 in TMEM       */
 #define TERNIX_B200_KERNEL_DECODE_MMA 4 /* batched decode (a few to a few dozen rows): TMA-streamed   */
                                        /* packed W decoded in registers into mma.sync.m16n8k32       */
-#define TERNIX_B200_KERNEL_SKINNY_TC 5 /* batched decode, 1..64 rows: TMA-streamed packed W decoded   */
+#define TERNIX_B200_KERNEL_SKINNY_TC 5 /* batched decode, 1..128 rows: TMA-streamed packed W decoded  */
                                        /* into tensor memory as the A operand of tcgen05 kind::i8     */
 
 /* ---- what a single-product call launched (ternix_b200_last_launched_kernel) ------------------- */
@@ -68,7 +68,7 @@ const char *ternix_b200_launched_kernel_name(int launched);
  * read once from the environment variable TERNIX_B200_<NAME> when the library is first used and can be changed
  * afterwards only here (value NULL or "" restores the default); do not change options while another thread
  * launches.  Names: tc3 (0|1), tc_bn (0|2|128|256), tc_ksplit (0|1), gemv_plan ("words,ksplit"), group_words
- * (16|32), gemv_pdl (-1|0|1), mma_rows ("lo,hi"), mma_slices, mma_cluster (0|2|4|8), skinny_rows ("lo,hi"), skinny_group_rows (lo, 0 = never), skinny_split (0|1|2),
+ * (16|32), gemv_pdl (-1|0|1), mma_rows ("lo,hi"), mma_slices, mma_cluster (0|2|4|8), skinny_rows ("lo,hi"), skinny_group_rows ("lo,hi", lo 0 = never), skinny_split (0|1|2),
  * host_slab (<columns>|r<rows>|0).  Unknown name: TERNIX_B200_ERR_INVALID_ARG. */
 int ternix_b200_set_option(const char *name, const char *value);
 /* The host-pointer entry point (and the unfused dequantising path) take device memory from a stream-ordered pool

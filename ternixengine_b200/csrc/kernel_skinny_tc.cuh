@@ -1,9 +1,9 @@
-// Batched-decode kernel on the tcgen05 tensor core: up to 64 rows of activations against a stream of packed weights.
+// Batched-decode kernel on the tcgen05 tensor core: up to 128 rows of activations against a stream of packed weights.
 //
 // As in the paired prefill kernel the product is computed transposed, C^T[n][m] = sum_k W[k][n] * A[m][k]: the
 // weights are the A operand of tcgen05.mma and live in TENSOR MEMORY (row = weight column = lane, four K-bytes per
 // 32-bit column), the activations are the B operand, straight from TMA in the K-major 128-byte-swizzle layout, with
-// the batch as the instruction's N (16, 32 or 64).  Nothing expanded is ever written to shared memory.
+// the batch as the instruction's N (16, 32, 64 or 128).  Nothing expanded is ever written to shared memory.
 //
 // Where it pays.  Measured on B200: a tcgen05.mma with M = 128 occupies the tensor unit for about 120 cycles whatever
 // its N (16, 32 and 64 rows take the same time, and alternating between independent accumulators changes nothing: it
@@ -11,7 +11,9 @@
 // one kilobyte of packed weights per SM and ~120 cycles, about 2.4 TB/s over the GPU, independent of the row count.
 // The warp-level mma.sync kernel (kernel_decode_mma.cuh) streams 5.5 TB/s up to 8 rows and 3.8 TB/s up to 16, but
 // needs one pass per 16 rows; from 17 rows up this kernel is the faster one (210 BitNet-2B projections: 225 us
-// against 288 us at 32 rows, 231 us against 538 us at 64 rows), and the dispatch uses it there.
+// against 288 us at 32 rows, 231 us against 538 us at 64 rows), and the dispatch uses it there.  Group members
+// with 65 to 128 rows run here as well (340 us at 128 rows; the paired prefill kernel pads them to 256-row tiles,
+// 416 us); a single product of that size is faster on the prefill kernel.
 //
 // From packed bytes to the operand in 17 instructions per 1024 weights and warp:
 //   * a stage is 128 k-rows x 64 packed bytes (256 weight columns), TMA with the 64-byte swizzle;
@@ -24,10 +26,11 @@
 //     0xC0, i.e. 0, +64, -64 as int8 (the two top bits of a byte ARE the sign-extended code).  The accumulators hold
 //     64 * sum; the final arithmetic shift by 6 is exact.  Bound 64 * 128 * K < 2^31, K <= 262143.
 //
-// Tensor memory (512 columns): two accumulator buffers x two 128-column blocks x NB columns, then a ring of operand
-// stages of 2 blocks x 32 columns each (6 stages for NB = 16 and 32, 4 for NB = 64).  Shared memory: a ring of 16
-// packed-weight stages (8 KB each: what is in flight from HBM) and a ring of 16 (8 for NB = 64) activation stages
-// (NB rows x 128 bytes).
+// Tensor memory (512 columns): two accumulator buffers (one for NB = 128) x two 128-column blocks x NB columns, then
+// a ring of operand stages of 2 blocks x 32 columns each (6 stages for NB = 16 and 32, 4 otherwise).  Shared memory:
+// a ring of 16 (8 for NB = 128) packed-weight stages (8 KB each: what is in flight from HBM) and a ring of 16 / 16 /
+// 8 / 6 activation stages (NB rows x 128 bytes).  Each 128-column block has its own accumulator barriers, so with a
+// single buffer the issuer of block 0 starts the next item while the epilogue still reads block 1.
 //
 // Roles (16 warps): 0 weight producer, 1 and 3 MMA issuers (one per 128-column block: a single thread's instruction
 // stream -- two waits, four instructions per MMA, a commit -- was what bounded the stage rate before it was split),
@@ -53,7 +56,6 @@
 
 namespace tb200 {
 
-constexpr int kSkWStages = 16;                    // packed-weight ring (shared memory)
 constexpr int kSkBK = 128;                        // k-rows per stage
 constexpr int kSkItemCols = 256;                  // weight columns per item: two MMA blocks of 128
 constexpr int kSkWpRowBytes = kSkItemCols / 4;    // 64
@@ -65,14 +67,16 @@ constexpr int kSkMaxCtas = 256;                   // flags per launch slot
 
 template <int NB>
 struct SkGeom {
-    static_assert(NB == 16 || NB == 32 || NB == 64, "batch rows per instruction");
+    static_assert(NB == 16 || NB == 32 || NB == 64 || NB == 128, "batch rows per instruction");
     static constexpr int kActBytes = NB * 128;                   // one box: NB rows x 128 K-bytes, 128-byte swizzle
-    static constexpr int kTStages = NB == 64 ? 4 : 6;            // operand ring (tensor memory)
-    static constexpr int kAStages = NB == 64 ? 8 : 16;           // activation ring (shared memory): deep, because every CTA
-                                                                 // asks the L2 for the same few lines at the same time
-    static constexpr uint32_t kRingCol = 4 * NB;                 // after the accumulators: [buffer][block] x NB columns
+    static constexpr int kAccBufs = NB == 128 ? 1 : 2;           // accumulator buffers per 128-column block
+    static constexpr int kTStages = NB <= 32 ? 6 : 4;            // operand ring (tensor memory)
+    static constexpr int kWStages = NB == 128 ? 8 : 16;          // packed-weight ring (shared memory): what is in flight from HBM
+    static constexpr int kAStages = NB == 128 ? 6 : NB == 64 ? 8 : 16;   // activation ring (shared memory)
+    static constexpr uint32_t kRingCol = 2 * kAccBufs * NB;      // after the accumulators: [buffer][block] x NB columns
     static_assert(kRingCol + kTStages * kSkStageCols <= 512, "tensor memory budget");
-    static constexpr size_t kSmemBytes = 1024 + size_t(kSkWStages) * kSkWpBytes + size_t(kAStages) * kActBytes + 768;
+    static constexpr size_t kSmemBytes = 1024 + size_t(kWStages) * kSkWpBytes + size_t(kAStages) * kActBytes + 768;
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
     // D = s32, A = B = s8, both K-major, N = NB, M = 128
     static constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(NB >> 3) << 17) | (uint32_t(128 >> 4) << 24);
 };
@@ -218,21 +222,21 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
                          const int* __restrict__ cta_first, int* __restrict__ flags, int epoch,
                          int32_t* __restrict__ status) {
     using G = SkGeom<NB>;
-    constexpr int TS = G::kTStages, AS = G::kAStages;
+    constexpr int TS = G::kTStages, AS = G::kAStages, WS = G::kWStages, BUFS = G::kAccBufs;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sW = base;                                              // [WStages][128 k][64]   64-byte swizzle
-    uint8_t* sAct = sW + kSkWStages * kSkWpBytes;                    // [AS][NB rows][128 k]   128-byte swizzle
+    uint8_t* sAct = sW + WS * kSkWpBytes;                    // [AS][NB rows][128 k]   128-byte swizzle
     uint64_t* bars = reinterpret_cast<uint64_t*>(sAct + AS * G::kActBytes);
     uint64_t* w_full = bars;                       // a packed-weight stage has landed
-    uint64_t* w_empty = w_full + kSkWStages;       // the four quarters have read it
-    uint64_t* a_full = w_empty + kSkWStages;       // an activation stage has landed
+    uint64_t* w_empty = w_full + WS;       // the four quarters have read it
+    uint64_t* a_full = w_empty + WS;       // an activation stage has landed
     uint64_t* a_empty = a_full + AS;               // the MMAs that read an activation stage have retired
     uint64_t* ready = a_empty + AS;                // the four quarters have written an operand stage
     uint64_t* t_free = ready + TS;                 // the MMAs that read an operand stage have retired
-    uint64_t* acc_full = t_free + TS;              // [2]
-    uint64_t* acc_empty = acc_full + 2;            // [2]
-    uint64_t* drain = acc_empty + 2;
+    uint64_t* acc_full = t_free + TS;              // [buffer][block]: that block's MMAs of a segment have retired
+    uint64_t* acc_empty = acc_full + 4;            // [buffer][block]: the epilogue has read that accumulator
+    uint64_t* drain = acc_empty + 4;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* epi_count = reinterpret_cast<int*>(tmem_slot + 2);    // epilogue warps done with the one partial tile a CTA writes
@@ -260,7 +264,7 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
         return w;
     };
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kSkWStages; ++s) {
+        for (int s = 0; s < WS; ++s) {
             mbar_init(&w_full[s], 1);
             mbar_init(&w_empty[s], 4);
         }
@@ -272,8 +276,8 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
             mbar_init(&ready[s], 4);
             mbar_init(&t_free[s], 2);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&acc_full[b], 2);
+        for (int b = 0; b < 4; ++b) {
+            mbar_init(&acc_full[b], 1);
             mbar_init(&acc_empty[b], 4);
         }
         mbar_init(drain, 2);
@@ -300,15 +304,15 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
             while (ok && w.next()) {
                 const int x = w.block * kSkWpRowBytes;
                 for (int s = w.s0; s < w.s1; ++s, ++it) {
-                    const uint32_t sl = it % kSkWStages;
-                    if (!mbar_wait_backoff(&w_empty[sl], ((it / kSkWStages) & 1) ^ 1, abort_flag, 32)) { ok = false; break; }
+                    const uint32_t sl = it % WS;
+                    if (!mbar_wait_backoff(&w_empty[sl], ((it / WS) & 1) ^ 1, abort_flag, 32)) { ok = false; break; }
                     mbar_arrive_expect_tx(&w_full[sl], kSkWpBytes);
                     tma_load_2d(sW + sl * kSkWpBytes, &w.p->tmap_w, x, s * kSkBK, &w_full[sl]);
                 }
             }
             if (!ok) {
-                const uint32_t first = it > kSkWStages ? it - kSkWStages : 0;
-                for (uint32_t j = first; j < it; ++j) mbar_drain(&w_full[j % kSkWStages], (j / kSkWStages) & 1);
+                const uint32_t first = it > WS ? it - WS : 0;
+                for (uint32_t j = first; j < it; ++j) mbar_drain(&w_full[j % WS], (j / WS) & 1);
             }
         }
     } else if (warp == 2) {
@@ -345,8 +349,10 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
             bool ok = true;
             SkWalk<kGrouped> w = make_walk();
             for (; ok && w.next(); ++lt) {
-                const uint32_t ab = lt & 1;
-                if (!mbar_wait(&acc_empty[ab], ((lt >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                // each issuer owns the accumulators of its block: with one buffer per block (NB = 128) the issuer of
+                // block 0 can start the next segment while the epilogue still reads block 1
+                const uint32_t ab = lt % BUFS, use = lt / BUFS;
+                if (!mbar_wait(&acc_empty[ab * 2 + hsel], (use & 1) ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
                 const bool mine = hsel >= static_cast<uint32_t>(w.h0) && hsel < static_cast<uint32_t>(w.h1);
                 const uint32_t d = tmem_base + (ab * 2 + hsel) * NB;
@@ -367,7 +373,7 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
                     if (++sl == TS) { sl = 0; ph_t ^= 1; }
                     if (++al == AS) { al = 0; ph_a ^= 1; }
                 }
-                if (ok) tc_commit(&acc_full[ab]);
+                if (ok) tc_commit(&acc_full[ab * 2 + hsel]);
             }
             tc_commit(drain);                      // both issuers: nothing of theirs is in flight when tensor memory is freed
             mbar_wait(drain, 0, abort_flag);
@@ -393,8 +399,8 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
         while (ok && w.next()) {
             for (int s = w.s0; s < w.s1; ++s, ++it) {
                 if ((it & 1) != turn) continue;
-                const uint32_t sw = it % kSkWStages, st = it % TS;
-                if (!mbar_wait_backoff(&w_full[sw], (it / kSkWStages) & 1, abort_flag, 32)) { ok = false; break; }
+                const uint32_t sw = it % WS, st = it % TS;
+                if (!mbar_wait_backoff(&w_full[sw], (it / WS) & 1, abort_flag, 32)) { ok = false; break; }
                 const uint32_t wp = w_sa + sw * kSkWpBytes;
                 // all loads of the stage first, so that their latencies overlap
                 uint32_t m[2][kSkBK / 32][4];
@@ -444,16 +450,21 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
         bool ok = true;
         SkWalk<kGrouped> w = make_walk();
         for (; ok && w.next(); ++lt) {
-            const uint32_t ab = lt & 1;
+            const uint32_t ab = lt % BUFS, use = lt / BUFS;
             const SkProblem* p = w.p;
             const int M = p->M, N = p->N;
             const long long ldc = p->ldc;
-            if (!mbar_wait_backoff(&acc_full[ab], (lt >> 1) & 1, abort_flag, 64)) { ok = false; break; }
-            tc_fence_after_sync();
             if (w.add_prev && !flag_wait(flags + blockIdx.x - 1, epoch, abort_flag)) { ok = false; break; }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                if (h < w.h0 || h >= w.h1) continue;
+                // both issuers signal every segment, also for a block the segment does not compute
+                if (!mbar_wait_backoff(&acc_full[ab * 2 + h], use & 1, abort_flag, 64)) { ok = false; break; }
+                tc_fence_after_sync();
+                if (h < w.h0 || h >= w.h1) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[ab * 2 + h]);
+                    continue;
+                }
                 const int col = w.block * kSkItemCols + h * 128 + col_in_block;
                 int32_t* out = p->C + col;
 #pragma unroll
@@ -461,10 +472,10 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
                     uint32_t r[16];
                     tmem_ld_32x32_x16(tmem_base + ((q * 32) << 16) + (ab * 2 + h) * NB + 16 * c, r);
                     tmem_ld_wait();
-                    if (h == w.h1 - 1 && c == NB / 16 - 1) {      // everything has been read: the next segment may accumulate here
+                    if (c == NB / 16 - 1) {      // this block's accumulator has been read: its issuer may use it again
                         tc_fence_before_sync();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(&acc_empty[ab]);
+                        if (lane == 0) mbar_arrive(&acc_empty[ab * 2 + h]);
                     }
                     if (col >= N) continue;
 #pragma unroll
@@ -480,6 +491,7 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
                     }
                 }
             }
+            if (!ok) break;
             if (!w.last) {
                 // raise this CTA's flag once all four epilogue warps have stored their part of the partial tile
                 __threadfence();

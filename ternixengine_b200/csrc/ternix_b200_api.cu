@@ -161,7 +161,7 @@ struct Options {
     int mma_slices = 0;                // K slices of a single mma.sync decode problem, 0 = cost model
     int mma_cluster = -1;              // 0 | 2 | 4 | 8: cluster form of the same, -1 = largest that fits
     int skinny_lo = 33, skinny_hi = 64; // rows of a single product served by the tensor-memory decode kernel (0,0 = never)
-    int skinny_group_lo = 17;          // the same for members of a problem group (one launch serves many products there)
+    int skinny_group_lo = 17, skinny_group_hi = 128;   // the same for members of a problem group (one launch serves many products there)
     int skinny_split = 1;              // 0: never share a block between CTAs; 1: only when blocks outnumber SMs; 2: whenever it evens the load
     int host_slab = -1;                // slab extent of the pipelined host-pointer call; 0 = off, -1 = plan
     bool host_slab_rows = false;
@@ -191,7 +191,9 @@ int apply_option(const char* name, const char* value) {
         g_opt.skinny_lo = def.skinny_lo; g_opt.skinny_hi = def.skinny_hi;
         if (!reset) std::sscanf(value, "%d,%d", &g_opt.skinny_lo, &g_opt.skinny_hi);
     } else if (!std::strcmp(name, "skinny_group_rows")) {
-        g_opt.skinny_group_lo = reset ? def.skinny_group_lo : std::atoi(value);
+        g_opt.skinny_group_lo = def.skinny_group_lo; g_opt.skinny_group_hi = def.skinny_group_hi;
+        if (!reset && std::sscanf(value, "%d,%d", &g_opt.skinny_group_lo, &g_opt.skinny_group_hi) == 1)
+            g_opt.skinny_group_hi = def.skinny_group_hi;
     } else if (!std::strcmp(name, "host_slab")) {
         g_opt.host_slab = def.host_slab; g_opt.host_slab_rows = false;
         if (!reset) {
@@ -264,9 +266,9 @@ constexpr int kGroupMmaMinRows = 2, kGroupMmaMaxRows = 64;
 bool decode_mma_ok(const void* dA, const void* dW, int M, int K, int N) {
     return M >= 1 && (N % 64) == 0 && (K % 16) == 0 && K >= 16 && K <= 65536 && aligned(dA, 16) && aligned(dW, 16);
 }
-// Tensor-memory decode kernel (kernel_skinny_tc.cuh): up to 64 rows.
+// Tensor-memory decode kernel (kernel_skinny_tc.cuh): up to 128 rows.
 bool skinny_ok(const void* dA, const void* dW, int M, int K, int N) {
-    return M >= 1 && M <= 64 && (N % 64) == 0 && (K % 16) == 0 && K >= 16 && K <= kMaxScaledK && aligned(dA, 16) &&
+    return M >= 1 && M <= 128 && (N % 64) == 0 && (K % 16) == 0 && K >= 16 && K <= kMaxScaledK && aligned(dA, 16) &&
            aligned(dW, 16);
 }
 
@@ -705,7 +707,7 @@ int next_skinny_epoch() {
     return static_cast<int>(e & 0x7fffffffu);
 }
 
-int skinny_rows_class(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : 64; }
+int skinny_rows_class(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
 
 int make_skinny_problem(tb200::SkProblem* out, const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int K, int N,
                         long long ldc) {
@@ -781,7 +783,8 @@ int launch_skinny_problem(const tb200::SkProblem& prob, int32_t* d_status, cudaS
     switch (skinny_rows_class(prob.M)) {
         case 16: return launch_skinny_t<16, false>(prob, sg, nullptr, nullptr, nullptr, grid, d_flags, epoch, d_status, st);
         case 32: return launch_skinny_t<32, false>(prob, sg, nullptr, nullptr, nullptr, grid, d_flags, epoch, d_status, st);
-        default: return launch_skinny_t<64, false>(prob, sg, nullptr, nullptr, nullptr, grid, d_flags, epoch, d_status, st);
+        case 64: return launch_skinny_t<64, false>(prob, sg, nullptr, nullptr, nullptr, grid, d_flags, epoch, d_status, st);
+        default: return launch_skinny_t<128, false>(prob, sg, nullptr, nullptr, nullptr, grid, d_flags, epoch, d_status, st);
     }
 }
 
@@ -939,14 +942,14 @@ struct ternix_b200_group {
         int grid = 0;
     } mma[2];
     size_t mma_grouped = 0;
-    // batched-decode members served by the tensor-memory kernel: one launch per batch class (16, 32, 64 rows)
+    // batched-decode members served by the tensor-memory kernel: one launch per batch class (16, 32, 64, 128 rows)
     struct SkTables {
         void* d_blob = nullptr;                 // [SkProblem[] | SkItem[] | int cta_first[]]
         const tb200::SkProblem* d_probs = nullptr;
         const tb200::SkItem* d_items = nullptr;
         const int* d_first = nullptr;
         int grid = 0;
-    } sk[3];
+    } sk[4];
     size_t sk_grouped = 0;
     // members the grouped kernels could not take but that have peer destinations: copied after their launch
     struct PeerCopy { ternix_b200_problem q; std::vector<int32_t*> peers; };
@@ -1602,7 +1605,7 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
     std::vector<tb200::Tc3Problem> tc3_probs;
     bool tc3_group = options().tc3 != 0;                  // option tc3 = 0: the expanding kernel
     std::vector<tb200::MmaProblem> mma_probs[2];          // row groups of 8, of 16
-    std::vector<tb200::SkProblem> sk_probs[3];            // batch classes 16, 32, 64
+    std::vector<tb200::SkProblem> sk_probs[4];            // batch classes 16, 32, 64, 128
     std::vector<tb200::GroupProblem> probs;
     struct HostItem { tb200::GroupItem item; long cost; };
     std::vector<HostItem> items;
@@ -1658,12 +1661,12 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
             for (int j = 0; j < n_peers; ++j) pc.peers.push_back(peer_dC[static_cast<size_t>(i) * n_peers + j]);
             g->single_peers.push_back(pc);
         }
-        if (!prepacked && opt.skinny_group_lo > 0 && q.M >= opt.skinny_group_lo && q.M <= 64 && q.K > 0 &&
+        if (!prepacked && opt.skinny_group_lo > 0 && q.M >= opt.skinny_group_lo && q.M <= opt.skinny_group_hi && q.K > 0 &&
             skinny_ok(q.dA, q.dW, q.M, q.K, q.N)) {
             tb200::SkProblem sp;
             const int rc = make_skinny_problem(&sp, q.dA, q.dW, q.dC, q.M, q.K, q.N, q.ldc);
             if (rc) { delete g; return rc; }
-            sk_probs[q.M <= 16 ? 0 : q.M <= 32 ? 1 : 2].push_back(sp);
+            sk_probs[q.M <= 16 ? 0 : q.M <= 32 ? 1 : q.M <= 64 ? 2 : 3].push_back(sp);
             ++g->sk_grouped;
             continue;
         }
@@ -1842,7 +1845,7 @@ static int group_create_impl(ternix_b200_group** out, const ternix_b200_problem*
         mt.d_first = reinterpret_cast<const int*>(d + b_probs + b_items);
         mt.grid = ctas;
     }
-    for (int v = 0; v < 3; ++v) {
+    for (int v = 0; v < 4; ++v) {
         if (sk_probs[v].empty()) continue;
         // whole-K items of 256 columns in (problem, block) order, dealt out to the least-loaded CTA: with equal costs
         // neighbouring CTAs stream neighbouring blocks of the same weight rows at the same time
@@ -1968,7 +1971,7 @@ int ternix_b200_group_run(const ternix_b200_group* g, int32_t* d_status, void* s
                 none, sg, mt.d_probs, mt.d_items, mt.d_first, d_status);
         TB_CUDA(cudaGetLastError());
     }
-    for (int v = 0; v < 3; ++v) {
+    for (int v = 0; v < 4; ++v) {
         const auto& t = g->sk[v];
         if (t.grid == 0) continue;
         const tb200::SkProblem none{};
@@ -1976,7 +1979,8 @@ int ternix_b200_group_run(const ternix_b200_group* g, int32_t* d_status, void* s
         int rc;
         if (v == 0) rc = launch_skinny_t<16, true>(none, sg, t.d_probs, t.d_items, t.d_first, t.grid, nullptr, 0, d_status, st);
         else if (v == 1) rc = launch_skinny_t<32, true>(none, sg, t.d_probs, t.d_items, t.d_first, t.grid, nullptr, 0, d_status, st);
-        else rc = launch_skinny_t<64, true>(none, sg, t.d_probs, t.d_items, t.d_first, t.grid, nullptr, 0, d_status, st);
+        else if (v == 2) rc = launch_skinny_t<64, true>(none, sg, t.d_probs, t.d_items, t.d_first, t.grid, nullptr, 0, d_status, st);
+        else rc = launch_skinny_t<128, true>(none, sg, t.d_probs, t.d_items, t.d_first, t.grid, nullptr, 0, d_status, st);
         if (rc) return rc;
     }
     for (const ternix_b200_problem& q : g->singles) {

@@ -18,7 +18,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 @pytest.mark.parametrize("split", ["1", "2", "0"])
 def test_skinny_tc_rows_shapes_and_edges(option, split):
-    """Every batch class and its edges (1, 16, 17, 32, 33, 64 rows), K that is not a multiple of the 128-row stage,
+    """Every batch class and its edges (1, 16, 17, 32, 33, 64, 65, 128 rows), K that is not a multiple of the 128-row stage,
     column counts that leave the second 128-column block of an item empty or ragged, a padded C, single-stage and
     deep problems; with the default plan (whole-K items unless blocks outnumber SMs), with blocks shared between CTAs
     wherever that evens the load (2: partial sums handed on through C, chains of up to three CTAs) and with whole
@@ -27,17 +27,18 @@ def test_skinny_tc_rows_shapes_and_edges(option, split):
     for (m, k, n, pad) in [(1, 64, 64, 0), (1, 2560, 6912, 0), (2, 2560, 640, 0), (3, 1040, 320, 1), (7, 4112, 1088, 0),
                            (15, 16, 64, 3), (16, 6912, 2560, 0), (17, 272, 576, 0), (32, 4096, 11008, 0),
                            (33, 8192, 128, 4), (48, 1024, 2112, 0), (64, 2560, 6912, 0), (64, 144, 704, 8),
-                           (5, 65536, 256, 0), (40, 512, 40960, 0)]:        # the last one: more 256-column blocks than SMs
+                           (5, 65536, 256, 0), (65, 272, 576, 0), (100, 2560, 6912, 8), (128, 4096, 2048, 0),
+                           (40, 512, 40960, 0)]:                            # the last one: more 256-column blocks than SMs
         a, wp = synth(m, k, n, 90 + m + k)
         assert_same(device_matmul(a, wp, "skinny_tc", pad_cols=pad), oracle_lib.matmul(a, wp),
                     f"skinny_tc split={split} {m}x{k}x{n} pad {pad}")
-    for m in (1, 16, 64):                                  # largest magnitudes: 64 * 128 * K stays inside int32
+    for m in (1, 16, 64, 128):                             # largest magnitudes: 64 * 128 * K stays inside int32
         k, n = 8192, 512
         a = np.full((m, k), -128, dtype=np.int8)
         wp = np.full((k, n // 4), 0xFF, dtype=np.uint8)
         assert (device_matmul(a, wp, "skinny_tc") == 128 * k).all()
-    with pytest.raises(ValueError):                        # 65 rows are the prefill kernels' business
-        a, wp = synth(65, 256, 256, 1)
+    with pytest.raises(ValueError):                        # more than 128 rows are the prefill kernels' business
+        a, wp = synth(129, 256, 256, 1)
         device_matmul(a, wp, "skinny_tc")
 
 
@@ -87,16 +88,16 @@ def test_skinny_tc_two_streams_use_two_flag_slots():
         assert all(bool((x == expect).all()) for x in o)
 
 
-@pytest.mark.parametrize("M", [2, 8, 16, 24, 64])
+@pytest.mark.parametrize("M", [2, 8, 16, 24, 64, 100])
 @pytest.mark.parametrize("skinny_from", ["default", "2", "0"])
 def test_projection_group_batched_decode(option, M, skinny_from):
     """config 5 at a few rows: one BitNet-shaped layer plus odd members in one group.  Members with several rows run
     on the tensor-memory decode kernel from 17 rows up (default), from 2 rows up, or never (then the mma.sync kernel
-    takes them all)."""
+    takes them up to 64 rows and larger ones are launched one by one)."""
     import torch
     if skinny_from != "default":
         option("skinny_group_rows", skinny_from)
-    lo = {"default": 17, "2": 2, "0": 65}[skinny_from]
+    lo = {"default": 17, "2": 2, "0": 129}[skinny_from]
     shapes = [(M, k, n) for (_, k, n) in BITNET_LAYER] + [(3, 1040, 320), (40, 144, 64), (1, 2560, 640)]
     probs, expect = [], []
     for i, (m, k, n) in enumerate(shapes):
@@ -107,9 +108,10 @@ def test_projection_group_batched_decode(option, M, skinny_from):
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     group = tb.ProjectionGroup(probs)
     rows = [m for (m, _, _) in shapes]
-    skinny_classes = {16 if m <= 16 else 32 if m <= 32 else 64 for m in rows if lo <= m <= 64}
-    mma_sizes = {8 if m <= 8 else 16 for m in rows if 2 <= m < lo}
-    assert group.launches == 1 + len(skinny_classes) + len(mma_sizes)
+    skinny_classes = {16 if m <= 16 else 32 if m <= 32 else 64 if m <= 64 else 128 for m in rows if lo <= m <= 128}
+    mma_sizes = {8 if m <= 8 else 16 for m in rows if 2 <= m < lo and m <= 64}
+    singles = sum(1 for m in rows if m > 64 and m < lo)          # 65..128 rows without the tensor-memory kernel: one by one
+    assert group.launches == 1 + len(skinny_classes) + len(mma_sizes) + singles
     for _ in range(3):
         for p in probs:
             p[2].fill_(-1)
