@@ -199,7 +199,10 @@ __device__ __forceinline__ void sts_u16(uint32_t saddr, uint16_t v) {
 // kBf16: the epilogue emits bfloat16 = bf16_rn((float(c) * row_scale[m]) * w_scale) instead of int32 (the scaling
 // step that follows the product in a BitNet-style layer); `stores` then describes bfloat16 tensors and `C`, `ldc`
 // are the bfloat16 output and its pitch in elements.
-template <bool kGrouped, bool kBf16 = false>
+// TA: activation rows per pair instruction (the MMA's N).  256 is the full-rate form; 128 serves products with at
+// most 128 rows, which the 256-row tile would pad to twice their work: each CTA then loads 64 rows per stage into
+// the same stage layout and the pair's MMAs are half as long.
+template <bool kGrouped, bool kBf16 = false, int TA = kTc3TileA>
 __global__ void __launch_bounds__(kTc3Threads, 1)
 ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                         const __grid_constant__ Tc3Stores stores, int32_t* __restrict__ C, int M, int K, int N,
@@ -207,6 +210,12 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         const int* __restrict__ pair_first, int32_t* __restrict__ status,
                         const float* __restrict__ row_scale = nullptr, float w_scale = 1.0f) {
     static_assert(!(kGrouped && kBf16), "the dequantising epilogue is built for single products");
+    static_assert(TA == 256 || (TA == 128 && !kGrouped && !kBf16), "the 128-row form is built for single int32 products");
+    constexpr int kRowsPerCta = TA / 2;                                    // activation rows a CTA loads per stage
+    constexpr uint32_t kStageTx = kRowsPerCta * kTc3BK + kTc3WpBytes;      // bytes a stage's TMA loads deliver
+    constexpr int kSteps = TA / 32 / kTc3EpiGroups;                        // accumulator steps of 32 rows per epilogue warp
+    constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(TA >> 3) << 17) |
+                                (static_cast<uint32_t>(256 >> 4) << 24);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sAct = base;                                            // [stages][128 rows][128 k]  128-byte swizzle
@@ -234,7 +243,7 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         } else {
             w.ta = &tmap_a; w.tw = &tmap_w; w.st = &stores;
             w.C = C; w.ldc = ldc; w.M = M; w.N = N;
-            w.a_tiles = (M + kTc3TileA - 1) / kTc3TileA;
+            w.a_tiles = (M + TA - 1) / TA;
             w.num_tiles = w.a_tiles * ((N + kTc3TileW - 1) / kTc3TileW);
             w.k_blocks = (K + kTc3BK - 1) / kTc3BK;
             w.tile = pair; w.stride = num_pairs;
@@ -276,12 +285,12 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             bool ok = true;
             Tc3Walk<kGrouped> w = make_walk();
             while (ok && w.next()) {
-                const int row0 = w.a_t * kTc3TileA + rank * 128;
+                const int row0 = w.a_t * TA + rank * kRowsPerCta;
                 const int wp_x = (w.w_t * kTc3TileW + rank * 128) / 4;
                 for (int kb = 0; kb < w.k_blocks; ++kb, ++it) {
                     const uint32_t s = it % kTc3Stages;
                     if (!mbar_wait_backoff(&empty[s], ((it / kTc3Stages) & 1) ^ 1, abort_flag, 32)) { ok = false; break; }
-                    mbar_arrive_expect_tx(&full[s], kTc3StageBytes);
+                    mbar_arrive_expect_tx(&full[s], kStageTx);
 #pragma unroll
                     for (int j = 0; j < kTc3BK / 128; ++j)
                         tma_load_2d(sAct + s * kTc3ActBytes + j * 16384, w.ta, kb * kTc3BK + j * 128, row0, &full[s]);
@@ -311,7 +320,7 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #pragma unroll
                     for (int g = 0; g < kTc3BK / 32; ++g) {
                         const uint64_t db = umma_desc_sw128(act_addr + (g >> 2) * 16384 + (g & 3) * 32, 16, 1024);
-                        tc_mma_i8_pair_tmem_a(tmem_base, a_col + 8 * g, db, kTc3Idesc, (kb != 0 || g != 0) ? 1u : 0u);
+                        tc_mma_i8_pair_tmem_a(tmem_base, a_col + 8 * g, db, kIdesc, (kb != 0 || g != 0) ? 1u : 0u);
                     }
                     tc_commit_pair_both(&empty[s]);
                 }
@@ -399,9 +408,9 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             tc_fence_after_sync();
             const int col0 = w.w_t * kTc3TileW + rank * 128;
             // this warp's share of the accumulator into registers, all of it, and tensor memory is free again
-            uint32_t r[kTc3StepsPerWarp][32];
+            uint32_t r[kSteps][32];
 #pragma unroll
-            for (int i = 0; i < kTc3StepsPerWarp; ++i)
+            for (int i = 0; i < kSteps; ++i)
                 tmem_ld_32x32(tmem_base + ((q * 32) << 16) + 32 * (eg + kTc3EpiGroups * i), r[i]);
             tmem_ld_wait();
             tc_fence_before_sync();
@@ -411,13 +420,13 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 else mbar_arrive_remote(acc_empty, 0);
             }
 #pragma unroll
-            for (int i = 0; i < kTc3StepsPerWarp; ++i, ++step) {
+            for (int i = 0; i < kSteps; ++i, ++step) {
                 const int c = eg + kTc3EpiGroups * i;
                 const uint32_t buf = epi_sa + (eg * kTc3EpiBufs + step % kTc3EpiBufs) * kTc3EpiBytes;
                 // the store that last read this buffer has finished reading
                 if (elected) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kTc3EpiBufs - 1) : "memory");
                 asm volatile("bar.sync %0, 128;" ::"r"(2 + eg) : "memory");
-                const int row0 = a_t * kTc3TileA + 32 * c;
+                const int row0 = a_t * TA + 32 * c;
                 if constexpr (kBf16) {
                     // in place: r[i][j] becomes the bfloat16 bit pattern of the scaled value
 #pragma unroll

@@ -567,9 +567,12 @@ int launch_gemm_tc2_expand(const int8_t* dA, const uint8_t* dW, int32_t* const* 
 
 // Paired CTAs with the weights as the A operand in tensor memory (kernel_gemm_tc3.cuh).  Several destinations need
 // every C to be describable to the TMA unit (16-byte aligned base and pitch); ERR_UNSUPPORTED otherwise.
-int make_tc3_act_map(CUtensorMap* out, const int8_t* dA, int M, int K) {
+// Activation rows per pair instruction: the 128-row form for products that have no more rows than that.
+int tc3_tile_rows(int M) { return M <= 128 ? 128 : 256; }
+
+int make_tc3_act_map(CUtensorMap* out, const int8_t* dA, int M, int K, int tile_rows = 256) {
     return make_tmap_2d(out, dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), tb200::kTcBK,
-                        128, CU_TENSOR_MAP_SWIZZLE_128B);
+                        tile_rows / 2, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 int make_tc3_weight_map(CUtensorMap* out, const uint8_t* dW, int K, int N) {
     return make_tmap_2d(out, dW, static_cast<uint64_t>(N / 4), static_cast<uint64_t>(K), static_cast<uint64_t>(N / 4),
@@ -579,11 +582,11 @@ int make_tc3_store_map(CUtensorMap* out, int32_t* dC, int M, int N, long long ld
     return make_tmap_2d_u32(out, dC, static_cast<uint64_t>(N), static_cast<uint64_t>(M), static_cast<uint64_t>(ldc) * 4, 128, 32);
 }
 
-int launch_gemm_tc3_maps(const CUtensorMap& tmap_a, const CUtensorMap& tmap_w, const tb200::Tc3Stores& stores, int32_t* dC0,
-                         int M, int K, int N, long long ldc, int32_t* d_status, cudaStream_t st) {
-    if (const int arc = ensure_smem_attr<tb200::ternary_gemm_tc3_kernel<false>>(tb200::kTc3SmemBytes)) return arc;
-    const long tiles = static_cast<long>((M + tb200::kTc3TileA - 1) / tb200::kTc3TileA) *
-                       ((N + tb200::kTc3TileW - 1) / tb200::kTc3TileW);
+template <int TA>
+int launch_gemm_tc3_maps_t(const CUtensorMap& tmap_a, const CUtensorMap& tmap_w, const tb200::Tc3Stores& stores, int32_t* dC0,
+                           int M, int K, int N, long long ldc, int32_t* d_status, cudaStream_t st) {
+    if (const int arc = ensure_smem_attr<tb200::ternary_gemm_tc3_kernel<false, false, TA>>(tb200::kTc3SmemBytes)) return arc;
+    const long tiles = static_cast<long>((M + TA - 1) / TA) * ((N + tb200::kTc3TileW - 1) / tb200::kTc3TileW);
     const long max_pairs = sm_count() / 2;
     const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
     cudaLaunchConfig_t cfg{};
@@ -601,9 +604,17 @@ int launch_gemm_tc3_maps(const CUtensorMap& tmap_a, const CUtensorMap& tmap_w, c
     const tb200::Tc3Problem* no_probs = nullptr;
     const tb200::Tc2Tile* no_tiles = nullptr;
     const int* no_first = nullptr;
-    TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc3_kernel<false>, tmap_a, tmap_w, stores, dC0, M, K, N, ldc,
+    TB_CUDA(cudaLaunchKernelEx(&cfg, tb200::ternary_gemm_tc3_kernel<false, false, TA>, tmap_a, tmap_w, stores, dC0, M, K, N, ldc,
                                no_probs, no_tiles, no_first, d_status, static_cast<const float*>(nullptr), 1.0f));
     return TERNIX_B200_OK;
+}
+
+// tmap_a must have been made for tc3_tile_rows(M).
+int launch_gemm_tc3_maps(const CUtensorMap& tmap_a, const CUtensorMap& tmap_w, const tb200::Tc3Stores& stores, int32_t* dC0,
+                         int M, int K, int N, long long ldc, int32_t* d_status, cudaStream_t st) {
+    if (tc3_tile_rows(M) == 128)
+        return launch_gemm_tc3_maps_t<128>(tmap_a, tmap_w, stores, dC0, M, K, N, ldc, d_status, st);
+    return launch_gemm_tc3_maps_t<256>(tmap_a, tmap_w, stores, dC0, M, K, N, ldc, d_status, st);
 }
 
 int launch_gemm_tc3(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list, int n_dest, int M, int K, int N,
@@ -613,7 +624,7 @@ int launch_gemm_tc3(const int8_t* dA, const uint8_t* dW, int32_t* const* dC_list
     for (int d = 0; d < n_dest; ++d) tma_ok = tma_ok && aligned(dC_list[d], 16);
     if (!tma_ok && n_dest > 1) return TERNIX_B200_ERR_UNSUPPORTED;
     CUtensorMap tmap_a, tmap_w;
-    int rc = make_tc3_act_map(&tmap_a, dA, M, K);
+    int rc = make_tc3_act_map(&tmap_a, dA, M, K, tc3_tile_rows(M));
     if (rc) return rc;
     rc = make_tc3_weight_map(&tmap_w, dW, K, N);
     if (rc) return rc;
@@ -2224,7 +2235,7 @@ int ternix_b200_weights_matmul(ternix_b200_weights* w, const int8_t* dA, int32_t
         {
             std::lock_guard<std::mutex> lock(w->mu);
             if (w->a_ptr[1] != dA || w->a_rows[1] != M) {
-                const int rc = make_tc3_act_map(&w->tmap_a[1], dA, M, K);
+                const int rc = make_tc3_act_map(&w->tmap_a[1], dA, M, K, tc3_tile_rows(M));
                 if (rc) return rc;
                 w->a_ptr[1] = dA;
                 w->a_rows[1] = M;
