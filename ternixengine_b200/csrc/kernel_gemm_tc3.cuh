@@ -83,7 +83,7 @@ constexpr int kTc3StepsPerWarp = kTc3TileA / 32 / kTc3EpiGroups;                
 // the last MMA of a tile, long before the stores have drained.  The kernel is launched with 96 registers per thread
 // (640 x 96 = 61,440), and 128 x 48 + 256 x 64 + 256 x 152 = 61,440 is exactly that.
 constexpr int kTc3RegsControl = 48, kTc3RegsExpand = 64, kTc3RegsEpilogue = 152;
-static_assert(kTc3EpiGroups == 2 && kTc3ExpandWarps == 8, "the register budget above is worked out for this role layout");
+static_assert(kTc3EpiGroups == 2 && kTc3ExpandWarps == 8, "the register counts above are worked out for this role layout");
 static_assert(128 * kTc3RegsControl + kTc3ExpandWarps * 32 * kTc3RegsExpand + kTc3EpiGroups * 128 * kTc3RegsEpilogue <=
                   kTc3Threads * 96,
               "register hand-over exceeds what the CTA owns at launch");
@@ -271,7 +271,7 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    // Each role branch opens with its register hand-over, so that the compiler sees the budget of the code behind it.
+    // Each role branch opens with its register hand-over, so that the compiler sees how many registers the code behind it may use.
     if (warp < kTc3FirstExpandWarp) {
       warpgroup_regs_release<kTc3RegsControl>();
       if (warp == 0) {

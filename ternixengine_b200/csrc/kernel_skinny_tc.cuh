@@ -74,9 +74,9 @@ struct SkGeom {
     static constexpr int kWStages = NB == 128 ? 8 : 16;          // packed-weight ring (shared memory): what is in flight from HBM
     static constexpr int kAStages = NB == 128 ? 6 : NB == 64 ? 8 : 16;   // activation ring (shared memory)
     static constexpr uint32_t kRingCol = 2 * kAccBufs * NB;      // after the accumulators: [buffer][block] x NB columns
-    static_assert(kRingCol + kTStages * kSkStageCols <= 512, "tensor memory budget");
+    static_assert(kRingCol + kTStages * kSkStageCols <= 512, "tensor memory: 512 columns");
     static constexpr size_t kSmemBytes = 1024 + size_t(kWStages) * kSkWpBytes + size_t(kAStages) * kActBytes + 768;
-    static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory: 227 KB per CTA");
     // D = s32, A = B = s8, both K-major, N = NB, M = 128
     static constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(NB >> 3) << 17) | (uint32_t(128 >> 4) << 24);
 };
