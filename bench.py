@@ -341,9 +341,23 @@ def run_b200(args):
     if world > 1:
         ms_store = max_over_ranks(timed(lambda: layer.forward(da, barrier=False), args.steps, args.warmup, barrier))
         ms_bar = max_over_ranks(timed(layer.stream_barrier, args.steps, args.warmup, barrier))
+        # what the store path alone sustains: the same output (same M, same shard, same destinations) from a product
+        # with K = 256, whose arithmetic is 1/32 of config 3's, so that the launch is all stores
+        k_probe = 256
+        probe = tb.ShardedTernaryLinear(tb.synth_packed_weights(k_probe, N, SEED + 77), device=dev)
+        da_probe = torch.from_numpy(tb.synth_activations((M, k_probe), SEED + 78)).to(dev)
+        ms_probe = max_over_ranks(timed(lambda: probe.forward(da_probe, barrier=False), args.steps, args.warmup, barrier))
+        ms_probe_local = max_over_ranks(timed(lambda: probe.local(da_probe, out=local_out[:, :shard.n_cols]), args.steps,
+                                              args.warmup, barrier))
+        out_bytes = 4 * M * shard.n_cols * (world - 1)
         gather_parts = {"gemm_with_peer_stores_ms": ms_store / args.steps, "stream_barrier_ms": ms_bar / args.steps,
-                        "shard_gemm_alone_ms": ms_local / args.steps,
-                        "nvlink_bytes_out_per_rank": 4 * M * shard.n_cols * (world - 1)}
+                        "shard_gemm_alone_ms": ms_local / args.steps, "nvlink_bytes_out_per_rank": out_bytes,
+                        "nvlink_gbs_out_per_rank": out_bytes / (ms_store / args.steps * 1e-3) / 1e9,
+                        "store_only_probe": {"what": f"same output from a K={k_probe} product: the launch is all stores",
+                                             "ms_with_peer_stores": ms_probe / args.steps,
+                                             "ms_local_stores_only": ms_probe_local / args.steps,
+                                             "nvlink_gbs_out_per_rank": out_bytes / (ms_probe / args.steps * 1e-3) / 1e9}}
+        del probe, da_probe
 
     # ---- sustained figure: the same launch back to back for seconds, clocks sampled throughout
     sustained = None
