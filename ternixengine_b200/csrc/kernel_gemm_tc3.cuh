@@ -64,6 +64,9 @@ constexpr uint32_t kTc3AccCols = 256, kTc3ARingCol = 256, kTc3AStageCols = kTc3B
 #ifndef TB200_TC3_SLEEP_NS
 #define TB200_TC3_SLEEP_NS 64
 #endif
+#ifndef TB200_TC3_ACC_SLEEP_NS
+#define TB200_TC3_ACC_SLEEP_NS 64        // pause between the epilogue warps' probes of the "accumulator full" barrier
+#endif
 constexpr int kTc3ExpandWarps = TB200_TC3_EXPAND_WARPS;      // 4, 8 or 12: one, two or three warps per lane quarter
 constexpr int kTc3WarpsPerQuarter = kTc3ExpandWarps / 4;     // they take the stages in turn (stage it -> warp it % n)
 static_assert(TB200_TC3_STAGES % (TB200_TC3_EXPAND_WARPS / 4) == 0,
@@ -404,7 +407,7 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             const int M = w.M, N = w.N;
             const long long ldc = w.ldc;
             int32_t* C = w.C;
-            if (!mbar_wait_backoff(acc_full, lt & 1, abort_flag, 256)) { ok = false; break; }
+            if (!mbar_wait_backoff(acc_full, lt & 1, abort_flag, TB200_TC3_ACC_SLEEP_NS)) { ok = false; break; }
             tc_fence_after_sync();
             const int col0 = w.w_t * kTc3TileW + rank * 128;
             // this warp's share of the accumulator into registers, all of it, and tensor memory is free again
