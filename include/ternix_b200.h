@@ -147,13 +147,17 @@ int ternix_b200_selftest_wait_timeout(unsigned long long limit_ns, int32_t *d_st
 /* ---- problem groups: many projections per launch ----------------------------------------------
  * No reference counterpart (the reference launches one product at a time; its README lists
  * graph-captured projection sets as future work, README.md:213).  A group is built once from a list of
- * problems on device pointers and then run any number of times.  Decode-regime problems (M <= 16,
- * K <= 8192, K % 16 == 0, N % 64 == 0, 16-byte aligned A and W) are served by ONE persistent kernel that
- * streams all their weights back to back; prefill-regime problems (M > 128, N >= 256, K % 16 == 0,
- * N % 64 == 0, aligned) by ONE launch of the paired-CTA tensor-core GEMM that walks all their tiles; the
- * others are launched one by one behind them.  create()
- * allocates a small device table (TMA descriptors and the work list) and copies it synchronously;
- * run() only launches, on `stream`.  The pointers inside the problems must stay valid while the group lives. */
+ * problems on device pointers and then run any number of times.  Members that a TMA descriptor can describe
+ * (K % 16 == 0, N % 64 == 0, 16-byte aligned A and W) share launches by regime: one-row members (K <= 8192) ONE
+ * persistent kernel that streams all their weights back to back; members with 2..16 rows one launch of the
+ * mma.sync decode kernel per row-group size (8, 16); members with 17..128 rows one launch of the tensor-memory
+ * decode kernel per batch class (16, 32, 64, 128); members with more than 128 rows (N >= 256) ONE launch of the
+ * paired-CTA tensor-core GEMM that walks all their tiles.  The others are launched one by one behind them.
+ * create() allocates small device tables (TMA descriptors and the work lists) and copies them synchronously;
+ * run() only launches, on `stream`.  The pointers inside the problems must stay valid while the group lives.
+ * A one-row batch with at most four work items per CTA is launched as a programmatic dependent of the kernel
+ * before it on the stream: behind another decode batch of this library it starts streaming weights while that
+ * batch finishes (activations are read and C is written only after it has completed). */
 typedef struct ternix_b200_problem {
     const int8_t *dA;      /* [M,K] int8 row-major          */
     const uint8_t *dW;     /* packed K x (N/4)              */
@@ -180,7 +184,7 @@ size_t ternix_b200_prepack_k4_bytes(int K, int N);
 int ternix_b200_prepack_k4(const uint8_t *dW, uint8_t *dW_prepacked, int K, int N, void *stream);
 int ternix_b200_group_create_prepacked(ternix_b200_group **out, const ternix_b200_problem *problems, int count);
 int ternix_b200_group_run(const ternix_b200_group *group, int32_t *d_status, void *stream);
-/* Kernel launches one run() makes (1 for the persistent kernel + 1 per problem it could not take). */
+/* Kernel launches one run() makes (one per regime in use + 1 per problem no grouped kernel could take). */
 int ternix_b200_group_launches(const ternix_b200_group *group);
 void ternix_b200_group_destroy(ternix_b200_group *group);
 
