@@ -89,3 +89,22 @@ def test_noalloc_batch_limits_and_rejections():
     assert _run_noalloc(many, outs, status) == tb.ERR_TOO_LARGE
     assert tb.lib.ternix_b200_gemv_batch_noalloc(None, 0, None, None) == tb.OK
     torch.cuda.synchronize()
+    # a member with K == 0 is an empty sum: its C is zeroed, as in the single-product calls
+    a0 = torch.zeros((2, 0), dtype=torch.int8, device="cuda")
+    w0 = torch.zeros((0, 16), dtype=torch.uint8, device="cuda")
+    c0 = torch.full((2, 64), 7, dtype=torch.int32, device="cuda")
+    prob = (tb._Problem * 1)(tb._Problem(a0.data_ptr(), w0.data_ptr(), c0.data_ptr(), 2, 0, 64, 64))
+    assert tb.lib.ternix_b200_gemv_batch_noalloc(prob, 1, status.data_ptr(), torch.cuda.current_stream().cuda_stream) == tb.OK
+    torch.cuda.synchronize()
+    assert bool((c0 == 0).all())
+    # a stream that is being captured is refused: the tables are uploaded from one fixed host buffer, which a graph
+    # would read at replay time, after later calls have rewritten it
+    s = torch.cuda.Stream()
+    out = torch.zeros((1, 64), dtype=torch.int32, device="cuda")
+    with torch.cuda.stream(s):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            prob = (tb._Problem * 1)(tb._Problem(a.data_ptr(), w.data_ptr(), out.data_ptr(), 1, 64, 64, 64))
+            rc = tb.lib.ternix_b200_gemv_batch_noalloc(prob, 1, None, s.cuda_stream)
+    assert rc == tb.ERR_UNSUPPORTED
+    torch.cuda.synchronize()
