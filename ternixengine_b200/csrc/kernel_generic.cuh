@@ -7,6 +7,8 @@
 //
 // CTA = 32 x 8 threads, output tile 32 rows x 128 columns, K walked in slabs of 64 through
 // shared memory.  Thread (tx, ty) owns rows 4*ty..4*ty+3 and the four columns of packed byte tx.
+// Problems with few output tiles (ragged decode shapes: a handful of rows, a thousand columns) are cut along K
+// over blockIdx.z; the slices then add into a C that the host has zeroed (integer adds: still exact).
 #pragma once
 #include <cstdint>
 
@@ -19,7 +21,7 @@ constexpr int kGenThreads = 256;
 
 __global__ void __launch_bounds__(kGenThreads)
 ternary_generic_kernel(const int8_t* __restrict__ A, const uint8_t* __restrict__ W, int32_t* __restrict__ C,
-                       int M, int K, int N, long long ldc) {
+                       int M, int K, int N, long long ldc, int k_per_slice) {
     __shared__ __align__(16) int8_t sA[kGenRows][kGenK];
     __shared__ __align__(16) uint8_t sW[kGenK][kGenBytes];
 
@@ -40,18 +42,23 @@ ternary_generic_kernel(const int8_t* __restrict__ A, const uint8_t* __restrict__
     const int a_row = tid >> 3, a_k = (tid & 7) * 8;
     const int w_k = tid >> 2, w_b = (tid & 3) * 8;
 
-    for (int k0 = 0; k0 < K; k0 += kGenK) {
+    // this CTA's k-range: all of K, or slice blockIdx.z of it (k_per_slice is a multiple of the slab)
+    const bool sliced = gridDim.z > 1;
+    const int k_begin = sliced ? static_cast<int>(blockIdx.z) * k_per_slice : 0;
+    const int k_end = sliced ? min(K, k_begin + k_per_slice) : K;
+
+    for (int k0 = k_begin; k0 < k_end; k0 += kGenK) {
         {
             const int grow = row0 + a_row;
             const int8_t* src = A + static_cast<size_t>(grow) * K + k0 + a_k;
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-                sA[a_row][a_k + i] = (grow < M && k0 + a_k + i < K) ? src[i] : int8_t(0);
+                sA[a_row][a_k + i] = (grow < M && k0 + a_k + i < k_end) ? src[i] : int8_t(0);
             const int gk = k0 + w_k;
             const uint8_t* wsrc = W + static_cast<size_t>(gk) * pitch + byte0 + w_b;
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-                sW[w_k][w_b + i] = (gk < K && byte0 + w_b + i < pitch) ? wsrc[i] : uint8_t(0);
+                sW[w_k][w_b + i] = (gk < k_end && byte0 + w_b + i < pitch) ? wsrc[i] : uint8_t(0);
         }
         __syncthreads();
 
@@ -84,8 +91,13 @@ ternary_generic_kernel(const int8_t* __restrict__ A, const uint8_t* __restrict__
             const int row = row0 + ty * 4 + r;
             if (row < M) {
                 int32_t* out = C + static_cast<size_t>(row) * ldc + col;
+                if (sliced) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) out[c] = acc[r][c];
+                    for (int c = 0; c < 4; ++c) atomicAdd(out + c, acc[r][c]);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) out[c] = acc[r][c];
+                }
             }
         }
     }

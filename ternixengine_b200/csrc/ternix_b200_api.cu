@@ -291,7 +291,18 @@ int launch_generic(const int8_t* dA, const uint8_t* dW, int32_t* dC, int M, int 
     const int pitch = N / 4;
     dim3 grid((pitch + tb200::kGenBytes - 1) / tb200::kGenBytes, (M + tb200::kGenRows - 1) / tb200::kGenRows);
     if (grid.y > 65535) return TERNIX_B200_ERR_INVALID_SHAPE;
-    tb200::ternary_generic_kernel<<<grid, tb200::kGenThreads, 0, st>>>(dA, dW, dC, M, K, N, ldc);
+    // Few output tiles: cut K into slices (two CTAs per SM in all) that add into a zeroed C.
+    const long tiles = static_cast<long>(grid.x) * grid.y;
+    const int slabs = (K + tb200::kGenK - 1) / tb200::kGenK;
+    int k_per_slice = K;
+    if (tiles < sm_count() && slabs >= 8) {
+        const int slices = static_cast<int>(std::min<long>(slabs, (2L * sm_count() + tiles - 1) / tiles));
+        const int slabs_per_slice = (slabs + slices - 1) / slices;
+        k_per_slice = slabs_per_slice * tb200::kGenK;
+        grid.z = static_cast<unsigned>((slabs + slabs_per_slice - 1) / slabs_per_slice);
+        if (grid.z > 1) TB_CUDA(cudaMemset2DAsync(dC, static_cast<size_t>(ldc) * 4, 0, static_cast<size_t>(N) * 4, M, st));
+    }
+    tb200::ternary_generic_kernel<<<grid, tb200::kGenThreads, 0, st>>>(dA, dW, dC, M, K, N, ldc, k_per_slice);
     TB_CUDA(cudaGetLastError());
     return TERNIX_B200_OK;
 }
