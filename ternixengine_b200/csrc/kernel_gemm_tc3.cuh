@@ -52,15 +52,36 @@ constexpr int kTc3TileA = 256;                    // activation rows per pair (1
 #ifndef TB200_TC3_BK
 #define TB200_TC3_BK 256
 #endif
-constexpr int kTc3BK = TB200_TC3_BK;              // K-bytes per stage: 128 or 256 (the latter as two 128-byte-swizzle boxes)
-constexpr int kTc3ActBytes = 128 * kTc3BK;
-constexpr int kTc3WpRowBytes = 32;
-constexpr int kTc3WpBytes = kTc3BK * kTc3WpRowBytes;
-constexpr int kTc3StageBytes = kTc3ActBytes + kTc3WpBytes;   // 20480
-constexpr uint32_t kTc3AccCols = 256, kTc3ARingCol = 256, kTc3AStageCols = kTc3BK / 4;
 #ifndef TB200_TC3_EXPAND_WARPS
 #define TB200_TC3_EXPAND_WARPS 8
 #endif
+#define TB200_TC3_EXPAND_WARPS_ TB200_TC3_EXPAND_WARPS
+constexpr int kTc3BK = TB200_TC3_BK;              // K-bytes per stage: 128 or 256 (the latter as two 128-byte-swizzle boxes)
+static_assert(kTc3BK == 256, "a stage is two boxes of 128 K-bytes");
+constexpr int kTc3WpRowBytes = 32;
+constexpr int kTc3WpBytes = kTc3BK * kTc3WpRowBytes;
+constexpr uint32_t kTc3ARingCol = 256, kTc3AStageCols = kTc3BK / 4;
+// Per tile form (TA = activation rows per pair instruction): the shared-memory ring of TMA stages, the accumulator
+// buffers in tensor memory, and the sizes that follow.  The operand ring in tensor memory always has kTc3Stages slots.
+template <int TA>
+struct Tc3Geom {
+    static_assert(TA == 128 || TA == 256, "activation rows per pair instruction");
+    static constexpr int kRowsPerCta = TA / 2;                   // activation rows a CTA loads per stage
+    static constexpr int kActBox = kRowsPerCta * 128;            // one TMA box: rows x 128 K-bytes, 128-byte swizzle
+    static constexpr int kActBytes = 2 * kActBox;
+    static constexpr int kStageBytes = kActBytes + kTc3WpBytes;
+    static constexpr int kAccBufs = 256 / TA;                    // accumulators of TA columns in tensor-memory columns 0-255
+#ifdef TB200_TC3_SMEM_STAGES_128
+    static constexpr int kSmemStages = TA == 128 ? TB200_TC3_SMEM_STAGES_128 : kTc3Stages;
+#else
+    static constexpr int kSmemStages = TA == 128 ? 6 : kTc3Stages;
+#endif
+    // an expander warp meets every phase of the barriers it waits on, and the stage whose retirement frees its operand
+    // slot (kTc3Stages back) belongs to a shared-memory slot that only this same warp's next stages can complete again
+    static_assert(kSmemStages >= kTc3Stages && kSmemStages % (TB200_TC3_EXPAND_WARPS_ / 4) == 0 &&
+                      (kSmemStages - kTc3Stages) % (TB200_TC3_EXPAND_WARPS_ / 4) == 0,
+                  "ring sizes");
+};
 #ifndef TB200_TC3_SLEEP_NS
 #define TB200_TC3_SLEEP_NS 64
 #endif
@@ -103,11 +124,13 @@ __device__ __forceinline__ void warpgroup_regs_acquire() {
 #endif
 constexpr int kTc3EpiBufs = TB200_TC3_EPI_BUFS;   // staging buffers per epilogue group
 constexpr int kTc3EpiBytes = 32 * 128 * 4;        // one step of the epilogue: 32 activation rows x 128 weight columns
-constexpr size_t kTc3SmemBytes = 1024 + size_t(kTc3Stages) * kTc3StageBytes +
-                                 size_t(kTc3EpiGroups) * kTc3EpiBufs * kTc3EpiBytes + 512;
-// M = 256 (pair), N = 256, int8 x int8 -> int32, both operands K-major
-constexpr uint32_t kTc3Idesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(256 >> 3) << 17) |
-                               (static_cast<uint32_t>(256 >> 4) << 24);
+template <int TA>
+constexpr size_t tc3_smem_bytes() {
+    return 1024 + size_t(Tc3Geom<TA>::kSmemStages) * Tc3Geom<TA>::kStageBytes +
+           size_t(kTc3EpiGroups) * kTc3EpiBufs * kTc3EpiBytes + 512;
+}
+static_assert(tc3_smem_bytes<128>() <= 227 * 1024 && tc3_smem_bytes<256>() <= 227 * 1024, "shared memory: 227 KB per CTA");
+constexpr size_t kTc3SmemBytes = tc3_smem_bytes<256>();
 
 __device__ __forceinline__ void tc_mma_i8_pair_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
                                                       uint32_t accumulate) {
@@ -127,16 +150,19 @@ __device__ __forceinline__ void tmem_st_16x128_x2(uint32_t taddr, uint32_t r0, u
                  : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void ldmatrix_x2_trans_b8_tc3(uint32_t (&r)[4], uint32_t smem_addr) {
+// ldmatrix without a memory clobber: the loads of a stage are issued back to back and only ordered by their uses
+// (the stage's shared memory is stable between the barrier wait before and the barrier arrive after them).
+__device__ __forceinline__ void ldmatrix_x2_trans_b8_nc(uint32_t (&r)[4], uint32_t smem_addr) {
     asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(smem_addr)
-                 : "memory");
+                 : "r"(smem_addr));
 }
-// Field `shift / 2` of every byte of T as int8: codes 0, 1, 3 -> 0, +1, -1.
-__device__ __forceinline__ uint32_t decode_field_s8(uint32_t T, uint32_t shift) {
-    const uint32_t x = (T >> shift) & 0x03030303u;
-    return (x & 0x02020202u) * 126u + x;          // 3 -> 3 + 252 = 0xFF; no carry between bytes
+// Field F of every byte of T as int8 scaled by 64: codes 0, 1, 3 -> 0, +64, -64 (the two top bits of a byte ARE the
+// sign-extended code once the field has been shifted there).
+template <int F>
+__device__ __forceinline__ uint32_t decode_field_x64(uint32_t T) {
+    if constexpr (F == 3) return T & 0xC0C0C0C0u;
+    else return (T << (6 - 2 * F)) & 0xC0C0C0C0u;
 }
 
 // Where the finished tiles go: the local C first, then the same place in each peer's C (fused gather over NVLink:
@@ -175,6 +201,20 @@ struct Tc3Walk {
     const Tc2Tile* tiles;
     int idx, end;
 
+    // (grouped) ask the TMA unit to fetch the operand descriptors of the tile that next() will return
+    __device__ __forceinline__ void prefetch_next_maps() const {
+        if (idx < end) {
+            const Tc3Problem* p = probs + tiles[idx].problem;
+            tma_prefetch_desc(&p->tmap_a);
+            tma_prefetch_desc(&p->tmap_w);
+        }
+    }
+    __device__ __forceinline__ void prefetch_next_store_map() const {
+        if (idx < end) {
+            const Tc3Problem* p = probs + tiles[idx].problem;
+            if (p->stores.count > 0) tma_prefetch_desc(&p->stores.tmap_c[0]);
+        }
+    }
     __device__ __forceinline__ bool next() {
         if constexpr (kGrouped) {
             if (idx >= end) return false;
@@ -202,9 +242,10 @@ __device__ __forceinline__ void sts_u16(uint32_t saddr, uint16_t v) {
 // kBf16: the epilogue emits bfloat16 = bf16_rn((float(c) * row_scale[m]) * w_scale) instead of int32 (the scaling
 // step that follows the product in a BitNet-style layer); `stores` then describes bfloat16 tensors and `C`, `ldc`
 // are the bfloat16 output and its pitch in elements.
-// TA: activation rows per pair instruction (the MMA's N).  256 is the full-rate form; 128 serves products with at
-// most 128 rows, which the 256-row tile would pad to twice their work: each CTA then loads 64 rows per stage into
-// the same stage layout and the pair's MMAs are half as long.
+// TA: activation rows per pair instruction (the MMA's N), 256 or 128.  With 128 each CTA loads 64 rows per stage, the
+// pair's MMAs are half as long, and tensor-memory columns 0-255 hold TWO accumulators: the MMAs of the next tile run
+// while the epilogue warps empty the previous one.  The shared-memory ring is then deeper than the operand ring in
+// tensor memory (a stage passes in half the time, the latency of a TMA load stays what it is).
 template <bool kGrouped, bool kBf16 = false, int TA = kTc3TileA>
 __global__ void __launch_bounds__(kTc3Threads, 1)
 ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
@@ -213,24 +254,27 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         const int* __restrict__ pair_first, int32_t* __restrict__ status,
                         const float* __restrict__ row_scale = nullptr, float w_scale = 1.0f) {
     static_assert(!(kGrouped && kBf16), "the dequantising epilogue is built for single products");
-    static_assert(TA == 256 || (TA == 128 && !kGrouped && !kBf16), "the 128-row form is built for single int32 products");
-    constexpr int kRowsPerCta = TA / 2;                                    // activation rows a CTA loads per stage
-    constexpr uint32_t kStageTx = kRowsPerCta * kTc3BK + kTc3WpBytes;      // bytes a stage's TMA loads deliver
+    using G = Tc3Geom<TA>;
+    constexpr int kRowsPerCta = G::kRowsPerCta;                            // activation rows a CTA loads per stage
+    constexpr uint32_t kStageTx = G::kStageBytes;                          // bytes a stage's TMA loads deliver
+    constexpr int S = G::kSmemStages;                                      // ring of TMA stages in shared memory
+    constexpr int TS = kTc3Stages;                                         // ring of operand stages in tensor memory
+    constexpr int BUFS = G::kAccBufs;
     constexpr int kSteps = TA / 32 / kTc3EpiGroups;                        // accumulator steps of 32 rows per epilogue warp
     constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(TA >> 3) << 17) |
                                 (static_cast<uint32_t>(256 >> 4) << 24);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sAct = base;                                            // [stages][128 rows][128 k]  128-byte swizzle
-    uint8_t* sWp = sAct + kTc3Stages * kTc3ActBytes;                 // [stages][128 k][32]        32-byte swizzle
-    uint8_t* sEpi = sWp + kTc3Stages * kTc3WpBytes;                  // [groups][bufs][32 rows][128] int32
+    uint8_t* sAct = base;                                            // [S][2 boxes][rows][128 k]  128-byte swizzle
+    uint8_t* sWp = sAct + S * G::kActBytes;                          // [S][256 k][32]             32-byte swizzle
+    uint8_t* sEpi = sWp + S * kTc3WpBytes;                           // [groups][bufs][32 rows][128] int32
     uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + kTc3EpiGroups * kTc3EpiBufs * kTc3EpiBytes);
-    uint64_t* full = bars;                         // this CTA's TMA bytes of a stage have landed
-    uint64_t* empty = full + kTc3Stages;           // the pair's MMAs on a stage have retired
-    uint64_t* ready = empty + kTc3Stages;          // (leader) both CTAs' operands of a stage are in place
-    uint64_t* acc_full = ready + kTc3Stages;       // [1]
-    uint64_t* acc_empty = acc_full + 1;            // [1] (leader)
-    uint64_t* drain = acc_empty + 1;
+    uint64_t* full = bars;                         // [S]  this CTA's TMA bytes of a stage have landed
+    uint64_t* empty = full + S;                    // [S]  the pair's MMAs on a stage have retired
+    uint64_t* ready = empty + S;                   // [TS] (leader) both CTAs' operands of a stage are in place
+    uint64_t* acc_full = ready + TS;               // [BUFS]
+    uint64_t* acc_empty = acc_full + BUFS;         // [BUFS] (leader)
+    uint64_t* drain = acc_empty + BUFS;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -254,13 +298,15 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         return w;
     };
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kTc3Stages; ++s) {
+        for (int s = 0; s < S; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
-            mbar_init(&ready[s], 2 * 4);
         }
-        mbar_init(acc_full, 1);
-        mbar_init(acc_empty, 8 * kTc3EpiGroups);
+        for (int s = 0; s < TS; ++s) mbar_init(&ready[s], 2 * 4);
+        for (int b = 0; b < BUFS; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 8 * kTc3EpiGroups);
+        }
         mbar_init(drain, 1);
         *abort_flag = 0;
         mbar_init_fence();
@@ -280,29 +326,34 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       if (warp == 0) {
         // ================================================================ TMA producer
         if (lane == 0) {
-            if constexpr (!kGrouped) {
-                tma_prefetch_desc(&tmap_a);
-                tma_prefetch_desc(&tmap_w);
-            }
             uint32_t it = 0;
             bool ok = true;
             Tc3Walk<kGrouped> w = make_walk();
+            if constexpr (!kGrouped) {
+                tma_prefetch_desc(&tmap_a);
+                tma_prefetch_desc(&tmap_w);
+            } else {
+                w.prefetch_next_maps();
+            }
             while (ok && w.next()) {
+                // the descriptors of the tile after this one: fetched while this tile's loads are issued, so that a
+                // change of problem does not stall the ring for the latency of two descriptor reads
+                if constexpr (kGrouped) w.prefetch_next_maps();
                 const int row0 = w.a_t * TA + rank * kRowsPerCta;
                 const int wp_x = (w.w_t * kTc3TileW + rank * 128) / 4;
                 for (int kb = 0; kb < w.k_blocks; ++kb, ++it) {
-                    const uint32_t s = it % kTc3Stages;
-                    if (!mbar_wait_backoff(&empty[s], ((it / kTc3Stages) & 1) ^ 1, abort_flag, 32)) { ok = false; break; }
+                    const uint32_t s = it % S;
+                    if (!mbar_wait_backoff(&empty[s], ((it / S) & 1) ^ 1, abort_flag, 32)) { ok = false; break; }
                     mbar_arrive_expect_tx(&full[s], kStageTx);
 #pragma unroll
-                    for (int j = 0; j < kTc3BK / 128; ++j)
-                        tma_load_2d(sAct + s * kTc3ActBytes + j * 16384, w.ta, kb * kTc3BK + j * 128, row0, &full[s]);
+                    for (int j = 0; j < 2; ++j)
+                        tma_load_2d(sAct + s * G::kActBytes + j * G::kActBox, w.ta, kb * kTc3BK + j * 128, row0, &full[s]);
                     tma_load_2d(sWp + s * kTc3WpBytes, w.tw, wp_x, kb * kTc3BK, &full[s]);
                 }
             }
             if (!ok) {
-                const uint32_t first = it > kTc3Stages ? it - kTc3Stages : 0;
-                for (uint32_t j = first; j < it; ++j) mbar_drain(&full[j % kTc3Stages], (j / kTc3Stages) & 1);
+                const uint32_t first = it > static_cast<uint32_t>(S) ? it - S : 0;
+                for (uint32_t j = first; j < it; ++j) mbar_drain(&full[j % S], (j / S) & 1);
             }
         }
       } else if (warp == 1) {
@@ -312,22 +363,24 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             bool ok = true;
             Tc3Walk<kGrouped> w = make_walk();
             for (; ok && w.next(); ++lt) {
-                if (!mbar_wait(acc_empty, (lt & 1) ^ 1, abort_flag)) { ok = false; break; }
+                const uint32_t ab = lt % BUFS;
+                if (!mbar_wait(&acc_empty[ab], ((lt / BUFS) & 1) ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
+                const uint32_t acc = tmem_base + ab * TA;
                 for (int kb = 0; kb < w.k_blocks; ++kb, ++it) {
-                    const uint32_t s = it % kTc3Stages;
-                    if (!mbar_wait(&ready[s], (it / kTc3Stages) & 1, abort_flag)) { ok = false; break; }
+                    const uint32_t s = it % S, ts = it % TS;
+                    if (!mbar_wait(&ready[ts], (it / TS) & 1, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t act_addr = smem_u32(sAct + s * kTc3ActBytes);
-                    const uint32_t a_col = tmem_base + kTc3ARingCol + s * kTc3AStageCols;
+                    const uint32_t act_addr = smem_u32(sAct + s * G::kActBytes);
+                    const uint32_t a_col = tmem_base + kTc3ARingCol + ts * kTc3AStageCols;
 #pragma unroll
                     for (int g = 0; g < kTc3BK / 32; ++g) {
-                        const uint64_t db = umma_desc_sw128(act_addr + (g >> 2) * 16384 + (g & 3) * 32, 16, 1024);
-                        tc_mma_i8_pair_tmem_a(tmem_base, a_col + 8 * g, db, kIdesc, (kb != 0 || g != 0) ? 1u : 0u);
+                        const uint64_t db = umma_desc_sw128(act_addr + (g >> 2) * G::kActBox + (g & 3) * 32, 16, 1024);
+                        tc_mma_i8_pair_tmem_a(acc, a_col + 8 * g, db, kIdesc, (kb != 0 || g != 0) ? 1u : 0u);
                     }
                     tc_commit_pair_both(&empty[s]);
                 }
-                if (ok) tc_commit_pair_both(acc_full);
+                if (ok) tc_commit_pair_both(&acc_full[ab]);
             }
             tc_commit_pair(drain);
             mbar_wait(drain, 0, abort_flag);
@@ -336,21 +389,20 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     } else if (warp < kTc3FirstEpilogueWarp) {
         warpgroup_regs_release<kTc3RegsExpand>();
         // ================================================================ expanders: packed bytes -> int8 rows of the A operand
-        // Lane L of the A operand is weight column L of the CTA's 128: byte column L / 4, field L % 4.  The warp of
-        // lane quarter q therefore needs byte columns 8q .. 8q+7 (half of the 16-byte chunk q / 2 of a row) in all
-        // four fields.
+        // The warp of lane quarter q writes operand rows 32q .. 32q+31: packed byte columns 8q .. 8q+7 of a row, i.e.
+        // half (q & 1) of the 16-byte chunk q / 2, in all four fields.
         const uint32_t q = warp & 3;
         const uint32_t slot = (warp - kTc3FirstExpandWarp) >> 2;       // this warp's turn among the warps of its quarter
         // ldmatrix.x2: matrix 0 = k 0-15, matrix 1 = k 16-31 of a 32-deep group, both of chunk q / 2; row (lane & 15),
-        // 32-byte swizzle (address bit 4 ^= address bit 7, i.e. chunk ^= bit 2 of the row)
+        // 32-byte swizzle (address bit 4 ^= address bit 7, i.e. chunk ^= bit 2 of the row).
+        // After the load lane (c, t) = (lane / 4, lane % 4) holds k-bytes 4t..4t+3 of byte column 8q + c (register q & 1
+        // of each matrix) -- exactly what lane (c, t) has to supply to tcgen05.st.16x128b for operand row c, columns t.
+        // So the operand rows are numbered the way the load delivers them: lane l of the quarter holds byte column
+        // l % 8 in field l / 8, i.e. weight column 4 (l % 8) + l / 8 of the quarter's 32, and no data moves between
+        // lanes.  The epilogue undoes the numbering when it writes the staging buffer.
         const uint32_t r_in = lane & 15;
         const uint32_t ld_off = (lane >> 4) * 512 + r_in * 32 + (((q >> 1) ^ ((r_in >> 2) & 1)) << 4);
-        // After the load lane (c, t) = (lane / 4, lane % 4) holds k-bytes 4t..4t+3 of byte column 8q + c (register q & 1
-        // of each matrix).  The store wants, in lane (g, t), rows g and g + 8 of a 16-lane group, i.e. byte columns
-        // g / 4 (+2, +4, +6) in field g % 4: four shuffles per matrix bring them over.
-        const int t4 = lane & 3, g4 = lane >> 4;
-        const int src0 = (g4 + 0) * 4 + t4, src1 = (g4 + 2) * 4 + t4, src2 = (g4 + 4) * 4 + t4, src3 = (g4 + 6) * 4 + t4;
-        const uint32_t shift = 2 * ((lane >> 2) & 3);
+        const bool odd = (q & 1) != 0;
         const uint32_t wp_sa = smem_u32(sWp);
         const uint32_t t_lane = (q * 32) << 16;
         uint32_t it = 0;
@@ -359,30 +411,41 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         while (ok && w.next()) {
             for (int kb = 0; kb < w.k_blocks; ++kb, ++it) {
                 if (it % kTc3WarpsPerQuarter != slot) continue;
-                const uint32_t s = it % kTc3Stages;
-                if (!mbar_wait_backoff(&full[s], (it / kTc3Stages) & 1, abort_flag, TB200_TC3_SLEEP_NS)) { ok = false; break; }
-                const uint32_t wp = wp_sa + s * kTc3WpBytes;
-                const uint32_t a_col = tmem_base + kTc3ARingCol + s * kTc3AStageCols;
+                const uint32_t s = it % S, ts = it % TS;
+                if (!mbar_wait_backoff(&full[s], (it / S) & 1, abort_flag, TB200_TC3_SLEEP_NS)) { ok = false; break; }
+                const uint32_t wp = wp_sa + s * kTc3WpBytes + ld_off;
+                uint32_t X[kTc3BK / 32], Y[kTc3BK / 32];
 #pragma unroll
                 for (int g = 0; g < kTc3BK / 32; ++g) {
                     uint32_t m[4];
-                    ldmatrix_x2_trans_b8_tc3(m, wp + g * 1024 + ld_off);
-                    const uint32_t X = (q & 1) ? m[1] : m[0], Y = (q & 1) ? m[3] : m[2];
-                    const uint32_t x0 = __shfl_sync(0xffffffffu, X, src0), x1 = __shfl_sync(0xffffffffu, X, src1);
-                    const uint32_t x2 = __shfl_sync(0xffffffffu, X, src2), x3 = __shfl_sync(0xffffffffu, X, src3);
-                    const uint32_t y0 = __shfl_sync(0xffffffffu, Y, src0), y1 = __shfl_sync(0xffffffffu, Y, src1);
-                    const uint32_t y2 = __shfl_sync(0xffffffffu, Y, src2), y3 = __shfl_sync(0xffffffffu, Y, src3);
-                    tmem_st_16x128_x2(a_col + t_lane + 8 * g, decode_field_s8(x0, shift), decode_field_s8(x1, shift),
-                                      decode_field_s8(y0, shift), decode_field_s8(y1, shift));
-                    tmem_st_16x128_x2(a_col + t_lane + (16u << 16) + 8 * g, decode_field_s8(x2, shift),
-                                      decode_field_s8(x3, shift), decode_field_s8(y2, shift), decode_field_s8(y3, shift));
+                    ldmatrix_x2_trans_b8_nc(m, wp + g * 1024);
+                    X[g] = odd ? m[1] : m[0];
+                    Y[g] = odd ? m[3] : m[2];
+                }
+                if constexpr (S != TS) {
+                    // The operand slot in tensor memory is free once the MMAs of stage it - TS have retired, which is what
+                    // the `empty` barrier of that stage's shared-memory slot says.  (That barrier cannot be a phase ahead:
+                    // its next completion needs stage it - TS + S > it expanded, and this warp expands in order.)
+                    if (it >= static_cast<uint32_t>(TS)) {
+                        const uint32_t j = it - TS;
+                        if (!mbar_wait_backoff(&empty[j % S], (j / S) & 1, abort_flag, 32)) { ok = false; break; }
+                    }
+                    tc_fence_after_sync();
+                }
+                const uint32_t a_col = tmem_base + kTc3ARingCol + ts * kTc3AStageCols + t_lane;
+#pragma unroll
+                for (int g = 0; g < kTc3BK / 32; ++g) {
+                    tmem_st_16x128_x2(a_col + 8 * g, decode_field_x64<0>(X[g]), decode_field_x64<1>(X[g]),
+                                      decode_field_x64<0>(Y[g]), decode_field_x64<1>(Y[g]));
+                    tmem_st_16x128_x2(a_col + (16u << 16) + 8 * g, decode_field_x64<2>(X[g]), decode_field_x64<3>(X[g]),
+                                      decode_field_x64<2>(Y[g]), decode_field_x64<3>(Y[g]));
                 }
                 tmem_st_wait();
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) {
-                    if (leader) mbar_arrive(&ready[s]);
-                    else mbar_arrive_remote(&ready[s], 0);
+                    if (leader) mbar_arrive(&ready[ts]);
+                    else mbar_arrive_remote(&ready[ts], 0);
                 }
             }
         }
@@ -394,33 +457,42 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         // per row: no bank conflicts), and one thread hands the buffer to the TMA unit (cp.async.bulk.tensor store).
         // The accumulator is released as soon as it has been read: the stores to global memory, whose rate per SM is
         // what an epilogue out of registers waits for, run in the background under the next tile's MMAs.
+        // Lane l of quarter q holds weight column 32q + 4 (l % 8) + l / 8 (the expanders' numbering), and 64 x the sum.
         const uint32_t q = warp & 3;
+        const uint32_t colp = q * 32 + 4 * (lane & 7) + (lane >> 3);
         const int eg = (warp - kTc3FirstEpilogueWarp) >> 2;             // group: takes steps eg, eg + groups, ...
         const bool elected = ((warp - kTc3FirstEpilogueWarp) & 3) == 0 && lane == 0;
         const uint32_t epi_sa = smem_u32(sEpi);
         uint32_t lt = 0, step = 0;                                      // step: steps taken by this group so far
         bool ok = true;
         Tc3Walk<kGrouped> w = make_walk();
+        if constexpr (kGrouped) {
+            if (elected) w.prefetch_next_store_map();
+        }
         for (; ok && w.next(); ++lt) {
+            if constexpr (kGrouped) {
+                if (elected) w.prefetch_next_store_map();
+            }
             const int a_t = w.a_t;
             const Tc3Stores* dst = w.st;
             const int M = w.M, N = w.N;
             const long long ldc = w.ldc;
             int32_t* C = w.C;
-            if (!mbar_wait_backoff(acc_full, lt & 1, abort_flag, TB200_TC3_ACC_SLEEP_NS)) { ok = false; break; }
+            const uint32_t ab = lt % BUFS;
+            if (!mbar_wait_backoff(&acc_full[ab], (lt / BUFS) & 1, abort_flag, TB200_TC3_ACC_SLEEP_NS)) { ok = false; break; }
             tc_fence_after_sync();
             const int col0 = w.w_t * kTc3TileW + rank * 128;
             // this warp's share of the accumulator into registers, all of it, and tensor memory is free again
             uint32_t r[kSteps][32];
 #pragma unroll
             for (int i = 0; i < kSteps; ++i)
-                tmem_ld_32x32(tmem_base + ((q * 32) << 16) + 32 * (eg + kTc3EpiGroups * i), r[i]);
+                tmem_ld_32x32(tmem_base + ((q * 32) << 16) + ab * TA + 32 * (eg + kTc3EpiGroups * i), r[i]);
             tmem_ld_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
-                if (leader) mbar_arrive(acc_empty);
-                else mbar_arrive_remote(acc_empty, 0);
+                if (leader) mbar_arrive(&acc_empty[ab]);
+                else mbar_arrive_remote(&acc_empty[ab], 0);
             }
 #pragma unroll
             for (int i = 0; i < kSteps; ++i, ++step) {
@@ -435,17 +507,18 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const float rs = row0 + j < M ? __ldg(row_scale + row0 + j) : 0.0f;
-                        const __nv_bfloat16 y = __float2bfloat16_rn((static_cast<float>(static_cast<int32_t>(r[i][j])) * rs) * w_scale);
+                        const __nv_bfloat16 y = __float2bfloat16_rn((static_cast<float>(static_cast<int32_t>(r[i][j]) >> 6) * rs) * w_scale);
                         r[i][j] = static_cast<uint32_t>(__bfloat16_as_ushort(y));
                     }
                 }
                 if (dst->count > 0) {
                     if constexpr (kBf16) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) sts_u16(buf + ((j * 128 + q * 32 + lane) << 1), static_cast<uint16_t>(r[i][j]));
+                        for (int j = 0; j < 32; ++j) sts_u16(buf + ((j * 128 + colp) << 1), static_cast<uint16_t>(r[i][j]));
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) sts_u32(buf + ((j * 128 + q * 32 + lane) << 2), r[i][j]);
+                        for (int j = 0; j < 32; ++j)
+                            sts_u32(buf + ((j * 128 + colp) << 2), static_cast<uint32_t>(static_cast<int32_t>(r[i][j]) >> 6));
                     }
                     fence_proxy_async_smem();
                     asm volatile("bar.sync %0, 128;" ::"r"(2 + eg) : "memory");
@@ -465,7 +538,7 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     }
                 } else {
                     // C cannot be described to the TMA unit (pitch or base not 16-byte aligned): 128-byte row pieces
-                    const int col = col0 + q * 32 + lane;
+                    const int col = col0 + static_cast<int>(colp);
                     if (col < N) {
                         if constexpr (kBf16) {
                             uint16_t* out = reinterpret_cast<uint16_t*>(C) + static_cast<size_t>(row0) * ldc + col;
@@ -476,7 +549,7 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                             int32_t* out = C + static_cast<size_t>(row0) * ldc + col;
 #pragma unroll
                             for (int j = 0; j < 32; ++j)
-                                if (row0 + j < M) out[static_cast<size_t>(j) * ldc] = static_cast<int32_t>(r[i][j]);
+                                if (row0 + j < M) out[static_cast<size_t>(j) * ldc] = static_cast<int32_t>(r[i][j]) >> 6;
                         }
                     }
                 }

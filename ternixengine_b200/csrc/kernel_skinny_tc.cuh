@@ -133,19 +133,6 @@ __device__ __forceinline__ void tmem_st_16x128_x8(uint32_t taddr, const uint32_t
         "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
-// ldmatrix without a memory clobber: the loads of a stage are issued back to back and only ordered by their uses
-// (the stage's shared memory is stable between the barrier wait before and the barrier arrive after them).
-__device__ __forceinline__ void ldmatrix_x2_trans_b8_nc(uint32_t (&r)[4], uint32_t smem_addr) {
-    asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(smem_addr));
-}
-// Field f of every byte of T as int8 scaled by 64: codes 0, 1, 3 -> 0, +64, -64.
-template <int F>
-__device__ __forceinline__ uint32_t decode_field_x64(uint32_t T) {
-    if constexpr (F == 3) return T & 0xC0C0C0C0u;
-    else return (T << (6 - 2 * F)) & 0xC0C0C0C0u;
-}
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
     int v;
     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");

@@ -151,6 +151,7 @@ int ensure_smem_attr(size_t bytes) {
 // (TERNIX_B200_<NAME>) when the library is first used and changed afterwards only through ternix_b200_set_option;
 // the launch path reads plain fields.
 struct Options {
+    int tc_tile_rows = 0;              // activation rows per pair instruction of the tensor-memory GEMM: 0 = by shape, 128, 256
     int tc3 = 1;                       // 0: the kernels that expand weights into shared memory instead of tensor memory
     int tc_bn = 0;                     // 128 | 256: single-CTA tiles of that width; 2: paired CTAs; 0: by shape
     int tc_ksplit = 1;                 // 0: no K split in the single-CTA kernel
@@ -174,6 +175,7 @@ int apply_option(const char* name, const char* value) {
     const bool reset = !value || !*value;
     auto num = [&](int d) { return reset ? d : std::atoi(value); };
     if (!std::strcmp(name, "tc3")) g_opt.tc3 = num(def.tc3);
+    else if (!std::strcmp(name, "tc_tile_rows")) g_opt.tc_tile_rows = num(def.tc_tile_rows);
     else if (!std::strcmp(name, "tc_bn")) g_opt.tc_bn = num(def.tc_bn);
     else if (!std::strcmp(name, "tc_ksplit")) g_opt.tc_ksplit = num(def.tc_ksplit);
     else if (!std::strcmp(name, "group_words")) g_opt.group_words = num(def.group_words);
@@ -207,7 +209,7 @@ int apply_option(const char* name, const char* value) {
 const Options& options() {
     static std::once_flag once;
     std::call_once(once, [] {
-        static const char* const names[] = {"tc3", "tc_bn", "tc_ksplit", "gemv_plan", "group_words", "gemv_pdl", "mma_rows", "mma_slices",
+        static const char* const names[] = {"tc3", "tc_tile_rows", "tc_bn", "tc_ksplit", "gemv_plan", "group_words", "gemv_pdl", "mma_rows", "mma_slices",
                                             "mma_cluster", "skinny_rows", "skinny_group_rows", "skinny_split", "host_slab"};
         std::lock_guard<std::mutex> lock(g_opt_mutex);
         for (const char* n : names) {
@@ -579,7 +581,11 @@ int launch_gemm_tc2_expand(const int8_t* dA, const uint8_t* dW, int32_t* const* 
 // Paired CTAs with the weights as the A operand in tensor memory (kernel_gemm_tc3.cuh).  Several destinations need
 // every C to be describable to the TMA unit (16-byte aligned base and pitch); ERR_UNSUPPORTED otherwise.
 // Activation rows per pair instruction: the 128-row form for products that have no more rows than that.
-int tc3_tile_rows(int M) { return M <= 128 ? 128 : 256; }
+int tc3_tile_rows(int M) {
+    const int forced = options().tc_tile_rows;
+    if (forced == 128 || forced == 256) return forced;
+    return M <= 128 ? 128 : 256;
+}
 
 int make_tc3_act_map(CUtensorMap* out, const int8_t* dA, int M, int K, int tile_rows = 256) {
     return make_tmap_2d(out, dA, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), tb200::kTcBK,
@@ -596,14 +602,14 @@ int make_tc3_store_map(CUtensorMap* out, int32_t* dC, int M, int N, long long ld
 template <int TA>
 int launch_gemm_tc3_maps_t(const CUtensorMap& tmap_a, const CUtensorMap& tmap_w, const tb200::Tc3Stores& stores, int32_t* dC0,
                            int M, int K, int N, long long ldc, int32_t* d_status, cudaStream_t st) {
-    if (const int arc = ensure_smem_attr<tb200::ternary_gemm_tc3_kernel<false, false, TA>>(tb200::kTc3SmemBytes)) return arc;
+    if (const int arc = ensure_smem_attr<tb200::ternary_gemm_tc3_kernel<false, false, TA>>(tb200::tc3_smem_bytes<TA>())) return arc;
     const long tiles = static_cast<long>((M + TA - 1) / TA) * ((N + tb200::kTc3TileW - 1) / tb200::kTc3TileW);
     const long max_pairs = sm_count() / 2;
     const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     cfg.blockDim = dim3(tb200::kTc3Threads, 1, 1);
-    cfg.dynamicSmemBytes = tb200::kTc3SmemBytes;
+    cfg.dynamicSmemBytes = tb200::tc3_smem_bytes<TA>();
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
