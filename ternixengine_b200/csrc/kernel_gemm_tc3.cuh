@@ -10,31 +10,46 @@
 //   * activations: 128 rows x 256 K-bytes per CTA and stage (two boxes of 128 K-bytes), straight from TMA into the
 //     K-major 128-byte-swizzle layout the B descriptor reads (the pair's two halves make the N = 256 columns of the instruction);
 //   * weights: 256 k-rows x 32 packed bytes per CTA and stage (its 128 weight columns), TMA with the 32-byte
-//     swizzle.  An expander warp reads them with ldmatrix.m16n16.x2.trans.b8, which leaves four consecutive K-bytes
-//     of one byte column in one register.  Lane L of the operand is weight column L of the CTA's 128, i.e. byte
-//     column L / 4, field L % 4, so the warp of lane quarter q needs byte columns 8q .. 8q+7 in all four fields:
-//     eight shuffles per 32-deep group bring each lane the registers of its rows, one variable shift and three ALU
-//     operations decode its field (2-bit code -> int8 -1/0/+1), and tcgen05.st.16x128b writes them to tensor
-//     memory.  Nothing expanded ever touches shared memory: per CTA and 128-deep k-block the expanders execute a
-//     few hundred instructions in all, and the ring holds 40 KB per 256-deep stage instead of 112 KB.
-//   * epilogue: lane = weight column, tensor-memory column = activation row.  A step moves 32 activation rows x
-//     128 columns into a staging buffer in shared memory, row-major as in C (a warp writes 128 contiguous bytes per
-//     row), and one thread hands the buffer to the TMA unit as a tensor store.  The accumulator is released as soon
-//     as it has been read; the stores to global memory, whose rate per SM (about 30 GB/s) is what an epilogue out
-//     of registers has to wait for, run in the background under the next tile's MMAs.
+//     swizzle.  An expander warp reads them with ldmatrix.m16n16.x2.trans.b8, which leaves, in lane (c, t) =
+//     (lane / 4, lane % 4), the bytes of k-rows 4t..4t+3 of packed byte column c -- exactly what lane (c, t) has to
+//     supply to tcgen05.st.16x128b for operand row c, columns t.  So the operand rows (tensor-memory lanes) are
+//     numbered the way the load delivers them: lane l of a 32-lane quarter holds weight column 4 (l % 8) + l / 8 of
+//     the quarter's 32, and no data moves between lanes.  A field is decoded without sign extension:
+//     (T << (6 - 2f)) & 0xC0C0C0C0 leaves every byte as 0x00, 0x40 or 0xC0, i.e. 0, +64, -64 as int8; the
+//     accumulators hold 64 x the sum and the epilogue's arithmetic shift by 6 is exact.  17 instructions per 1024
+//     weights and warp (the first version, which kept the natural row order, needed eight shuffles and 45
+//     instructions, and the tensor pipe waited for the expanders 11 % of the time).  Nothing expanded ever touches
+//     shared memory; the ring holds 40 KB per 256-deep stage instead of 112 KB.
+//   * epilogue: lane = weight column (in the expanders' numbering), tensor-memory column = activation row.  The
+//     epilogue warps read their whole share of the accumulator into registers and release it at once (about 700
+//     cycles from the last MMA's retirement to the first MMA of the next tile).  A step then moves 32 activation
+//     rows x 128 columns into a staging buffer in shared memory, row-major as in C, and one thread hands the buffer
+//     to the TMA unit as a tensor store; the stores run in the background under the next tile's MMAs, a few hundred
+//     nanoseconds apart (see kTc3StorePauseNsPerStage).
 //
 // Tensor memory (512 columns per CTA): columns 0-255 the accumulator (128 weight columns x 256 activation rows,
-// int32, single-buffered), columns 256-511 the A ring: 4 stages x 64 columns (256 K-bytes per lane).
+// int32, single-buffered; two buffers of 128 rows in the 128-row form), columns 256-511 the A ring: 4 stages x 64
+// columns (256 K-bytes per lane).
 // Stages are 256 deep because every hand-over of a stage (TMA -> expanders -> leader -> tensor core -> producer)
-// costs about the same whatever it carries: 128-deep stages ran 10 % slower with the tensor pipe 71 % busy, these 85 %.
+// costs about the same whatever it carries: 128-deep stages ran 10 % slower.  A pair MMA with 128 instead of 256
+// activation rows takes as long as the full one, so the 128-row form (which could double-buffer its accumulator)
+// runs at two thirds of the rate and only serves products with at most 128 rows.
 //
-// Roles per CTA (warps): 0 TMA producer; 1 MMA issuer (leader CTA only: eight M=256 N=256 K=32 pair MMAs per
-// stage, commit -> `empty` of both CTAs); 2-9 expanders (lane quarter = warp % 4; the two warps of a quarter take
-// the stages in turn, so that a warp's chain of load, shuffle, decode, tensor-memory store and its wait spans two
-// stage times; after tcgen05.wait::st they arrive on the leader's `ready`, which therefore also says that this
-// CTA's activation tile has landed); 10-17 epilogue, two groups of four that take alternate steps.
+// Where the time goes (4096 x 8192 x 28672, per-CTA cycle counters): a tile of 32 stages takes 35,900 cycles for
+// 32,768 cycles of MMAs.  About 800 are the hand-over of the single accumulator; most of the rest are stages that
+// wait for their TMA loads in the 5,000 cycles after a tile ends, when every CTA's epilogue stores its 128 KB: the
+// loads' latency doubles meanwhile (with the stores left out the tile takes 34,100 cycles and the SM clock under
+// the power cap is higher as well).  A deeper shared-memory ring, L2 prefetches of the weight boxes, evict-first
+// stores and stores from registers were all measured and change nothing.
 //
-// Exactness: int8 x int8 -> int32 on decoded -1/0/+1 weights, no scaling; any K the tensor maps can describe.
+// Roles per CTA (warps, in whole warpgroups because registers are moved between them): 0 TMA producer; 1 MMA
+// issuer (leader CTA only: eight M=256 N=256 K=32 pair MMAs per stage, commit -> `empty` of both CTAs); 2-3 idle;
+// 4-11 expanders (lane quarter = warp % 4; the two warps of a quarter take the stages in turn; after
+// tcgen05.wait::st they arrive on the leader's `ready`, which therefore also says that this CTA's activation tile
+// has landed); 12-19 epilogue, two groups of four that take alternate steps.
+//
+// Exactness: int8 x int8 -> int32 on weights decoded as -64/0/+64; |64 * sum| <= 64 * 128 * K < 2^31 for
+// K <= 262143 (the host checks), and the shift by 6 in the epilogue restores the sum exactly.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -96,6 +111,7 @@ static_assert(TB200_TC3_STAGES % (TB200_TC3_EXPAND_WARPS / 4) == 0,
 // control (TMA producer, MMA issuer, two idle), then the expanders, then the epilogue.
 constexpr int kTc3FirstExpandWarp = 4;
 constexpr int kTc3FirstEpilogueWarp = kTc3FirstExpandWarp + kTc3ExpandWarps;    // 12
+constexpr unsigned kTc3StorePauseNsPerStage = 40;   // pause between an epilogue group's steps, per k-stage of the tile
 #ifndef TB200_TC3_EPI_GROUPS
 #define TB200_TC3_EPI_GROUPS 2
 #endif
@@ -536,6 +552,9 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         }
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
+                    // Pace the group's stores: issued back to back right after a tile ends (by every CTA of the grid at
+                    // about the same moment) they double the latency of the loads that refill the ring just then.
+                    if (i + 1 < kSteps) __nanosleep(static_cast<unsigned>(w.k_blocks) * kTc3StorePauseNsPerStage);
                 } else {
                     // C cannot be described to the TMA unit (pitch or base not 16-byte aligned): 128-byte row pieces
                     const int col = col0 + static_cast<int>(colp);
