@@ -492,7 +492,7 @@ def gathered_to_row_major(gathered: np.ndarray, N: int, granule: int = 64) -> np
 
 # Rates behind should_shard(), measured on B200: what one GPU sustains on the paired tensor-core GEMM, and what one
 # rank's epilogue stores sustain towards its peers over NVLink (per direction).
-_GEMM_OPS_PER_S = 3.0e15
+_GEMM_OPS_PER_S = 3.5e15
 _PEER_STORE_BYTES_PER_S = 6.0e11
 _GATHER_FIXED_S = 30e-6            # the stream barrier after the stores, the tail of stores behind the last tile
 
@@ -502,7 +502,8 @@ def should_shard(M: int, K: int, N: int, world: int, granule: int = 64, out_byte
     GPU needs the full C.  Sharding divides the compute by `world` but each rank must ship its columns to world - 1
     peers and all ranks meet at a barrier: per step max(compute / world, out_bytes * M * N * (world - 1) / world /
     link) + a fixed cost, against compute.  With int32 outputs that favours sharding only for large products with
-    deep K (K > ~10000 * (world - 1) / world): config 3 (K = 8192) gains at 2 and 4 GPUs, BitNet-2B projections
+    deep K (K > ~12000 * (world - 1) / world): config 3 (K = 8192) gains at 2 GPUs and is even at 4 (measured 0.43
+    and 0.56 ms against 0.53-0.55 ms on one GPU), BitNet-2B projections
     (K = 2560, 6912; microseconds each) never do.  Small or skinny problems stay whole:
     a shard must keep at least one 256-column tile per rank and the problem must be in the tensor-core regime."""
     if not (world > 1 and M > 64 and N // world >= 256 and N % granule == 0):
