@@ -67,7 +67,7 @@ const char *ternix_b200_launched_kernel_name(int launched);
 /* Tuning options.  The defaults are the measured best; tests and experiments force the other paths.  Each option is
  * read once from the environment variable TERNIX_B200_<NAME> when the library is first used and can be changed
  * afterwards only here (value NULL or "" restores the default); do not change options while another thread
- * launches.  Names: tc3 (0|1), tc_bn (0|2|128|256), tc_ksplit (0|1), gemv_plan ("words,ksplit"), group_words
+ * launches.  Names: tc3 (0|1), tc_tile_rows (0|128|256: activation rows per pair instruction of the prefill kernel), tc_bn (0|2|128|256), tc_ksplit (0|1), gemv_plan ("words,ksplit"), group_words
  * (16|32), gemv_pdl (-1|0|1), mma_rows ("lo,hi"), mma_slices, mma_cluster (0|2|4|8), skinny_rows ("lo,hi"), skinny_group_rows ("lo,hi", lo 0 = never), skinny_split (0|1|2),
  * host_slab (<columns>|r<rows>|0).  Unknown name: TERNIX_B200_ERR_INVALID_ARG. */
 int ternix_b200_set_option(const char *name, const char *value);

@@ -148,6 +148,31 @@ def test_gemm_tc_tile_widths_and_ragged_edges(bn, option):
     assert_same(device_matmul(a, wp, "gemm_tc", pad_cols=3), oracle_lib.matmul(a, wp), f"gemm_tc bn={bn} odd pitch")
 
 
+@pytest.mark.parametrize("tile_rows", ["128", "256"])
+def test_prefill_kernel_tile_forms(tile_rows, option):
+    """Both tile forms of the tensor-memory prefill kernel on products of any row count: the 128-row form alternates
+    between two accumulators (several tiles per CTA pair here), the 256-row form pads products with few rows."""
+    option("tc_tile_rows", tile_rows)
+    for (m, k, n) in [(100, 4096, 1024), (129, 272, 1984), (300, 1040, 832), (512, 2560, 2560), (384, 528, 45056)]:
+        a, wp = synth(m, k, n, 7 * m + k + n)
+        assert_same(device_matmul(a, wp, "gemm_tc", pad_cols=4), oracle_lib.matmul(a, wp),
+                    f"gemm_tc tile_rows={tile_rows} {m}x{k}x{n}")
+        assert tb.last_launched_kernel() == "ternary_gemm_tc3_kernel"
+
+
+def test_prefill_kernel_deepest_k():
+    """The largest K the scaled accumulators allow (64 * 128 * K < 2^31) at the worst-case magnitudes."""
+    m, k, n = 256, 262128, 256
+    a = np.full((m, k), -128, dtype=np.int8)
+    wp = np.full((k, n // 4), 0xFF, dtype=np.uint8)
+    assert (device_matmul(a, wp, "gemm_tc") == 128 * k).all()
+    a[:] = 127
+    a[::2, ::2] = -128
+    expect = -a.astype(np.int64).sum(axis=1)
+    got = device_matmul(a, wp, "gemm_tc")
+    assert (got == expect[:, None]).all()
+
+
 @pytest.mark.parametrize("shape", [(1, 3001, 1028), (7, 129, 4), (37, 4099, 2052), (255, 2561, 6916)])
 def test_config4_ragged_and_worst_case(shape):
     m, k, n = shape
