@@ -499,8 +499,8 @@ def run_b200(args):
         "cpu_baseline_one_core": cpu_one,
         "e2e": e2e,
         "e2e_host_call": host_call,
-        "gpu_launches": args.steps,
-        "gpu_launches_note": "one launch of this library's GEMM per timed step and rank (the barrier at N > 1 is NCCL's kernel)",
+        "gpu_launches": args.steps * (2 if world > 1 else 1),
+        "gpu_launches_note": "per timed step and rank: one launch of this library's GEMM and, at N > 1, one of its peer-barrier kernel",
         "clocks": clocks,
     }
     print(json.dumps(line), flush=True)

@@ -56,7 +56,7 @@ EXPORTS = (
     "ternix_b200_gemv_batch_noalloc", "ternix_b200_gemv_batch_noalloc_limits",
     "ternix_b200_quantize_rows", "ternix_b200_matmul_dequant",
     "ternix_b200_matmul_bcast", "ternix_b200_peer_alloc", "ternix_b200_peer_free", "ternix_b200_peer_export",
-    "ternix_b200_peer_import", "ternix_b200_peer_close",
+    "ternix_b200_peer_import", "ternix_b200_peer_close", "ternix_b200_peer_barrier",
     "ternix_b200_shard_columns", "ternix_b200_unpack_gathered",
     "ternix_b200_synth_activations", "ternix_b200_synth_packed_weights", "ternix_b200_synth_weights",
 )
@@ -123,6 +123,7 @@ def _load() -> ctypes.CDLL:
         "ternix_b200_peer_export": (i32, [vp, c.c_char_p]),
         "ternix_b200_peer_import": (i32, [c.c_char_p, c.POINTER(vp)]),
         "ternix_b200_peer_close": (i32, [vp]),
+        "ternix_b200_peer_barrier": (i32, [c.POINTER(vp), i32, i32, c.c_uint, u64, vp, vp]),
         "ternix_b200_shard_columns": (i32, [i32, i32, i32, i32, c.POINTER(i32), c.POINTER(i32)]),
         "ternix_b200_unpack_gathered": (i32, [vp, vp, i32, i32, i64, i32, i32, i32, vp]),
         "ternix_b200_synth_activations": (None, [vp, sz, u64, i32]),
@@ -562,6 +563,61 @@ class _DeviceBuffer:
         self.ptr = None
 
 
+class PeerBarrier:
+    """A barrier between the ranks of a torch.distributed group on the current CUDA stream, made of one small kernel
+    per rank (ternix_b200_peer_barrier): every rank raises a flag in every peer's memory and waits for theirs.  When
+    it has passed on a rank, every rank's kernels enqueued before its own call have finished and their stores into
+    this rank's memory are visible.  Collective: construct it and call it on every rank, equally often.
+    A peer that does not arrive within the library's wait limit sets the timeout code in `status`."""
+
+    def __init__(self, group=None, device=None):
+        import torch
+        import torch.distributed as dist
+
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.epoch = 0
+        self._own = None
+        self._arrays = None
+        if self.world == 1:
+            return
+        with torch.cuda.device(self.device):
+            self._own = _DeviceBuffer(256)
+            flags = self._own.as_tensor((64,), torch.int32, self.device)
+            flags.zero_()
+            torch.cuda.synchronize(self.device)       # zeroed before any peer can learn the handle
+            handles = [None] * self.world
+            dist.all_gather_object(handles, self._own.export(), group=group)
+            ptrs = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    ptrs.append(self._own.ptr)
+                else:
+                    p = ctypes.c_void_p()
+                    _check(lib.ternix_b200_peer_import(h, ctypes.byref(p)), "peer_import")
+                    ptrs.append(p.value)
+            self._arrays = (ctypes.c_void_p * self.world)(*ptrs)
+        self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def __call__(self, status=None):
+        import torch
+
+        if self.world == 1:
+            return
+        self.epoch += 1
+        st = status if status is not None else self._status
+        with torch.cuda.device(self.device):
+            _check(lib.ternix_b200_peer_barrier(self._arrays, self.world, self.rank, self.epoch & 0xFFFFFFFF, 0,
+                                                st.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream),
+                   "peer_barrier")
+
+    def timed_out(self) -> bool:
+        """Whether a barrier without a caller's status word has run out of time so far (synchronises the stream)."""
+        return self.world > 1 and int(self._status.item()) != 0
+
+
 class ShardedTernaryLinear:
     """One projection W[K,N], N-column-sharded over the ranks of a torch.distributed group (one process
     per GPU).  Each rank keeps only its packed column shard on its GPU; forward(a) returns the full
@@ -569,7 +625,8 @@ class ShardedTernaryLinear:
 
     mode="peer" (default when world > 1): C lives in a buffer every rank maps from every other rank; the
         GEMM epilogue of each rank stores its columns into all of them (ternix_b200_matmul_bcast) and a
-        tiny all-reduce on the same stream is the barrier.  The transfer overlaps the main loop.
+        flag barrier on the same stream (PeerBarrier) says when all of them have landed.  The transfer overlaps
+        the main loop.
     mode="nccl": the baseline -- compute the local block, ncclAllGather equal-sized blocks, scatter to
         row-major with ternix_b200_unpack_gathered.
     """
@@ -594,7 +651,7 @@ class ShardedTernaryLinear:
         self._c_bufs = None
         self._c = None
         self._peer_ptrs = None
-        self._token = None
+        self._barrier = None
         self._step = 0
 
     def local(self, a, out=None):
@@ -633,19 +690,16 @@ class ShardedTernaryLinear:
         # own buffer first, then the peers, each offset to this rank's first column
         order = [self.rank] + [r for r in range(self.world) if r != self.rank]
         self._peer_ptrs = [(ctypes.c_void_p * self.world)(*[row[r] + 4 * self.shard.n0 for r in order]) for row in ptrs]
-        self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._M = M
         self._step = 0
 
-    def stream_barrier(self):
-        """A barrier on the current stream: when it has passed, every rank's kernels enqueued before it have finished."""
-        import torch
-        import torch.distributed as dist
-
+    def stream_barrier(self, status=None):
+        """A barrier on the current stream: when it has passed, every rank's kernels enqueued before it have finished
+        and what they stored into this rank's buffers is visible.  The first call sets the flag arrays up (collective)."""
         if self.world > 1:
-            if self._token is None:
-                self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
-            dist.all_reduce(self._token, group=self.group)
+            if self._barrier is None:
+                self._barrier = PeerBarrier(self.group, self.device)
+            self._barrier(status)
 
     def forward(self, a, out=None, status=None, barrier=True):
         """Full row-major C[M, N] on every rank.  In peer mode the result is a view of one of two internal buffers
@@ -674,7 +728,7 @@ class ShardedTernaryLinear:
                                                         status.data_ptr() if status is not None else None,
                                                         s.cuda_stream), "matmul_bcast")
             if barrier:
-                self.stream_barrier()      # every rank's stores of this step have landed
+                self.stream_barrier(status)      # every rank's stores of this step have landed
             if out is not None:
                 out.copy_(self._c[b])
                 return out
@@ -704,7 +758,7 @@ class ShardedTernaryLinear:
             matmul_dequant(a, self.w_local, row_scale, w_scale,
                            out=self._y[b][:, self.shard.n0:self.shard.n0 + self.shard.n_cols], status=status,
                            extra_dest_ptrs=self._y_peers[b])
-        self.stream_barrier()
+        self.stream_barrier(status)
         return self._y[b]
 
     def _forward_nccl(self, a, out, status):
@@ -805,17 +859,15 @@ class ShardedProjectionSet:
             self._groups.append(ProjectionGroup(problems, peer_ptrs=peer_rows if self.any_sharded else None))
         self.outputs = self._outputs[0]
         self.launches = self._groups[0].launches
-        self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._barrier = PeerBarrier(self.group, self.device) if self.world > 1 and self.any_sharded else None
         self._step = 0
 
     def run(self, status=None):
-        import torch.distributed as dist
-
         b = gather_buffer_index(self._step) if self.any_sharded else 0
         self._step += 1
         self._groups[b].run(status=status)
-        if self.world > 1 and self.any_sharded:
-            dist.all_reduce(self._token, group=self.group)
+        if self._barrier is not None:
+            self._barrier(status)
         self.outputs = self._outputs[b]
         return self.outputs
 

@@ -855,6 +855,36 @@ __global__ void wait_timeout_selftest_kernel(unsigned long long limit_ns, int32_
     if (threadIdx.x == 0 && waited_ns) *waited_ns = tb200::global_timer_ns() - t0;
 }
 
+// Barrier between the GPUs of a sharded product, on a stream: thread t tells rank t that this rank has arrived (a
+// release store, at system scope, of the barrier's epoch into slot `rank` of rank t's flag array) and then waits until
+// rank t's epoch shows in slot t of this rank's own array.  Stream order puts the kernel behind this rank's GEMM, so
+// the release also covers the GEMM's stores into the peers' C; the acquire on the other side makes them visible to
+// what the peer runs next.  Epochs only grow, so a rank that is a barrier ahead does no harm.  The wait is bounded
+// like every other wait of this library (status word, no trap).
+constexpr int kPeerBarrierMaxRanks = 32;
+struct PeerFlags {
+    unsigned* flags[kPeerBarrierMaxRanks];     // flags[r]: rank r's array of `world` slots (own rank: the local array)
+};
+__global__ void peer_barrier_kernel(const __grid_constant__ PeerFlags pf, int world, int rank, unsigned epoch,
+                                    unsigned long long limit_ns, int32_t* __restrict__ status) {
+    const int t = threadIdx.x;
+    if (t >= world || t == rank) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pf.flags[t] + rank), "r"(epoch) : "memory");
+    const unsigned* mine = pf.flags[rank] + t;
+    const uint64_t t0 = tb200::global_timer_ns();
+    for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if (static_cast<int>(v - epoch) >= 0) break;
+        if (tb200::global_timer_ns() - t0 > limit_ns) {
+            if (status) atomicMax(status, tb200::kStatusTimeout);
+            break;
+        }
+        __nanosleep(100);
+    }
+}
+
 // Device-side packer: four consecutive int8 weights -> one byte, the arithmetic of the host packer
 // (code = 1 for +1, 3 for -1, else 0; field j in bits 2j..2j+1).  One thread packs 16 weights into 4 bytes.
 __global__ void pack_ternary_kernel(const int8_t* __restrict__ w, uint8_t* __restrict__ packed, size_t n_bytes) {
@@ -2278,6 +2308,22 @@ int ternix_b200_selftest_wait_timeout(unsigned long long limit_ns, int32_t* d_st
                                       void* stream) {
     if (limit_ns == 0 || limit_ns > 100000000ull) return TERNIX_B200_ERR_INVALID_ARG;      // at most 100 ms
     wait_timeout_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns, d_status, d_waited_ns);
+    TB_CUDA(cudaGetLastError());
+    return TERNIX_B200_OK;
+}
+
+int ternix_b200_peer_barrier(void* const* flag_arrays, int world, int rank, unsigned epoch, unsigned long long limit_ns,
+                             int32_t* d_status, void* stream) {
+    if (world < 1 || world > kPeerBarrierMaxRanks || rank < 0 || rank >= world || !flag_arrays) return TERNIX_B200_ERR_INVALID_ARG;
+    if (limit_ns == 0) limit_ns = tb200::kWaitLimitNs;
+    if (limit_ns > tb200::kWaitLimitNs) return TERNIX_B200_ERR_INVALID_ARG;
+    if (world == 1) return TERNIX_B200_OK;
+    PeerFlags pf{};
+    for (int r = 0; r < world; ++r) {
+        if (!flag_arrays[r]) return TERNIX_B200_ERR_INVALID_ARG;
+        pf.flags[r] = static_cast<unsigned*>(flag_arrays[r]);
+    }
+    peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, world, rank, epoch, limit_ns, d_status);
     TB_CUDA(cudaGetLastError());
     return TERNIX_B200_OK;
 }

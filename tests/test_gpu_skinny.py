@@ -228,6 +228,40 @@ def test_bounded_wait_runs_out_and_the_context_survives():
     assert_same(device_matmul(a, wp, "auto"), oracle_lib.matmul(a, wp), "product after the timeout self-test")
 
 
+def test_peer_barrier_signals_waits_and_gives_up():
+    """ternix_b200_peer_barrier on one GPU with both ranks' flag arrays local: the signal lands in the peer's array;
+    a peer whose epoch is already there lets the barrier pass; a peer that never arrives ends the wait after its
+    limit with TERNIX_B200_ERR_TIMEOUT in the status word, and the context stays usable."""
+    import ctypes
+    import torch
+    flags = [torch.zeros(64, dtype=torch.int32, device="cuda") for _ in range(2)]
+    arrays = (ctypes.c_void_p * 2)(flags[0].data_ptr(), flags[1].data_ptr())
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    flags[0][1] = 1                                       # "rank 1 has arrived at barrier 1"
+    assert tb.lib.ternix_b200_peer_barrier(arrays, 2, 0, 1, 0, status.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert int(flags[1][0].item()) == 1                   # rank 0's signal, in rank 1's array
+    flags[0][1] = 5                                       # a peer that is several barriers ahead does not block either
+    assert tb.lib.ternix_b200_peer_barrier(arrays, 2, 0, 2, 0, status.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and int(flags[1][0].item()) == 2
+    # nobody answers barrier 6: 20 ms, then the status word
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    assert tb.lib.ternix_b200_peer_barrier(arrays, 2, 0, 6, 20_000_000, status.data_ptr(), stream) == 0
+    e1.record()
+    torch.cuda.synchronize()
+    assert int(status.item()) == tb.ERR_TIMEOUT
+    assert 15.0 < e0.elapsed_time(e1) < 500.0
+    assert tb.lib.ternix_b200_peer_barrier(arrays, 0, 0, 1, 0, None, None) == tb.ERR_INVALID_ARG
+    assert tb.lib.ternix_b200_peer_barrier(arrays, 2, 2, 1, 0, None, None) == tb.ERR_INVALID_ARG
+    assert tb.lib.ternix_b200_peer_barrier(arrays, 1, 0, 1, 0, None, None) == 0      # one rank: nothing to wait for
+    a, wp = synth(32, 1024, 512, 4)
+    assert_same(device_matmul(a, wp, "auto"), oracle_lib.matmul(a, wp), "product after the barrier timeout")
+
+
 def test_second_gpu_in_the_same_process():
     """Per-device state (shared-memory opt-ins, SM counts, flag and scratch addresses): every kernel family on
     device 1 after device 0 in one process."""

@@ -74,9 +74,39 @@ def test_should_shard_policy():
     assert not tb.should_shard(4096, 8192, 28672, 1)
 
 
-def _protocol_rank(rank, world, port, tmp):
+class _FlagBarrier:
+    """ternix_b200_peer_barrier restated on memory-mapped files: rank r's flag array has one slot per rank; arriving
+    means writing the epoch into slot `rank` of every peer's array, then waiting (with a limit) until every peer's
+    epoch shows in the own array.  Epochs only grow, so `>=` is the test."""
+
+    def __init__(self, tmp, rank, world):
+        self.rank, self.world, self.epoch = rank, world, 0
+        self.flags = [np.load(os.path.join(tmp, f"flags{r}.npy"), mmap_mode="r+") for r in range(world)]
+
+    @staticmethod
+    def create(tmp, rank, world):
+        np.lib.format.open_memmap(os.path.join(tmp, f"flags{rank}.npy"), mode="w+", dtype=np.uint32, shape=(world,))[:] = 0
+
+    def __call__(self, limit_s=20.0):
+        import time
+        self.epoch += 1
+        for t in range(self.world):
+            if t != self.rank:
+                self.flags[t][self.rank] = self.epoch
+                self.flags[t].flush()
+        t0 = time.monotonic()
+        for t in range(self.world):
+            while t != self.rank and int(self.flags[self.rank][t]) < self.epoch:
+                if time.monotonic() - t0 > limit_s:
+                    return False                      # the status word's timeout code; nothing hangs
+                time.sleep(0.0005)
+        return True
+
+
+def _protocol_rank(rank, world, port, tmp, barrier_kind="gloo"):
     """The two-buffer gather protocol of ShardedTernaryLinear with CPU ranks: memory-mapped files stand in for the
-    peer-mapped C buffers, the oracle for the GPU kernel, a gloo barrier for the stream barrier.  The activations
+    peer-mapped C buffers, the oracle for the GPU kernel, and either a gloo barrier or the flag protocol of
+    ternix_b200_peer_barrier (restated above) for the stream barrier.  The activations
     change every step and one rank reads its result late, while the others are already storing the next step."""
     import time
     sys.path.insert(0, ROOT)
@@ -93,7 +123,9 @@ def _protocol_rank(rank, world, port, tmp):
         local_w = tb.slice_columns(wp, sh.n0, sh.n_cols)
         for b in range(2):                                   # this rank's two C buffers
             np.lib.format.open_memmap(os.path.join(tmp, f"c{rank}_{b}.npy"), mode="w+", dtype=np.int32, shape=(M, N))[:] = -1
+        _FlagBarrier.create(tmp, rank, world)
         dist.barrier()
+        flag_barrier = _FlagBarrier(tmp, rank, world)
         bufs = [[np.load(os.path.join(tmp, f"c{r}_{b}.npy"), mmap_mode="r+") for b in range(2)] for r in range(world)]
         for step in range(8):
             a = tb.synth_activations((M, K), 100 + step)     # new activations every step
@@ -102,7 +134,10 @@ def _protocol_rank(rank, world, port, tmp):
             for r in range(world):                           # the epilogue's stores into every rank's C
                 bufs[r][b][:, sh.n0:sh.n0 + sh.n_cols] = mine
                 bufs[r][b].flush()
-            dist.barrier()                                   # all stores of this step have landed
+            if barrier_kind == "gloo":
+                dist.barrier()                               # all stores of this step have landed
+            else:
+                assert flag_barrier(), f"rank {rank} step {step}: a peer did not arrive"
             if rank == 0:
                 time.sleep(0.05)                             # a slow reader: the other ranks run ahead into the next step
             got = np.array(bufs[rank][b])
@@ -112,7 +147,14 @@ def _protocol_rank(rank, world, port, tmp):
         dist.destroy_process_group()
 
 
-def test_two_buffer_gather_protocol_over_gloo(tmp_path):
-    world = 2
-    mp.spawn(_protocol_rank, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+@pytest.mark.parametrize("world,barrier_kind", [(2, "gloo"), (2, "flags"), (3, "flags")])
+def test_two_buffer_gather_protocol_over_gloo(world, barrier_kind, tmp_path):
+    mp.spawn(_protocol_rank, args=(world, _free_port(), str(tmp_path), barrier_kind), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+def test_flag_barrier_gives_up_on_an_absent_peer(tmp_path):
+    """A peer that never arrives: the wait runs out and reports it, as the kernel does through the status word."""
+    for r in range(2):
+        _FlagBarrier.create(str(tmp_path), r, 2)
+    assert _FlagBarrier(str(tmp_path), 0, 2)(limit_s=0.2) is False
