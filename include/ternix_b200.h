@@ -130,6 +130,12 @@ typedef struct ternix_b200_weights ternix_b200_weights;
 int ternix_b200_weights_create(ternix_b200_weights **out, const uint8_t *dW, int K, int N);
 int ternix_b200_weights_matmul(ternix_b200_weights *weights, const int8_t *dA, int32_t *dC, int M, long long ldc,
                                int32_t *d_status, void *stream);
+/* The serving form of the host-pointer call: the weights stay on the device (the handle), the activations come from
+ * host memory and C goes back to host memory, in row slabs on three streams (upload of slab j+1, product of slab j,
+ * download of slab j-1), so that the call takes little more than the download of C.  Pinned host memory makes the
+ * copies asynchronous; pageable memory works and is slower.  Synchronous: C is complete when it returns.  Calls on one
+ * device run one after the other. */
+int ternix_b200_weights_matmul_host(ternix_b200_weights *weights, const int8_t *A_host, int32_t *C_host, int M);
 void ternix_b200_weights_destroy(ternix_b200_weights *weights);
 
 /* replaces: ternix::pack_ternary_weights (src/bitpack.cpp:5-15) for weights that are already on the device: the same

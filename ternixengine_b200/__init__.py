@@ -46,7 +46,7 @@ EXPORTS = (
     "ternix_b200_status_string", "ternix_b200_last_cuda_error", "ternix_b200_cuda_error_string",
     "ternix_b200_version", "ternix_b200_last_launched_kernel", "ternix_b200_launched_kernel_name",
     "ternix_b200_set_option", "ternix_b200_release_cached_memory",
-    "ternix_b200_weights_create", "ternix_b200_weights_matmul", "ternix_b200_weights_destroy",
+    "ternix_b200_weights_create", "ternix_b200_weights_matmul", "ternix_b200_weights_matmul_host", "ternix_b200_weights_destroy",
     "ternix_b200_pack_ternary_device", "ternix_b200_selftest_wait_timeout",
     "ternix_b200_pack_ternary", "ternix_b200_unpack_ternary", "ternix_b200_interleave_offline",
     "ternix_b200_find_non_ternary", "ternix_b200_slice_columns",
@@ -93,6 +93,7 @@ def _load() -> ctypes.CDLL:
         "ternix_b200_release_cached_memory": (i32, []),
         "ternix_b200_weights_create": (i32, [c.POINTER(vp), vp, i32, i32]),
         "ternix_b200_weights_matmul": (i32, [vp, vp, vp, i32, i64, vp, vp]),
+        "ternix_b200_weights_matmul_host": (i32, [vp, vp, vp, i32]),
         "ternix_b200_weights_destroy": (None, [vp]),
         "ternix_b200_pack_ternary_device": (i32, [vp, vp, sz, vp]),
         "ternix_b200_selftest_wait_timeout": (i32, [c.c_ulonglong, vp, vp, vp]),
@@ -321,6 +322,30 @@ class TernaryWeights:
                                                   status.data_ptr() if status is not None else None, s.cuda_stream),
                    "weights_matmul")
         return out
+
+    def matmul_host(self, a_host, out_host=None):
+        """C = A x W with the activations and the result in host memory (numpy arrays or CPU torch tensors, ideally
+        pinned) and the weights resident on the device: row slabs on three streams, so the call takes little more
+        than the download of C (ternix_b200_weights_matmul_host).  Synchronous."""
+        import torch
+
+        def host_ptr(x, dtype_np, dtype_t, shape, what):
+            if isinstance(x, np.ndarray):
+                if x.dtype != dtype_np or x.shape != shape or not x.flags["C_CONTIGUOUS"]:
+                    raise ValueError(f"{what} must be a C-contiguous {np.dtype(dtype_np).name} array of shape {shape}")
+                return x.ctypes.data
+            if x.is_cuda or x.dtype != dtype_t or tuple(x.shape) != shape or not x.is_contiguous():
+                raise ValueError(f"{what} must be a contiguous CPU tensor of shape {shape}")
+            return x.data_ptr()
+
+        M = a_host.shape[0]
+        if out_host is None:
+            out_host = torch.empty((M, self.N), dtype=torch.int32, pin_memory=True)
+        pa = host_ptr(a_host, np.int8, torch.int8, (M, self.K), "A")
+        pc = host_ptr(out_host, np.int32, torch.int32, (M, self.N), "out")
+        with torch.cuda.device(self.w.device):
+            _check(lib.ternix_b200_weights_matmul_host(self._h, pa, pc, M), "weights_matmul_host")
+        return out_host
 
     def close(self):
         if getattr(self, "_h", None) and lib is not None:
@@ -734,6 +759,72 @@ class ShardedTernaryLinear:
                 return out
             return self._c[b]
         return self._forward_nccl(a, out, status)
+
+    def forward_host(self, a_host, out_host=None, slab_rows=None, status=None):
+        """The step with its operands in host memory: every rank passes the same activations (a CPU tensor, ideally
+        pinned); a rank that passes `out_host` (a CPU int32 (M, N) tensor) gets the full C there.  Collective: every
+        rank calls it, with the same M and slab_rows.  The rows are cut into slabs (about 64 MB of C each, multiples
+        of 256 rows): the activations of slab j+1 go up while slab j is computed and gathered and slab j-1 comes down,
+        so the call takes little more than the download of C.  On one GPU this is TernaryWeights.matmul_host.
+        Synchronous."""
+        import torch
+
+        M = a_host.shape[0]
+        if self.mode == "local":
+            if getattr(self, "_handle", None) is None:
+                self._handle = TernaryWeights(self.w_local)
+            if out_host is None:
+                out_host = torch.empty((M, self.N), dtype=torch.int32, pin_memory=True)
+            return self._handle.matmul_host(a_host, out_host)
+        if slab_rows is None:
+            slabs = min(16, max(1, (4 * M * self.N) // (64 << 20)))
+            slab_rows = min(M, -(-(-(-M // slabs)) // 256) * 256)
+        n_slabs = -(-M // slab_rows)
+        dev = self.device
+        hs = getattr(self, "_host_state", None)
+        if hs is None or hs["rows"] != slab_rows:
+            if hs is not None:
+                raise ValueError("the slab extent is fixed by the first call (the gathered C buffers are kept)")
+            hs = {"rows": slab_rows,
+                  "a": [torch.zeros((slab_rows, self.K), dtype=torch.int8, device=dev) for _ in range(2)],
+                  "stage": None,
+                  "s_in": torch.cuda.Stream(dev), "s_out": torch.cuda.Stream(dev),
+                  "ev_in": [torch.cuda.Event() for _ in range(2)], "ev_fwd": [torch.cuda.Event() for _ in range(2)],
+                  "ev_out": [torch.cuda.Event() for _ in range(2)]}
+            self._host_state = hs
+        if out_host is not None and hs["stage"] is None:
+            hs["stage"] = [torch.empty((slab_rows, self.N), dtype=torch.int32, device=dev) for _ in range(2)]
+        main = torch.cuda.current_stream(dev)
+        hs["s_in"].wait_stream(main)
+        for j in range(n_slabs):
+            r0 = j * slab_rows
+            ext = min(slab_rows, M - r0)
+            b = j & 1
+            with torch.cuda.stream(hs["s_in"]):
+                if j >= 2:
+                    hs["s_in"].wait_event(hs["ev_fwd"][b])        # the product of slab j-2 has read this buffer
+                hs["a"][b][:ext].copy_(a_host[r0:r0 + ext], non_blocking=True)
+                if ext < slab_rows:
+                    hs["a"][b][ext:].zero_()
+                hs["ev_in"][b].record(hs["s_in"])
+            main.wait_event(hs["ev_in"][b])
+            c = self.forward(hs["a"][b], status=status)           # gathered on every rank; valid until the call after next
+            if out_host is not None:
+                # a private copy, on the calling stream (the gather protocol wants the readers of a step there), so
+                # that the download can still run while the peers store the slab after next into the same buffer
+                if j >= 2:
+                    main.wait_event(hs["ev_out"][b])
+                hs["stage"][b][:ext].copy_(c[:ext], non_blocking=True)
+            hs["ev_fwd"][b].record(main)
+            if out_host is not None:
+                hs["s_out"].wait_event(hs["ev_fwd"][b])
+                with torch.cuda.stream(hs["s_out"]):
+                    out_host[r0:r0 + ext].copy_(hs["stage"][b][:ext], non_blocking=True)
+                    hs["ev_out"][b].record(hs["s_out"])
+        main.wait_stream(hs["s_out"])
+        main.wait_stream(hs["s_in"])
+        main.synchronize()
+        return out_host
 
     def forward_dequant(self, a, row_scale, w_scale: float, status=None):
         """bfloat16 C = (A x W) * row_scale[:, None] * w_scale on every rank.  With more than one rank the GEMM

@@ -1026,6 +1026,7 @@ struct ternix_b200_weights {
     // last activation operand seen per kernel family, and last output
     const int8_t* a_ptr[2] = {nullptr, nullptr};
     int a_rows[2] = {0, 0};
+    int a_tile_rows = 0;               // tile form the prefill kernel's activation map was made for
     CUtensorMap tmap_a[2] = {};
     int32_t* c_ptr = nullptr;
     int c_rows = 0;
@@ -1428,8 +1429,10 @@ int host_pipe(HostPipe** out) {
 // arrived.  Column slabs (by_rows == false) share A and take W slab by slab; W and C of a slab are compact on the
 // device and the copies are pitched on the host side.  Row slabs share W and take A slab by slab; every copy is
 // contiguous.
+// d_w_resident: the packed weights are on the device already (row slabs only): nothing is uploaded but A.
 int matmul_host_pipelined(const int8_t* A, const uint8_t* Wp, int32_t* C, int M, int K, int N, int kernel, int slab,
-                          bool by_rows) {
+                          bool by_rows, const uint8_t* d_w_resident = nullptr) {
+    if (d_w_resident && !by_rows) return TERNIX_B200_ERR_INVALID_ARG;
     HostPipe* hp = nullptr;
     int rc = host_pipe(&hp);
     if (rc) return rc;
@@ -1439,7 +1442,7 @@ int matmul_host_pipelined(const int8_t* A, const uint8_t* Wp, int32_t* C, int M,
     if (n_slabs > HostPipe::kMaxSlabs) return TERNIX_B200_ERR_INVALID_ARG;
     auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
     // [status | shared operand | per slab: its input, its C]
-    const size_t shared_bytes = by_rows ? static_cast<size_t>(K) * (N / 4) : static_cast<size_t>(M) * K;
+    const size_t shared_bytes = d_w_resident ? 0 : by_rows ? static_cast<size_t>(K) * (N / 4) : static_cast<size_t>(M) * K;
     size_t off_in[HostPipe::kMaxSlabs], off_c[HostPipe::kMaxSlabs];
     size_t total = 256 + up(shared_bytes);
     for (int j = 0; j < n_slabs; ++j) {
@@ -1456,7 +1459,7 @@ int matmul_host_pipelined(const int8_t* A, const uint8_t* Wp, int32_t* C, int M,
     cudaError_t e = cudaMallocFromPoolAsync(reinterpret_cast<void**>(&blob), total, pool, hp->s_run);
     if (e != cudaSuccess) return cuda_fail(e);
     int32_t* dS = reinterpret_cast<int32_t*>(blob);
-    uint8_t* d_shared = blob + 256;
+    const uint8_t* d_shared = d_w_resident ? d_w_resident : blob + 256;
     int32_t h_status = 0;
     do {
         if ((e = cudaMemsetAsync(dS, 0, 4, hp->s_run)) != cudaSuccess) break;
@@ -1474,8 +1477,9 @@ int matmul_host_pipelined(const int8_t* A, const uint8_t* Wp, int32_t* C, int M,
                                       hp->s_in);
             if (e == cudaSuccess) e = cudaEventRecord(hp->ev_w[j], hp->s_in);
             if (j == 0 && e == cudaSuccess) {
-                e = cudaMemcpyAsync(d_shared, by_rows ? static_cast<const void*>(Wp) : static_cast<const void*>(A),
-                                    shared_bytes, cudaMemcpyHostToDevice, hp->s_in);
+                if (!d_w_resident)
+                    e = cudaMemcpyAsync(blob + 256, by_rows ? static_cast<const void*>(Wp) : static_cast<const void*>(A),
+                                        shared_bytes, cudaMemcpyHostToDevice, hp->s_in);
                 if (e == cudaSuccess) e = cudaEventRecord(hp->ev_a, hp->s_in);
             }
         }
@@ -1489,7 +1493,7 @@ int matmul_host_pipelined(const int8_t* A, const uint8_t* Wp, int32_t* C, int M,
                 rc = ternix_b200_matmul_ex(reinterpret_cast<const int8_t*>(blob + off_in[j]), d_shared, dCj, ext, K, N, N,
                                            kernel, dS, hp->s_run);
             else
-                rc = ternix_b200_matmul_ex(reinterpret_cast<const int8_t*>(d_shared), blob + off_in[j], dCj, M, K, ext,
+                rc = ternix_b200_matmul_ex(reinterpret_cast<const int8_t*>(blob + 256), blob + off_in[j], dCj, M, K, ext,
                                            ext, kernel, dS, hp->s_run);
             if (rc) break;
             if ((e = cudaEventRecord(hp->ev_c[j], hp->s_run)) != cudaSuccess) break;
@@ -2246,6 +2250,22 @@ int ternix_b200_weights_create(ternix_b200_weights** out, const uint8_t* dW, int
     return TERNIX_B200_OK;
 }
 
+int ternix_b200_weights_matmul_host(ternix_b200_weights* w, const int8_t* A, int32_t* C, int M) {
+    if (!w) return TERNIX_B200_ERR_INVALID_ARG;
+    if (M < 0) return TERNIX_B200_ERR_INVALID_SHAPE;
+    const int K = w->K, N = w->N;
+    if (M == 0 || N == 0) return TERNIX_B200_OK;
+    if (!C || (K > 0 && !A)) return TERNIX_B200_ERR_INVALID_ARG;
+    // Row slabs of about 64 MB of C (multiples of 256 rows, at most 16 slabs): the activations of slab j+1 go up while
+    // slab j is computed and slab j-1 comes down.  A product with a small C runs as one slab.
+    const long long c_bytes = static_cast<long long>(M) * N * 4;
+    long long slabs = std::min<long long>(HostPipe::kMaxSlabs, std::max<long long>(1, c_bytes / (static_cast<long long>(64) << 20)));
+    long long rows = (M + slabs - 1) / slabs;
+    rows = std::min<long long>(M, ((rows + 255) / 256) * 256);
+    if ((M + rows - 1) / rows > HostPipe::kMaxSlabs) rows = M;
+    return matmul_host_pipelined(A, nullptr, C, M, K, N, TERNIX_B200_KERNEL_AUTO, static_cast<int>(rows), true, w->dW);
+}
+
 void ternix_b200_weights_destroy(ternix_b200_weights* w) { delete w; }
 
 int ternix_b200_weights_matmul(ternix_b200_weights* w, const int8_t* dA, int32_t* dC, int M, long long ldc,
@@ -2281,11 +2301,13 @@ int ternix_b200_weights_matmul(ternix_b200_weights* w, const int8_t* dA, int32_t
         tb200::Tc3Stores stores{};
         {
             std::lock_guard<std::mutex> lock(w->mu);
-            if (w->a_ptr[1] != dA || w->a_rows[1] != M) {
-                const int rc = make_tc3_act_map(&w->tmap_a[1], dA, M, K, tc3_tile_rows(M));
+            const int tile_rows = tc3_tile_rows(M);          // part of the key: an option can change it between calls
+            if (w->a_ptr[1] != dA || w->a_rows[1] != M || w->a_tile_rows != tile_rows) {
+                const int rc = make_tc3_act_map(&w->tmap_a[1], dA, M, K, tile_rows);
                 if (rc) return rc;
                 w->a_ptr[1] = dA;
                 w->a_rows[1] = M;
+                w->a_tile_rows = tile_rows;
             }
             if (w->c_ptr != dC || w->c_rows != M || w->c_ld != ldc) {
                 const int rc = make_tc3_store_map(&w->tmap_c, dC, M, N, ldc);

@@ -183,6 +183,46 @@ def test_weight_handle_matches_and_caches():
         handle.close()
 
 
+def test_weight_handle_notices_a_change_of_tile_form(option):
+    """The handle's cached activation descriptor is made for one tile form of the prefill kernel; an option that
+    changes the form between two calls with the same activations must not be served the old descriptor."""
+    import torch
+    m, k, n = 300, 1040, 832
+    wp = tb.synth_packed_weights(k, n, 9)
+    a = tb.synth_activations((m, k), 10)
+    expect = oracle_lib.matmul(a, wp)
+    dw, da = torch.from_numpy(wp).cuda(), torch.from_numpy(a).cuda()
+    handle = tb.TernaryWeights(dw)
+    out = torch.empty((m, n), dtype=torch.int32, device="cuda")
+    for rows in ("256", "128", "256", ""):
+        option("tc_tile_rows", rows)
+        out.fill_(-7)
+        handle.matmul(da, out=out)
+        torch.cuda.synchronize()
+        assert_same(out.cpu().numpy(), expect, f"weight handle, tile form {rows!r}")
+    handle.close()
+
+
+def test_weight_handle_host_call():
+    """ternix_b200_weights_matmul_host: activations and C in host memory (pinned torch tensors and plain numpy arrays),
+    weights resident; one slab, several slabs with a ragged last one, every regime's row counts."""
+    import torch
+    for (m, k, n) in [(300, 1040, 832), (1, 2560, 6912), (32, 4096, 1024), (2304, 528, 16384)]:
+        wp = tb.synth_packed_weights(k, n, 21 + k)
+        handle = tb.TernaryWeights(torch.from_numpy(wp).cuda())
+        for rep in range(2):
+            a = tb.synth_activations((m, k), 40 + rep)
+            expect = oracle_lib.matmul(a, wp)
+            if rep == 0:
+                out = handle.matmul_host(torch.from_numpy(a).pin_memory())
+                assert_same(out.numpy(), expect, f"matmul_host pinned {m}x{k}x{n}")
+            else:
+                out = np.full((m, n), -9, dtype=np.int32)
+                handle.matmul_host(a, out)
+                assert_same(out, expect, f"matmul_host numpy {m}x{k}x{n}")
+        handle.close()
+
+
 def test_pack_ternary_on_the_device():
     """ternix_b200_pack_ternary_device writes the bytes of the host packer (and of the oracle's), for aligned and
     unaligned buffers and for sizes that are not multiples of 16."""

@@ -100,6 +100,21 @@ def _rank_main(rank, world, port, out_dir):
                 for i, out in enumerate(outs):
                     assert np.array_equal(out.cpu().numpy(), oracle_lib.matmul(acts_h[i], weights[i])), \
                         f"rank {rank}: member {i} (shard={shard}, rep {rep})"
+        # the step with host operands: row slabs on three streams; a ragged last slab; C wanted on rank 0 only,
+        # then on every rank; new activations on every call
+        m, k, n = 1664, 1040, 4096
+        wp = tb.synth_packed_weights(k, n, 31)
+        layer = tb.ShardedTernaryLinear(wp, device=dev, mode="peer")
+        for rep in range(3):
+            a = tb.synth_activations((m, k), 300 + rep)
+            a_host = torch.from_numpy(a).pin_memory()
+            want = rank == 0 or rep == 2
+            out_host = torch.full((m, n), -3, dtype=torch.int32).pin_memory() if want else None
+            layer.forward_host(a_host, out_host, slab_rows=512, status=status)
+            dist.barrier()
+            assert int(status.item()) == 0
+            if want:
+                assert np.array_equal(out_host.numpy(), oracle_lib.matmul(a, wp)), f"rank {rank}: forward_host rep {rep}"
         open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
     finally:
         dist.destroy_process_group()
