@@ -1438,15 +1438,23 @@ int matmul_host_pipelined(const int8_t* A, const uint8_t* Wp, int32_t* C, int M,
     if (rc) return rc;
     std::lock_guard<std::mutex> lock(hp->mu);
     const int extent = by_rows ? M : N;
-    const int n_slabs = (extent + slab - 1) / slab;
+    // With resident weights nothing but the first slab's activations stands before the first product, so a short first
+    // slab (256 rows) lets the download start a few hundred microseconds earlier.
+    const int first = (d_w_resident && extent > slab && slab > 256) ? 256 : slab;
+    const int n_slabs = 1 + (extent > first ? (extent - first + slab - 1) / slab : 0);
     if (n_slabs > HostPipe::kMaxSlabs) return TERNIX_B200_ERR_INVALID_ARG;
+    int start[HostPipe::kMaxSlabs], ext_of[HostPipe::kMaxSlabs];
+    for (int j = 0; j < n_slabs; ++j) {
+        start[j] = j == 0 ? 0 : first + (j - 1) * slab;
+        ext_of[j] = j == 0 ? std::min(first, extent) : std::min(slab, extent - start[j]);
+    }
     auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
     // [status | shared operand | per slab: its input, its C]
     const size_t shared_bytes = d_w_resident ? 0 : by_rows ? static_cast<size_t>(K) * (N / 4) : static_cast<size_t>(M) * K;
     size_t off_in[HostPipe::kMaxSlabs], off_c[HostPipe::kMaxSlabs];
     size_t total = 256 + up(shared_bytes);
     for (int j = 0; j < n_slabs; ++j) {
-        const size_t ext = std::min(slab, extent - j * slab);
+        const size_t ext = static_cast<size_t>(ext_of[j]);
         off_in[j] = total;
         total += up(by_rows ? ext * K : static_cast<size_t>(K) * (ext / 4));
         off_c[j] = total;
@@ -1468,7 +1476,7 @@ int matmul_host_pipelined(const int8_t* A, const uint8_t* Wp, int32_t* C, int M,
         if ((e = cudaStreamWaitEvent(hp->s_out, hp->ev_alloc, 0)) != cudaSuccess) break;
         // up: the first slab's own input, then the shared operand, then the other slabs
         for (int j = 0; j < n_slabs && e == cudaSuccess; ++j) {
-            const int x0 = j * slab, ext = std::min(slab, extent - x0);
+            const int x0 = start[j], ext = ext_of[j];
             if (by_rows)
                 e = cudaMemcpyAsync(blob + off_in[j], A + static_cast<size_t>(x0) * K, static_cast<size_t>(ext) * K,
                                     cudaMemcpyHostToDevice, hp->s_in);
@@ -1486,7 +1494,7 @@ int matmul_host_pipelined(const int8_t* A, const uint8_t* Wp, int32_t* C, int M,
         if (e != cudaSuccess) break;
         if ((e = cudaStreamWaitEvent(hp->s_run, hp->ev_a, 0)) != cudaSuccess) break;
         for (int j = 0; j < n_slabs; ++j) {
-            const int x0 = j * slab, ext = std::min(slab, extent - x0);
+            const int x0 = start[j], ext = ext_of[j];
             int32_t* dCj = reinterpret_cast<int32_t*>(blob + off_c[j]);
             if ((e = cudaStreamWaitEvent(hp->s_run, hp->ev_w[j], 0)) != cudaSuccess) break;
             if (by_rows)
@@ -2262,7 +2270,7 @@ int ternix_b200_weights_matmul_host(ternix_b200_weights* w, const int8_t* A, int
     long long slabs = std::min<long long>(HostPipe::kMaxSlabs, std::max<long long>(1, c_bytes / (static_cast<long long>(64) << 20)));
     long long rows = (M + slabs - 1) / slabs;
     rows = std::min<long long>(M, ((rows + 255) / 256) * 256);
-    if ((M + rows - 1) / rows > HostPipe::kMaxSlabs) rows = M;
+    if ((M + rows - 1) / rows + 1 > HostPipe::kMaxSlabs) rows = M;          // + 1: the short first slab
     return matmul_host_pipelined(A, nullptr, C, M, K, N, TERNIX_B200_KERNEL_AUTO, static_cast<int>(rows), true, w->dW);
 }
 
