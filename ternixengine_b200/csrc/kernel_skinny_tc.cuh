@@ -60,7 +60,7 @@ constexpr int kSkBK = 128;                        // k-rows per stage
 constexpr int kSkItemCols = 256;                  // weight columns per item: two MMA blocks of 128
 constexpr int kSkWpRowBytes = kSkItemCols / 4;    // 64
 constexpr int kSkWpBytes = kSkBK * kSkWpRowBytes; // 8192
-constexpr int kSkThreads = 16 * 32;
+constexpr int kSkThreads = 18 * 32;               // warps 16 and 17: the second pair of MMA issuers
 constexpr int kSkFirstExpandWarp = 4, kSkFirstEpilogueWarp = 12;
 constexpr uint32_t kSkStageCols = 64;              // operand stage: 2 blocks x 128 K-bytes = 2 x 32 columns
 constexpr int kSkMaxCtas = 256;                   // flags per launch slot
@@ -69,11 +69,18 @@ template <int NB>
 struct SkGeom {
     static_assert(NB == 16 || NB == 32 || NB == 64 || NB == 128, "batch rows per instruction");
     static constexpr int kActBytes = NB * 128;                   // one box: NB rows x 128 K-bytes, 128-byte swizzle
-    static constexpr int kAccBufs = NB == 128 ? 1 : 2;           // accumulator buffers per 128-column block
-    static constexpr int kTStages = NB <= 32 ? 6 : 4;            // operand ring (tensor memory)
+    // Four MMA issuers for NB <= 64: the stages of a segment go alternately to two pairs of issuers, each pair with
+    // accumulators of its own, and the epilogue adds the two.  (One thread issues a small-N MMA every 60-90 cycles and
+    // spends 180 on a commit, far more than the tensor pipe needs to execute them; two threads per block double that.)
+    // (Giving the second pair half of the activation rows instead, for NB = 64, was measured: every issuer then meets
+    // every stage, and the stage rate is that of two issuers again.)
+    static constexpr bool kSplitK = NB <= 64;
+    static constexpr int kParts = kSplitK ? 2 : 1;
+    static constexpr int kAccBufs = NB <= 32 ? 2 : 1;            // accumulator buffers per 128-column block and part
+    static constexpr int kTStages = NB == 16 ? 6 : 4;            // operand ring (tensor memory)
     static constexpr int kWStages = NB == 128 ? 8 : 16;          // packed-weight ring (shared memory): what is in flight from HBM
     static constexpr int kAStages = NB == 128 ? 6 : NB == 64 ? 8 : 16;   // activation ring (shared memory)
-    static constexpr uint32_t kRingCol = 2 * kAccBufs * NB;      // after the accumulators: [buffer][block] x NB columns
+    static constexpr uint32_t kRingCol = 2 * kParts * kAccBufs * NB;   // after the accumulators: [buffer][part][block] x NB columns
     static_assert(kRingCol + kTStages * kSkStageCols <= 512, "tensor memory: 512 columns");
     static constexpr size_t kSmemBytes = 1024 + size_t(kWStages) * kSkWpBytes + size_t(kAStages) * kActBytes + 768;
     static_assert(kSmemBytes <= 227 * 1024, "shared memory: 227 KB per CTA");
@@ -261,13 +268,13 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
         }
         for (int s = 0; s < TS; ++s) {
             mbar_init(&ready[s], 4);
-            mbar_init(&t_free[s], 2);
+            mbar_init(&t_free[s], 2);                  // the two issuers that read the stage
         }
         for (int b = 0; b < 4; ++b) {
-            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_full[b], G::kParts);      // one commit per issuer of the block
             mbar_init(&acc_empty[b], 4);
         }
-        mbar_init(drain, 2);
+        mbar_init(drain, 2 * G::kParts);
         *abort_flag = 0;
         *epi_count = 0;
         mbar_init_fence();
@@ -322,14 +329,17 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
                 for (uint32_t j = first; j < it; ++j) mbar_drain(&a_full[j % AS], (j / AS) & 1);
             }
         }
-    } else if (warp == 1 || warp == 3) {
+    } else if (warp == 1 || warp == 3 || (G::kParts == 2 && warp >= 16)) {
         // ================================================================ MMA issuers
-        // Two threads, one per 128-column block of the box (different accumulators, so the order between them does not
-        // matter).  A single thread's instruction stream -- waits, descriptor arithmetic, four instructions per MMA --
-        // is what bounds the stage rate of this kernel, so it is split in two and kept short: ring positions and
-        // the descriptor's low word advance by additions, no division, no 64-bit arithmetic.
+        // One thread per 128-column block of the box and, for NB <= 64, per parity of the stage count: warps 1 and 3
+        // take the even stages (counted over the CTA's whole walk), warps 16 and 17 the odd ones, each into accumulators
+        // of its own, so the order between issuers never matters.  A thread's instruction stream -- waits, descriptor
+        // arithmetic, 60-90 cycles per MMA, 180 per commit -- is what bounds the stage rate of this kernel, which is why
+        // it is split four ways and kept short: ring positions and the descriptor's low word advance by additions.
         if (lane == 0) {
-            const uint32_t hsel = warp == 3 ? 1u : 0u;
+            const uint32_t hsel = (warp == 3 || warp == 17) ? 1u : 0u;
+            const uint32_t part = warp >= 16 ? 1u : 0u;
+            uint32_t it = 0;
             const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);          // stride 1024 B, version 1, 128-byte swizzle
             const uint32_t desc_lo0 = ((smem_u32(sAct) & 0x3FFFFu) >> 4) | (1u << 16);  // start address, leading offset 16 B
             uint32_t sl = 0, ph_t = 0, al = 0, ph_a = 0, lt = 0;
@@ -342,9 +352,14 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
                 if (!mbar_wait(&acc_empty[ab * 2 + hsel], (use & 1) ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
                 const bool mine = hsel >= static_cast<uint32_t>(w.h0) && hsel < static_cast<uint32_t>(w.h1);
-                const uint32_t d = tmem_base + (ab * 2 + hsel) * NB;
+                const uint32_t d = tmem_base + ((ab * G::kParts + part) * 2 + hsel) * NB;
                 uint32_t acc = 0;
-                for (int s = w.s0; s < w.s1; ++s) {
+                for (int s = w.s0; s < w.s1; ++s, ++it) {
+                    if (G::kSplitK && (it & 1u) != part) {          // the other pair's stage: only the ring positions move
+                        if (++sl == TS) { sl = 0; ph_t ^= 1; }
+                        if (++al == AS) { al = 0; ph_a ^= 1; }
+                        continue;
+                    }
                     if (!mbar_wait(&ready[sl], ph_t, abort_flag) || !mbar_wait(&a_full[al], ph_a, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
                     if (mine) {
@@ -427,17 +442,22 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
                 }
             }
         }
-    } else if (warp >= kSkFirstEpilogueWarp) {
+    } else if (warp >= kSkFirstEpilogueWarp && warp < kSkFirstEpilogueWarp + 4) {
         // ================================================================ epilogue
         // Thread = operand row = weight column; registers = batch rows.  Lane l of quarter q is weight column
         // 32q + 4 (l % 8) + l / 8 of its 128-column block.
         const uint32_t q = warp & 3;
         const int col_in_block = 32 * q + 4 * (lane & 7) + (lane >> 3);
-        uint32_t lt = 0;
+        uint32_t lt = 0, it = 0;                   // it: stages before this segment (their parity says whose they were)
         bool ok = true;
         SkWalk<kGrouped> w = make_walk();
         for (; ok && w.next(); ++lt) {
             const uint32_t ab = lt % BUFS, use = lt / BUFS;
+            const uint32_t n_stages = static_cast<uint32_t>(w.s1 - w.s0);
+            // which of the two issuer pairs had a stage of this segment (a pair without one left its accumulator untouched)
+            const bool has0 = !G::kSplitK || n_stages >= 2 || (it & 1u) == 0u;
+            const bool has1 = G::kSplitK && (n_stages >= 2 || (it & 1u) == 1u);
+            it += n_stages;
             const SkProblem* p = w.p;
             const int M = p->M, N = p->N;
             const long long ldc = p->ldc;
@@ -454,26 +474,53 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
                 }
                 const int col = w.block * kSkItemCols + h * 128 + col_in_block;
                 int32_t* out = p->C + col;
+                // A batch of up to 64 rows goes into registers (the two issuer pairs' accumulators added), and when the
+                // last batch is there the accumulator is released, before any of its rows is stored: with one buffer per
+                // block the issuers wait for exactly this.
+                constexpr int kBatch = NB / 16 < 4 ? NB / 16 : 4;
 #pragma unroll
-                for (int c = 0; c < NB / 16; ++c) {
-                    uint32_t r[16];
-                    tmem_ld_32x32_x16(tmem_base + ((q * 32) << 16) + (ab * 2 + h) * NB + 16 * c, r);
+                for (int c0 = 0; c0 < NB / 16; c0 += kBatch) {
+                    uint32_t r[kBatch][16];
+#pragma unroll
+                    for (int c = 0; c < kBatch; ++c) {
+                        if (has0) {
+                            tmem_ld_32x32_x16(tmem_base + ((q * 32) << 16) + ((ab * G::kParts + 0) * 2 + h) * NB + 16 * (c0 + c), r[c]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) r[c][j] = 0;
+                        }
+                    }
+                    if constexpr (G::kSplitK) {
+                        if (has1) {
+#pragma unroll
+                            for (int c = 0; c < kBatch; ++c) {
+                                uint32_t r1[16];
+                                tmem_ld_32x32_x16(tmem_base + ((q * 32) << 16) + ((ab * G::kParts + 1) * 2 + h) * NB + 16 * (c0 + c), r1);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int j = 0; j < 16; ++j) r[c][j] += r1[j];
+                            }
+                        }
+                    }
                     tmem_ld_wait();
-                    if (c == NB / 16 - 1) {      // this block's accumulator has been read: its issuer may use it again
+                    if (c0 + kBatch >= NB / 16) {      // this block's accumulator has been read: its issuers may use it again
                         tc_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&acc_empty[ab * 2 + h]);
                     }
                     if (col >= N) continue;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int row = 16 * c + j;
-                        if (row < M) {
-                            int32_t* dst = out + static_cast<size_t>(row) * ldc;
-                            int32_t v = static_cast<int32_t>(r[j]);
-                            if (w.add_prev) v += __ldcg(dst);
-                            if (w.last) *dst = v >> 6;
-                            else __stcg(dst, v);
+                    for (int c = 0; c < kBatch; ++c) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int row = 16 * (c0 + c) + j;
+                            if (row < M) {
+                                int32_t* dst = out + static_cast<size_t>(row) * ldc;
+                                int32_t v = static_cast<int32_t>(r[c][j]);
+                                if (w.add_prev) v += __ldcg(dst);
+                                if (w.last) *dst = v >> 6;
+                                else __stcg(dst, v);
+                            }
                         }
                     }
                 }
