@@ -60,7 +60,7 @@ constexpr int kSkBK = 128;                        // k-rows per stage
 constexpr int kSkItemCols = 256;                  // weight columns per item: two MMA blocks of 128
 constexpr int kSkWpRowBytes = kSkItemCols / 4;    // 64
 constexpr int kSkWpBytes = kSkBK * kSkWpRowBytes; // 8192
-constexpr int kSkThreads = 18 * 32;               // warps 16 and 17: the second pair of MMA issuers
+constexpr int kSkBaseWarps = 16;                  // + two warps per additional pair of MMA issuers (SkGeom::kThreads)
 constexpr int kSkFirstExpandWarp = 4, kSkFirstEpilogueWarp = 12;
 constexpr uint32_t kSkStageCols = 64;              // operand stage: 2 blocks x 128 K-bytes = 2 x 32 columns
 constexpr int kSkMaxCtas = 256;                   // flags per launch slot
@@ -74,10 +74,13 @@ struct SkGeom {
     // spends 180 on a commit, far more than the tensor pipe needs to execute them; two threads per block double that.)
     // (Giving the second pair half of the activation rows instead, for NB = 64, was measured: every issuer then meets
     // every stage, and the stage rate is that of two issuers again.)
-    static constexpr bool kSplitK = NB <= 64;
-    static constexpr int kParts = kSplitK ? 2 : 1;
+    // (Four pairs for NB <= 32, which leaves room for one accumulator buffer only, were measured as well: 170-176 us
+    // against 158 us for the 210 projections of the header's example.)
+    static constexpr int kParts = NB <= 64 ? 2 : 1;              // pairs of issuers; stage i goes to pair i % kParts
+    static constexpr bool kSplitK = kParts > 1;
     static constexpr int kAccBufs = NB <= 32 ? 2 : 1;            // accumulator buffers per 128-column block and part
     static constexpr int kTStages = NB == 16 ? 6 : 4;            // operand ring (tensor memory)
+    static constexpr int kThreads = (kSkBaseWarps + 2 * (kParts - 1)) * 32;   // 18 or 16 warps
     static constexpr int kWStages = NB == 128 ? 8 : 16;          // packed-weight ring (shared memory): what is in flight from HBM
     static constexpr int kAStages = NB == 128 ? 6 : NB == 64 ? 8 : 16;   // activation ring (shared memory)
     static constexpr uint32_t kRingCol = 2 * kParts * kAccBufs * NB;   // after the accumulators: [buffer][part][block] x NB columns
@@ -210,7 +213,7 @@ struct SkWalk {
 };
 
 template <int NB, bool kGrouped>
-__global__ void __launch_bounds__(kSkThreads, 1)
+__global__ void __launch_bounds__(SkGeom<NB>::kThreads, 1)
 ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingle sg,
                          const SkProblem* __restrict__ probs, const SkItem* __restrict__ items,
                          const int* __restrict__ cta_first, int* __restrict__ flags, int epoch,
@@ -329,7 +332,7 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
                 for (uint32_t j = first; j < it; ++j) mbar_drain(&a_full[j % AS], (j / AS) & 1);
             }
         }
-    } else if (warp == 1 || warp == 3 || (G::kParts == 2 && warp >= 16)) {
+    } else if (warp == 1 || warp == 3 || (warp >= 16 && 1 + ((warp - 16) >> 1) < G::kParts)) {
         // ================================================================ MMA issuers
         // One thread per 128-column block of the box and, for NB <= 64, per parity of the stage count: warps 1 and 3
         // take the even stages (counted over the CTA's whole walk), warps 16 and 17 the odd ones, each into accumulators
@@ -337,8 +340,8 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
         // arithmetic, 60-90 cycles per MMA, 180 per commit -- is what bounds the stage rate of this kernel, which is why
         // it is split four ways and kept short: ring positions and the descriptor's low word advance by additions.
         if (lane == 0) {
-            const uint32_t hsel = (warp == 3 || warp == 17) ? 1u : 0u;
-            const uint32_t part = warp >= 16 ? 1u : 0u;
+            const uint32_t hsel = warp < 16 ? (warp == 3 ? 1u : 0u) : static_cast<uint32_t>(warp & 1);
+            const uint32_t part = warp < 16 ? 0u : 1u + (static_cast<uint32_t>(warp - 16) >> 1);
             uint32_t it = 0;
             const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);          // stride 1024 B, version 1, 128-byte swizzle
             const uint32_t desc_lo0 = ((smem_u32(sAct) & 0x3FFFFu) >> 4) | (1u << 16);  // start address, leading offset 16 B
@@ -355,7 +358,7 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
                 const uint32_t d = tmem_base + ((ab * G::kParts + part) * 2 + hsel) * NB;
                 uint32_t acc = 0;
                 for (int s = w.s0; s < w.s1; ++s, ++it) {
-                    if (G::kSplitK && (it & 1u) != part) {          // the other pair's stage: only the ring positions move
+                    if (G::kSplitK && (it & (G::kParts - 1)) != part) {   // another pair's stage: only the ring positions move
                         if (++sl == TS) { sl = 0; ph_t ^= 1; }
                         if (++al == AS) { al = 0; ph_a ^= 1; }
                         continue;
@@ -454,9 +457,9 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
         for (; ok && w.next(); ++lt) {
             const uint32_t ab = lt % BUFS, use = lt / BUFS;
             const uint32_t n_stages = static_cast<uint32_t>(w.s1 - w.s0);
-            // which of the two issuer pairs had a stage of this segment (a pair without one left its accumulator untouched)
-            const bool has0 = !G::kSplitK || n_stages >= 2 || (it & 1u) == 0u;
-            const bool has1 = G::kSplitK && (n_stages >= 2 || (it & 1u) == 1u);
+            // which issuer pairs had a stage of this segment (a pair without one left its accumulator untouched):
+            // pair p took the stages i of the walk with i % kParts == p
+            const uint32_t first_part = it & (G::kParts - 1);
             it += n_stages;
             const SkProblem* p = w.p;
             const int M = p->M, N = p->N;
@@ -483,23 +486,19 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
                     uint32_t r[kBatch][16];
 #pragma unroll
                     for (int c = 0; c < kBatch; ++c) {
-                        if (has0) {
-                            tmem_ld_32x32_x16(tmem_base + ((q * 32) << 16) + ((ab * G::kParts + 0) * 2 + h) * NB + 16 * (c0 + c), r[c]);
-                        } else {
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) r[c][j] = 0;
-                        }
+                        for (int j = 0; j < 16; ++j) r[c][j] = 0;
                     }
-                    if constexpr (G::kSplitK) {
-                        if (has1) {
 #pragma unroll
-                            for (int c = 0; c < kBatch; ++c) {
-                                uint32_t r1[16];
-                                tmem_ld_32x32_x16(tmem_base + ((q * 32) << 16) + ((ab * G::kParts + 1) * 2 + h) * NB + 16 * (c0 + c), r1);
-                                tmem_ld_wait();
+                    for (int part = 0; part < G::kParts; ++part) {
+                        if (((static_cast<uint32_t>(part) - first_part) & (G::kParts - 1)) >= n_stages) continue;
 #pragma unroll
-                                for (int j = 0; j < 16; ++j) r[c][j] += r1[j];
-                            }
+                        for (int c = 0; c < kBatch; ++c) {
+                            uint32_t r1[16];
+                            tmem_ld_32x32_x16(tmem_base + ((q * 32) << 16) + ((ab * G::kParts + part) * 2 + h) * NB + 16 * (c0 + c), r1);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) r[c][j] += r1[j];
                         }
                     }
                     tmem_ld_wait();

@@ -760,7 +760,7 @@ int launch_skinny_t(const tb200::SkProblem& single, const tb200::SkSingle& sg, c
                     int32_t* d_status, cudaStream_t st) {
     if (const int arc = ensure_smem_attr<tb200::ternary_skinny_tc_kernel<NB, kGrouped>>(tb200::SkGeom<NB>::kSmemBytes))
         return arc;
-    tb200::ternary_skinny_tc_kernel<NB, kGrouped><<<grid, tb200::kSkThreads, tb200::SkGeom<NB>::kSmemBytes, st>>>(
+    tb200::ternary_skinny_tc_kernel<NB, kGrouped><<<grid, tb200::SkGeom<NB>::kThreads, tb200::SkGeom<NB>::kSmemBytes, st>>>(
         single, sg, d_probs, d_items, d_first, d_flags, epoch, d_status);
     TB_CUDA(cudaGetLastError());
     return TERNIX_B200_OK;
