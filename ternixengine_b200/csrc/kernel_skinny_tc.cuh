@@ -5,15 +5,19 @@
 // 32-bit column), the activations are the B operand, straight from TMA in the K-major 128-byte-swizzle layout, with
 // the batch as the instruction's N (16, 32, 64 or 128).  Nothing expanded is ever written to shared memory.
 //
-// Where it pays.  Measured on B200: a tcgen05.mma with M = 128 occupies the tensor unit for about 120 cycles whatever
-// its N (16, 32 and 64 rows take the same time, and alternating between independent accumulators changes nothing: it
-// is occupancy of the unit, sized for N = 256, not a dependency between MMAs), so this kernel streams at most
-// one kilobyte of packed weights per SM and ~120 cycles, about 2.4 TB/s over the GPU, independent of the row count.
-// The warp-level mma.sync kernel (kernel_decode_mma.cuh) streams 5.5 TB/s up to 8 rows and 3.8 TB/s up to 16, but
-// needs one pass per 16 rows; from 17 rows up this kernel is the faster one (210 BitNet-2B projections: 225 us
-// against 288 us at 32 rows, 231 us against 538 us at 64 rows), and the dispatch uses it there.  Group members
-// with 65 to 128 rows run here as well (340 us at 128 rows; the paired prefill kernel pads them to 256-row tiles,
-// 416 us); a single product of that size is faster on the prefill kernel.
+// Where it pays, and what bounds it.  The tensor pipe is far from busy here (an N = 32 MMA occupies it for about 16
+// cycles; ncu shows the pipe 20 % active): what bounds the kernel is the instruction stream of the threads that ISSUE
+// the MMAs.  Measured on B200 with one issuing thread: a tcgen05.mma with N <= 64 leaves the thread every 60-90
+// cycles whatever its N (N = 128: 64 cycles, N = 256: 128 cycles, the pipe's own time), a tcgen05.commit costs it
+// about 180 cycles, a wait on an mbarrier that has long completed 60-150; a second issuing thread in another warp
+// runs at the same rate beside the first.  With one issuer per 128-column block (two threads) a stage of 8 KB of
+// packed weights took about 960 cycles, 2.4 TB/s over the GPU whatever the row count; with the stages dealt
+// alternately to two such pairs (four threads, accumulators of their own, added in the epilogue) 640 cycles,
+// 3.3 TB/s of packed weights.  The warp-level mma.sync kernel (kernel_decode_mma.cuh) streams 5.5 TB/s up to 8 rows and
+// 3.8 TB/s up to 16, but needs one pass per 16 rows; from 17 rows up this kernel is the faster one (210 BitNet-2B
+// projections: 158 us against 288 us at 32 rows, 207 us against 538 us at 64 rows), and the dispatch uses it
+// there.  Group members with 65 to 128 rows run here as well (274 us at 128 rows; the paired prefill kernel pads
+// them to 256-row tiles, 367 us); a single product of that size is faster on the prefill kernel.
 //
 // From packed bytes to the operand in 17 instructions per 1024 weights and warp:
 //   * a stage is 128 k-rows x 64 packed bytes (256 weight columns), TMA with the 64-byte swizzle;
@@ -26,16 +30,18 @@
 //     0xC0, i.e. 0, +64, -64 as int8 (the two top bits of a byte ARE the sign-extended code).  The accumulators hold
 //     64 * sum; the final arithmetic shift by 6 is exact.  Bound 64 * 128 * K < 2^31, K <= 262143.
 //
-// Tensor memory (512 columns): two accumulator buffers (one for NB = 128) x two 128-column blocks x NB columns, then
-// a ring of operand stages of 2 blocks x 32 columns each (6 stages for NB = 16 and 32, 4 otherwise).  Shared memory:
-// a ring of 16 (8 for NB = 128) packed-weight stages (8 KB each: what is in flight from HBM) and a ring of 16 / 16 /
-// 8 / 6 activation stages (NB rows x 128 bytes).  Each 128-column block has its own accumulator barriers, so with a
-// single buffer the issuer of block 0 starts the next item while the epilogue still reads block 1.
+// Tensor memory (512 columns): accumulators [buffer][issuer pair][128-column block] x NB columns (two buffers for
+// NB <= 32, one otherwise; two issuer pairs for NB <= 64, one for NB = 128), then a ring of operand stages of
+// 2 blocks x 32 columns each (6 stages for NB = 16, 4 otherwise).  Shared memory: a ring of 16 (8 for NB = 128)
+// packed-weight stages (8 KB each: what is in flight from HBM) and a ring of 16 / 16 / 8 / 6 activation stages
+// (NB rows x 128 bytes).  Each 128-column block has its own accumulator barriers, and the epilogue reads a whole
+// batch of up to 64 rows into registers and releases the accumulator before it stores any of them, so with a single
+// buffer the issuers wait for a few tcgen05.ld only.
 //
-// Roles (16 warps): 0 weight producer, 1 and 3 MMA issuers (one per 128-column block: a single thread's instruction
-// stream -- two waits, four instructions per MMA, a commit -- was what bounded the stage rate before it was split),
-// 2 activation producer, 4-11 expanders (lane quarter = warp % 4, the two warps of a quarter take the stages in
-// turn), 12-15 epilogue (lane quarter = warp % 4).
+// Roles (18 warps for NB <= 64, 16 for NB = 128): 0 weight producer; 1 and 3 MMA issuers of the even stages (one per
+// 128-column block), 16 and 17 those of the odd stages (NB <= 64; stages are counted over the CTA's whole walk);
+// 2 activation producer; 4-11 expanders (lane quarter = warp % 4, the two warps of a quarter take the stages in
+// turn); 12-15 epilogue (lane quarter = warp % 4).
 //
 // Work.  Grouped launches walk a host-built list of (problem, 256-column block) items over the whole of K.  One
 // problem alone runs as whole-K items too whenever they occupy the machine reasonably (items of 128 columns, half a
