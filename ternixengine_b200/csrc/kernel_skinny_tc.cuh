@@ -15,8 +15,8 @@
 // alternately to two such pairs (four threads, accumulators of their own, added in the epilogue) 640 cycles,
 // 3.3 TB/s of packed weights.  The warp-level mma.sync kernel (kernel_decode_mma.cuh) streams 5.5 TB/s up to 8 rows and
 // 3.8 TB/s up to 16, but needs one pass per 16 rows; from 17 rows up this kernel is the faster one (210 BitNet-2B
-// projections: 158 us against 288 us at 32 rows, 207 us against 538 us at 64 rows), and the dispatch uses it
-// there.  Group members with 65 to 128 rows run here as well (274 us at 128 rows; the paired prefill kernel pads
+// projections: 156 us against 288 us at 32 rows, 200 us against 538 us at 64 rows), and the dispatch uses it
+// there.  Group members with 65 to 128 rows run here as well (247 us at 128 rows; the paired prefill kernel pads
 // them to 256-row tiles, 367 us); a single product of that size is faster on the prefill kernel.
 //
 // From packed bytes to the operand in 17 instructions per 1024 weights and warp:
@@ -38,7 +38,8 @@
 // batch of up to 64 rows into registers and releases the accumulator before it stores any of them, so with a single
 // buffer the issuers wait for a few tcgen05.ld only.
 //
-// Roles (18 warps for NB <= 64, 16 for NB = 128): 0 weight producer; 1 and 3 MMA issuers of the even stages (one per
+// Roles (19 warps for NB <= 64, 17 for NB = 128; the last one forwards "activations landed" to the `ready` barriers,
+// so that an issuer waits on one barrier per stage): 0 weight producer; 1 and 3 MMA issuers of the even stages (one per
 // 128-column block), 16 and 17 those of the odd stages (NB <= 64; stages are counted over the CTA's whole walk);
 // 2 activation producer; 4-11 expanders (lane quarter = warp % 4, the two warps of a quarter take the stages in
 // turn); 12-15 epilogue (lane quarter = warp % 4).
@@ -86,7 +87,8 @@ struct SkGeom {
     static constexpr bool kSplitK = kParts > 1;
     static constexpr int kAccBufs = NB <= 32 ? 2 : 1;            // accumulator buffers per 128-column block and part
     static constexpr int kTStages = NB == 16 ? 6 : 4;            // operand ring (tensor memory)
-    static constexpr int kThreads = (kSkBaseWarps + 2 * (kParts - 1)) * 32;   // 18 or 16 warps
+    static constexpr int kForwardWarp = kSkBaseWarps + 2 * (kParts - 1);     // the warp after the last issuer
+    static constexpr int kThreads = (kForwardWarp + 1) * 32;                 // 19 or 17 warps
     static constexpr int kWStages = NB == 128 ? 8 : 16;          // packed-weight ring (shared memory): what is in flight from HBM
     static constexpr int kAStages = NB == 128 ? 6 : NB == 64 ? 8 : 16;   // activation ring (shared memory)
     static constexpr uint32_t kRingCol = 2 * kParts * kAccBufs * NB;   // after the accumulators: [buffer][part][block] x NB columns
@@ -276,7 +278,7 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
             mbar_init(&a_empty[s], 1);
         }
         for (int s = 0; s < TS; ++s) {
-            mbar_init(&ready[s], 4);
+            mbar_init(&ready[s], 5);                   // the four quarters and the activation forwarder
             mbar_init(&t_free[s], 2);                  // the two issuers that read the stage
         }
         for (int b = 0; b < 4; ++b) {
@@ -369,7 +371,8 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
                         if (++al == AS) { al = 0; ph_a ^= 1; }
                         continue;
                     }
-                    if (!mbar_wait(&ready[sl], ph_t, abort_flag) || !mbar_wait(&a_full[al], ph_a, abort_flag)) { ok = false; break; }
+                    // `ready` also says that the stage's activations have landed (the forwarder's arrival)
+                    if (!mbar_wait(&ready[sl], ph_t, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
                     if (mine) {
                         const uint32_t a_col = tmem_base + G::kRingCol + sl * kSkStageCols + hsel * 32;
@@ -388,6 +391,24 @@ ternary_skinny_tc_kernel(const __grid_constant__ SkProblem single, const SkSingl
             }
             tc_commit(drain);                      // both issuers: nothing of theirs is in flight when tensor memory is freed
             mbar_wait(drain, 0, abort_flag);
+        }
+    } else if (warp == G::kForwardWarp) {
+        // ================================================================ activation forwarder
+        // Passes "the activations of stage i have landed" on to the stage's `ready` barrier, so that an issuer, whose
+        // instruction stream is what bounds the kernel, waits on one barrier per stage instead of two.  Like an
+        // expander it may arrive for a stage only when the operand slot's previous use has retired.
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            SkWalk<kGrouped> w = make_walk();
+            while (ok && w.next()) {
+                for (int s = w.s0; s < w.s1; ++s, ++it) {
+                    const uint32_t st = it % TS, al = it % AS;
+                    if (!mbar_wait_backoff(&t_free[st], ((it / TS) & 1) ^ 1, abort_flag, 32) ||
+                        !mbar_wait_backoff(&a_full[al], (it / AS) & 1, abort_flag, 32)) { ok = false; break; }
+                    mbar_arrive(&ready[st]);
+                }
+            }
         }
     } else if (warp >= kSkFirstExpandWarp && warp < kSkFirstEpilogueWarp) {
         // ================================================================ expanders: packed bytes -> operand rows in tensor memory
