@@ -10,7 +10,9 @@
 //   * activations: 128 rows x 256 K-bytes per CTA and stage (two boxes of 128 K-bytes), straight from TMA into the
 //     K-major 128-byte-swizzle layout the B descriptor reads (the pair's two halves make the N = 256 columns of the instruction);
 //   * weights: 256 k-rows x 32 packed bytes per CTA and stage (its 128 weight columns), TMA with the 32-byte
-//     swizzle.  An expander warp reads them with ldmatrix.m16n16.x2.trans.b8, which leaves, in lane (c, t) =
+//     swizzle, through a ring of their own that runs eight k-blocks ahead (they are small and mostly come from DRAM;
+//     the activations come from L2 through a ring of four; a weight slot is free as soon as the expanders have read
+//     it).  An expander warp reads them with ldmatrix.m16n16.x2.trans.b8, which leaves, in lane (c, t) =
 //     (lane / 4, lane % 4), the bytes of k-rows 4t..4t+3 of packed byte column c -- exactly what lane (c, t) has to
 //     supply to tcgen05.st.16x128b for operand row c, columns t.  So the operand rows (tensor-memory lanes) are
 //     numbered the way the load delivers them: lane l of a 32-lane quarter holds weight column 4 (l % 8) + l / 8 of
@@ -19,7 +21,7 @@
 //     accumulators hold 64 x the sum and the epilogue's arithmetic shift by 6 is exact.  17 instructions per 1024
 //     weights and warp (the first version, which kept the natural row order, needed eight shuffles and 45
 //     instructions, and the tensor pipe waited for the expanders 11 % of the time).  Nothing expanded ever touches
-//     shared memory; the ring holds 40 KB per 256-deep stage instead of 112 KB.
+//     shared memory; the rings hold 40 KB per 256-deep stage (32 KB of activations, 8 KB of packed weights) instead of 112 KB.
 //   * epilogue: lane = weight column (in the expanders' numbering), tensor-memory column = activation row.  The
 //     epilogue warps read their whole share of the accumulator into registers and release it at once (about 700
 //     cycles from the last MMA's retirement to the first MMA of the next tile).  A step then moves 32 activation
@@ -42,11 +44,11 @@
 // the power cap is higher as well).  A deeper shared-memory ring, L2 prefetches of the weight boxes, evict-first
 // stores and stores from registers were all measured and change nothing.
 //
-// Roles per CTA (warps, in whole warpgroups because registers are moved between them): 0 TMA producer; 1 MMA
-// issuer (leader CTA only: eight M=256 N=256 K=32 pair MMAs per stage, commit -> `empty` of both CTAs); 2-3 idle;
-// 4-11 expanders (lane quarter = warp % 4; the two warps of a quarter take the stages in turn; after
-// tcgen05.wait::st they arrive on the leader's `ready`, which therefore also says that this CTA's activation tile
-// has landed); 12-19 epilogue, two groups of four that take alternate steps.
+// Roles per CTA (warps, in whole warpgroups because registers are moved between them): 0 activation producer;
+// 1 MMA issuer (leader CTA only: eight M=256 N=256 K=32 pair MMAs per stage, commit -> `empty` of both CTAs);
+// 2 weight producer; 3 idle; 4-11 expanders (lane quarter = warp % 4; the two warps of a quarter take the stages
+// in turn; after tcgen05.wait::st they arrive on the leader's `ready`, quarter 0 only once the stage's activations
+// have landed, so `ready` says that too); 12-19 epilogue, two groups of four that take alternate steps.
 //
 // Exactness: int8 x int8 -> int32 on weights decoded as -64/0/+64; |64 * sum| <= 64 * 128 * K < 2^31 for
 // K <= 262143 (the host checks), and the shift by 6 in the epilogue restores the sum exactly.
@@ -84,7 +86,7 @@ struct Tc3Geom {
     static constexpr int kRowsPerCta = TA / 2;                   // activation rows a CTA loads per stage
     static constexpr int kActBox = kRowsPerCta * 128;            // one TMA box: rows x 128 K-bytes, 128-byte swizzle
     static constexpr int kActBytes = 2 * kActBox;
-    static constexpr int kStageBytes = kActBytes + kTc3WpBytes;
+    static constexpr int kStageBytes = kActBytes;                // a stage of the activation ring (the weights have a ring of their own)
     static constexpr int kAccBufs = 256 / TA;                    // accumulators of TA columns in tensor-memory columns 0-255
 #ifdef TB200_TC3_SMEM_STAGES_128
     static constexpr int kSmemStages = TA == 128 ? TB200_TC3_SMEM_STAGES_128 : kTc3Stages;
@@ -136,13 +138,18 @@ __device__ __forceinline__ void warpgroup_regs_acquire() {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
 }
 #ifndef TB200_TC3_EPI_BUFS
-#define TB200_TC3_EPI_BUFS 2
+#define TB200_TC3_EPI_BUFS 1
 #endif
 constexpr int kTc3EpiBufs = TB200_TC3_EPI_BUFS;   // staging buffers per epilogue group
 constexpr int kTc3EpiBytes = 32 * 128 * 4;        // one step of the epilogue: 32 activation rows x 128 weight columns
+#ifndef TB200_TC3_W_STAGES
+#define TB200_TC3_W_STAGES 8
+#endif
+constexpr int kTc3WStages = TB200_TC3_W_STAGES;   // packed-weight ring: 8 KB stages, loaded up to this many k-blocks ahead (they come from DRAM)
+static_assert(kTc3WStages % (TB200_TC3_EXPAND_WARPS_ / 4) == 0, "an expander warp must meet every phase of the barriers it waits on");
 template <int TA>
 constexpr size_t tc3_smem_bytes() {
-    return 1024 + size_t(Tc3Geom<TA>::kSmemStages) * Tc3Geom<TA>::kStageBytes +
+    return 1024 + size_t(Tc3Geom<TA>::kSmemStages) * Tc3Geom<TA>::kStageBytes + size_t(kTc3WStages) * kTc3WpBytes +
            size_t(kTc3EpiGroups) * kTc3EpiBufs * kTc3EpiBytes + 512;
 }
 static_assert(tc3_smem_bytes<128>() <= 227 * 1024 && tc3_smem_bytes<256>() <= 227 * 1024, "shared memory: 227 KB per CTA");
@@ -282,15 +289,18 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sAct = base;                                            // [S][2 boxes][rows][128 k]  128-byte swizzle
-    uint8_t* sWp = sAct + S * G::kActBytes;                          // [S][256 k][32]             32-byte swizzle
-    uint8_t* sEpi = sWp + S * kTc3WpBytes;                           // [groups][bufs][32 rows][128] int32
+    constexpr int WS = kTc3WStages;
+    uint8_t* sWp = sAct + S * G::kActBytes;                          // [WS][256 k][32]            32-byte swizzle
+    uint8_t* sEpi = sWp + WS * kTc3WpBytes;                          // [groups][bufs][32 rows][128] int32
     uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + kTc3EpiGroups * kTc3EpiBufs * kTc3EpiBytes);
     uint64_t* full = bars;                         // [S]  this CTA's TMA bytes of a stage have landed
     uint64_t* empty = full + S;                    // [S]  the pair's MMAs on a stage have retired
     uint64_t* ready = empty + S;                   // [TS] (leader) both CTAs' operands of a stage are in place
     uint64_t* acc_full = ready + TS;               // [BUFS]
     uint64_t* acc_empty = acc_full + BUFS;         // [BUFS] (leader)
-    uint64_t* drain = acc_empty + BUFS;
+    uint64_t* w_full = acc_empty + BUFS;           // [WS] a packed-weight stage has landed
+    uint64_t* w_empty = w_full + WS;               // [WS] this CTA's four lane quarters have read it
+    uint64_t* drain = w_empty + WS;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -319,6 +329,10 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             mbar_init(&empty[s], 1);
         }
         for (int s = 0; s < TS; ++s) mbar_init(&ready[s], 2 * 4);
+        for (int s = 0; s < WS; ++s) {
+            mbar_init(&w_full[s], 1);
+            mbar_init(&w_empty[s], 4);
+        }
         for (int b = 0; b < BUFS; ++b) {
             mbar_init(&acc_full[b], 1);
             mbar_init(&acc_empty[b], 8 * kTc3EpiGroups);
@@ -356,7 +370,6 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 // change of problem does not stall the ring for the latency of two descriptor reads
                 if constexpr (kGrouped) w.prefetch_next_maps();
                 const int row0 = w.a_t * TA + rank * kRowsPerCta;
-                const int wp_x = (w.w_t * kTc3TileW + rank * 128) / 4;
                 for (int kb = 0; kb < w.k_blocks; ++kb, ++it) {
                     const uint32_t s = it % S;
                     if (!mbar_wait_backoff(&empty[s], ((it / S) & 1) ^ 1, abort_flag, 32)) { ok = false; break; }
@@ -364,7 +377,6 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #pragma unroll
                     for (int j = 0; j < 2; ++j)
                         tma_load_2d(sAct + s * G::kActBytes + j * G::kActBox, w.ta, kb * kTc3BK + j * 128, row0, &full[s]);
-                    tma_load_2d(sWp + s * kTc3WpBytes, w.tw, wp_x, kb * kTc3BK, &full[s]);
                 }
             }
             if (!ok) {
@@ -401,7 +413,33 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             tc_commit_pair(drain);
             mbar_wait(drain, 0, abort_flag);
         }
-      }     // warps 2, 3 have nothing to do: they only fill the control warpgroup
+      } else if (warp == 2) {
+        // ================================================================ packed weights: a ring of their own
+        // The weight boxes are small (8 KB) and, unlike the activations, mostly come from DRAM, so they are requested
+        // kTc3WStages k-blocks ahead instead of the activation ring's four; a slot is free again as soon as the four
+        // expander quarters have read it, long before the stage's MMAs retire.
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            Tc3Walk<kGrouped> w = make_walk();
+            if constexpr (kGrouped) w.prefetch_next_maps();
+            else tma_prefetch_desc(&tmap_w);
+            while (ok && w.next()) {
+                if constexpr (kGrouped) w.prefetch_next_maps();
+                const int wp_x = (w.w_t * kTc3TileW + rank * 128) / 4;
+                for (int kb = 0; kb < w.k_blocks; ++kb, ++it) {
+                    const uint32_t sw = it % WS;
+                    if (!mbar_wait_backoff(&w_empty[sw], ((it / WS) & 1) ^ 1, abort_flag, 32)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&w_full[sw], kTc3WpBytes);
+                    tma_load_2d(sWp + sw * kTc3WpBytes, w.tw, wp_x, kb * kTc3BK, &w_full[sw]);
+                }
+            }
+            if (!ok) {
+                const uint32_t first = it > static_cast<uint32_t>(WS) ? it - WS : 0;
+                for (uint32_t j = first; j < it; ++j) mbar_drain(&w_full[j % WS], (j / WS) & 1);
+            }
+        }
+      }     // warp 3 has nothing to do: it only fills the control warpgroup
     } else if (warp < kTc3FirstEpilogueWarp) {
         warpgroup_regs_release<kTc3RegsExpand>();
         // ================================================================ expanders: packed bytes -> int8 rows of the A operand
@@ -427,9 +465,9 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         while (ok && w.next()) {
             for (int kb = 0; kb < w.k_blocks; ++kb, ++it) {
                 if (it % kTc3WarpsPerQuarter != slot) continue;
-                const uint32_t s = it % S, ts = it % TS;
-                if (!mbar_wait_backoff(&full[s], (it / S) & 1, abort_flag, TB200_TC3_SLEEP_NS)) { ok = false; break; }
-                const uint32_t wp = wp_sa + s * kTc3WpBytes + ld_off;
+                const uint32_t s = it % S, ts = it % TS, sw = it % WS;
+                if (!mbar_wait_backoff(&w_full[sw], (it / WS) & 1, abort_flag, TB200_TC3_SLEEP_NS)) { ok = false; break; }
+                const uint32_t wp = wp_sa + sw * kTc3WpBytes + ld_off;
                 uint32_t X[kTc3BK / 32], Y[kTc3BK / 32];
 #pragma unroll
                 for (int g = 0; g < kTc3BK / 32; ++g) {
@@ -438,10 +476,10 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     X[g] = odd ? m[1] : m[0];
                     Y[g] = odd ? m[3] : m[2];
                 }
-                if constexpr (S != TS) {
+                {
                     // The operand slot in tensor memory is free once the MMAs of stage it - TS have retired, which is what
-                    // the `empty` barrier of that stage's shared-memory slot says.  (That barrier cannot be a phase ahead:
-                    // its next completion needs stage it - TS + S > it expanded, and this warp expands in order.)
+                    // the `empty` barrier of that stage's activation slot says.  (That barrier cannot be a phase ahead:
+                    // its next completion needs stage it - TS + S >= it expanded, and this warp expands in order.)
                     if (it >= static_cast<uint32_t>(TS)) {
                         const uint32_t j = it - TS;
                         if (!mbar_wait_backoff(&empty[j % S], (j / S) & 1, abort_flag, 32)) { ok = false; break; }
@@ -456,8 +494,13 @@ ternary_gemm_tc3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     tmem_st_16x128_x2(a_col + (16u << 16) + 8 * g, decode_field_x64<2>(X[g]), decode_field_x64<3>(X[g]),
                                       decode_field_x64<2>(Y[g]), decode_field_x64<3>(Y[g]));
                 }
+                // the stage's packed bytes have been decoded out of their registers: the weight slot is free
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&w_empty[sw]);
                 tmem_st_wait();
                 tc_fence_before_sync();
+                // `ready` also has to say that this CTA's activations of the stage have landed: quarter 0 answers for that
+                if (q == 0 && !mbar_wait_backoff(&full[s], (it / S) & 1, abort_flag, 32)) { ok = false; break; }
                 __syncwarp();
                 if (lane == 0) {
                     if (leader) mbar_arrive(&ready[ts]);
