@@ -539,6 +539,16 @@ def should_shard(M: int, K: int, N: int, world: int, granule: int = 64, out_byte
     return max(compute / world, gather) + _GATHER_FIXED_S < compute
 
 
+def host_slab_rows(M: int, N: int) -> int:
+    """Rows per slab of the host-operand step (forward_host): about 64 MB of int32 C per slab, at most 16 slabs,
+    multiples of 256 rows (whole tiles of the prefill kernel), never more than M."""
+    if M <= 0:
+        return 0
+    slabs = min(16, max(1, (4 * M * N) // (64 << 20)))
+    rows = -(-M // slabs)
+    return min(M, -(-rows // 256) * 256)
+
+
 def gather_buffer_index(step: int) -> int:
     """Which of a rank's two gathered-C buffers step `step` fills.  Two buffers, because the barrier after a step
     only says that every rank's stores have landed: a fast rank may start its next step, and store into its peers,
@@ -777,8 +787,7 @@ class ShardedTernaryLinear:
                 out_host = torch.empty((M, self.N), dtype=torch.int32, pin_memory=True)
             return self._handle.matmul_host(a_host, out_host)
         if slab_rows is None:
-            slabs = min(16, max(1, (4 * M * self.N) // (64 << 20)))
-            slab_rows = min(M, -(-(-(-M // slabs)) // 256) * 256)
+            slab_rows = host_slab_rows(M, self.N)
         n_slabs = -(-M // slab_rows)
         dev = self.device
         hs = getattr(self, "_host_state", None)

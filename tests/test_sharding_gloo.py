@@ -57,10 +57,24 @@ def test_column_sharded_product_over_gloo(world, shape, granule, tmp_path):
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
 
 
+def test_host_slab_plan():
+    """forward_host's slab extent: about 64 MB of C per slab, whole 256-row tiles, at most 16 slabs, never above M."""
+    sys.path.insert(0, ROOT)
+    import ternixengine_b200 as tb
+    assert tb.host_slab_rows(4096, 28672) == 768                   # config 3: 470 MB of C in 6 slabs
+    assert tb.host_slab_rows(100, 1024) == 100                     # small products are one slab
+    assert tb.host_slab_rows(1, 6912) == 1
+    assert tb.host_slab_rows(0, 64) == 0
+    for (m, n) in [(4096, 28672), (65536, 8192), (300, 832), (1 << 20, 4096), (5000, 100000)]:
+        rows = tb.host_slab_rows(m, n)
+        assert 0 < rows <= m and (rows % 256 == 0 or rows == m)
+        assert -(-m // rows) <= 16
+
+
 def test_should_shard_policy():
     sys.path.insert(0, ROOT)
     import ternixengine_b200 as tb
-    # config 3 (K = 8192, int32 C on every rank): the gather hides under the compute at 2 and 4 GPUs, not at 8
+    # config 3 (K = 8192, int32 C on every rank): sharding pays at 2 GPUs, not at 4 or 8
     assert tb.should_shard(4096, 8192, 28672, 2)
     assert not tb.should_shard(4096, 8192, 28672, 4)               # the gather (0.59 ms) outweighs one GPU's 0.55 ms
     assert not tb.should_shard(4096, 8192, 28672, 8)
